@@ -1,0 +1,167 @@
+/*
+ * rgx -- differentiable Gaussian ray marching for NVIDIA B200 (sm_100a).
+ *
+ * C ABI of the shared library librgx.so.  It replaces, for one device, what the
+ * reference renderer does between its autograd boundary and the GPU: bounding
+ * boxes, acceleration-structure build, per-view colour evaluation, the forward
+ * ray march and the backward ray march with all gradient reductions.
+ *
+ * Conventions
+ *   - every pointer named in a struct or argument list is a DEVICE pointer to
+ *     contiguous fp32 (or int32) data owned by the caller, unless stated;
+ *   - every call enqueues its work on the given CUDA stream and returns without
+ *     synchronising; no call performs a device->host copy unless stated;
+ *   - return value 0 is success, negative values are RGX_E_*; nothing throws;
+ *   - a context belongs to one device and one host thread at a time;
+ *   - the context owns its workspace (device memory grown on demand in
+ *     rgx_build / rgx_forward / rgx_backward, freed in rgx_destroy).
+ */
+#ifndef RGX_H
+#define RGX_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define RGX_API __attribute__((visibility("default")))
+#else
+#define RGX_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct rgx_ctx rgx_ctx;
+typedef void* rgx_stream; /* a cudaStream_t */
+
+enum {
+    RGX_OK = 0,
+    RGX_E_INVALID = -1, /* bad argument (null pointer, negative size, unsupported SH count ...) */
+    RGX_E_CUDA = -2,    /* a CUDA runtime call failed; see rgx_last_error */
+    RGX_E_NOT_BUILT = -3, /* rgx_forward / rgx_backward before rgx_build, or with a different Gaussian count */
+    RGX_E_TOO_LARGE = -4  /* size beyond a fixed capacity (see the call's comment) */
+};
+
+/* The Gaussian set: the eight tensors the reference operator receives
+ * (optix_raycasting/render_optix.py:94-95), produced by PointCloud.get_data
+ * (classes/point_cloud.py:549-559). */
+typedef struct rgx_scene {
+    int32_t n;              /* number of Gaussians */
+    int32_t sh_coeffs;      /* coefficients per channel, (degree+1)^2: 1, 4, 9 or 16 */
+    int32_t num_lobes;      /* spherical-Gaussian lobes per Gaussian (0..8) */
+    const float* positions;      /* [n,3] */
+    const float* scales;         /* [n,3] already exponentiated */
+    const float* quaternions;    /* [n,4] (w,x,y,z), used as given (not renormalised) */
+    const float* densities;      /* [n]   raw; Gaussians with density <= sigma_threshold never contribute */
+    const float* color_features; /* [n,3,sh_coeffs] channel-major */
+    const float* sg_features;    /* [n,3,num_lobes] or NULL when num_lobes == 0 */
+    const float* sharpness;      /* [n,num_lobes] */
+    const float* lobe_axis;      /* [n,num_lobes,3] */
+} rgx_scene;
+
+/* Pinhole camera: the launch-parameter fields of optix_raycasting/optix_utils.py:258-266. */
+typedef struct rgx_camera {
+    float eye[3];          /* camera_center */
+    float u[3], v[3], w[3];/* columns 0,1,2 of world_view_transform[:3,:3]: camera x (right), y (down), z (forward) */
+    float tan_half_fov[2]; /* tan(FoVx/2), tan(FoVy/2) */
+    float pp[2];           /* principal point as a fraction of the image (0.5 = centre) */
+    int32_t width, height; /* in rays: image size times supersampling */
+} rgx_camera;
+
+/* Marching parameters: Params of cuda_train/forward/gaussians_aabb.h:14-44 plus the
+ * constants of :2-5 that a caller may need to vary. */
+typedef struct rgx_march {
+    float dt_step;
+    int32_t dynamic_sampling;
+    int32_t max_prim_slice;    /* hit cap per 32-sample slab; further hits of that slab are dropped and counted */
+    int32_t white_background;
+    float transmittance_eps;   /* 1e-3 in the reference */
+    int32_t row_begin, row_end;/* image rows [row_begin,row_end) to march; rays outside are left untouched */
+    int32_t flags;             /* RGX_FLAG_* */
+} rgx_march;
+
+enum {
+    RGX_FLAG_COUNT_WORK = 1,     /* also accumulate the work counters read by rgx_read_counters */
+    RGX_FLAG_BRUTE_FORCE = 2,    /* skip the hierarchy: test every Gaussian in every query (validation only) */
+    RGX_FLAG_EXACT_SH_GRAD = 4,  /* backward: exact d(basis 9)/dy instead of the reference's term (utils/sh_utils.cu:367) */
+    RGX_FLAG_ACCUMULATE = 8      /* backward: add into the gradient tensors instead of overwriting them */
+};
+
+/* Gradient tensors, shaped like the inputs (what RenderOptixFunction.backward
+ * returns, render_optix.py:199).  sg_* may be NULL when num_lobes == 0. */
+typedef struct rgx_grads {
+    float* positions;      /* [n,3] march gradient plus the view-direction term */
+    float* scales;         /* [n,3] w.r.t. the exponentiated scales */
+    float* quaternions;    /* [n,4] derivative of the un-normalised rotation formula */
+    float* densities;      /* [n] */
+    float* color_features; /* [n,3,sh_coeffs] */
+    float* sg_features;    /* [n,3,num_lobes] */
+    float* sharpness;      /* [n,num_lobes] */
+    float* lobe_axis;      /* [n,num_lobes,3] */
+} rgx_grads;
+
+/* Work counters summed over the rays marched since the last reset (host struct). */
+typedef struct rgx_counters {
+    uint64_t rays;          /* rays marched */
+    uint64_t slabs;         /* S: slab iterations */
+    uint64_t slabs_hit;     /* S_h: slabs with at least one hit */
+    uint64_t closest_queries;/* Q_c: closest-hit queries */
+    uint64_t hits;          /* P: hit-list entries summed over slabs */
+    uint64_t pairs_inside;  /* E_in: (sample, Gaussian) pairs inside the truncation ellipsoid */
+    uint64_t overflow_slabs;/* OVF: slabs that reached max_prim_slice */
+    uint64_t node_tests;    /* box tests against hierarchy nodes (32 per warp step) */
+    uint64_t prim_tests;    /* box tests against Gaussians */
+    uint64_t ellipsoid_tests;/* exact ray/ellipsoid tests */
+    uint64_t stack_overflows;/* traversal-stack overflows (results invalid if non-zero) */
+    uint64_t hits_hash;     /* order-independent hash of every (ray, slab, Gaussian) hit triple */
+} rgx_counters;
+
+/* Replaces: ox.DeviceContext / module / pipeline creation (optix_utils.py:154-210). */
+RGX_API int rgx_create(int device, rgx_ctx** out);
+RGX_API void rgx_destroy(rgx_ctx* ctx);
+/* Host string describing the last failure on this context (never NULL). */
+RGX_API const char* rgx_last_error(const rgx_ctx* ctx);
+
+/* Replaces: ellipsoids_bbox_from_quat + create_acceleration_structure
+ * (optix_utils.py:82-109,139-142; called from render_optix.py:109-117).
+ * Computes per-Gaussian boxes of the sigma_threshold iso-ellipsoid, the scene box,
+ * 3*morton_bits-bit Morton keys of the centres (morton_bits 10 or 20), sorts them
+ * (CUB radix sort) and refits a 32-ary hierarchy bottom-up.  Only positions,
+ * scales, quaternions and densities of `scene` are read.  Must be called again
+ * whenever one of those four tensors changes. */
+RGX_API int rgx_build(rgx_ctx* ctx, const rgx_scene* scene, float sigma_threshold, int morton_bits, rgx_stream stream);
+
+/* Replaces: compute_cupy_rgb + launch_pipeline_forward (render_optix.py:121-131;
+ * device code cuda_train/forward/gaussians_aabb.cu, utils/sh_utils.cu:122-216).
+ * rgb [R,3] is required; alpha [R] (1 - final transmittance) and depth [R]
+ * (expected depth, cuda_gui/gaussians_aabb.cu:189-202) may be NULL.  R = width*height. */
+RGX_API int rgx_forward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, const rgx_march* march,
+                float* rgb, float* alpha, float* depth, rgx_stream stream);
+
+/* Replaces: launch_pipeline_backward + reduce_temp_grads + compute_cupy_sh_grad
+ * (render_optix.py:166-185; device code cuda_train/backward/gaussians_aabb.cu,
+ * utils/sh_utils.cu:218-412).  rgb is the forward's output for the same camera,
+ * dL_drgb [R,3] the incoming gradient; rays outside [row_begin,row_end) are not read. */
+RGX_API int rgx_backward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, const rgx_march* march,
+                 const float* rgb, const float* dL_drgb, const rgx_grads* grads, rgx_stream stream);
+
+/* Per-Gaussian view-dependent colour only (render_optix.py:19-32): rgb_out [n,3]
+ * in the caller's Gaussian order. */
+RGX_API int rgx_gaussian_colors(rgx_ctx* ctx, const rgx_scene* scene, const float eye[3], float* rgb_out,
+                        rgx_stream stream);
+
+/* Scene box computed by the last rgx_build, copied to host (synchronises the stream). */
+RGX_API int rgx_scene_box(rgx_ctx* ctx, float bb_min[3], float bb_max[3], rgx_stream stream);
+
+/* Work counters (RGX_FLAG_COUNT_WORK).  rgx_read_counters synchronises the stream. */
+RGX_API int rgx_reset_counters(rgx_ctx* ctx, rgx_stream stream);
+RGX_API int rgx_read_counters(rgx_ctx* ctx, rgx_counters* out, rgx_stream stream);
+
+/* Bytes of device memory currently held by the context's workspace. */
+RGX_API size_t rgx_workspace_bytes(const rgx_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RGX_H */

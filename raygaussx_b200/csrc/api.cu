@@ -1,0 +1,357 @@
+// C ABI of librgx.so: context, workspace and the entry points of include/rgx.h.
+#include "rgx_internal.cuh"
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <unordered_map>
+
+using namespace rgx;
+
+struct rgx_ctx {
+    int device = 0;
+    std::string error;
+    // workspace (device), grown on demand
+    int cap_n_pad = 0;          // capacity in sorted slots
+    int cap_boxes = 0;
+    size_t cap_cub = 0;
+    size_t bytes = 0;
+    uint64_t *keys_in = nullptr, *keys_out = nullptr;
+    uint32_t *vals_in = nullptr, *vals_out = nullptr;
+    float2 *bx = nullptr, *by = nullptr, *bz = nullptr;
+    float4 *g0 = nullptr, *g1 = nullptr, *g2 = nullptr, *quat = nullptr, *sdens = nullptr, *rgba = nullptr;
+    float4* grad_rows = nullptr;
+    float* hk = nullptr;
+    unsigned int* refit_counters = nullptr;
+    unsigned char* cub_temp = nullptr;
+    std::unordered_map<void*, size_t> alloc_bytes;
+    int* bounds = nullptr;
+    SceneBox* box = nullptr;
+    DeviceCounters* counters = nullptr;
+    // state of the last build
+    bool built = false;
+    int n = 0, n_pad = 0;
+    float sigma_threshold = 0.1f;
+    Hierarchy hier{};
+};
+
+namespace {
+
+int fail(rgx_ctx* ctx, int code, const std::string& msg) {
+    if (ctx) ctx->error = msg;
+    return code;
+}
+
+int cuda_fail(rgx_ctx* ctx, cudaError_t e, const char* where) {
+    return fail(ctx, RGX_E_CUDA, std::string(where) + ": " + cudaGetErrorString(e));
+}
+
+template <class T>
+cudaError_t regrow(rgx_ctx* ctx, T*& p, size_t count) {
+    if (p) {
+        cudaFree(p);
+        ctx->bytes -= ctx->alloc_bytes[(void*)p];
+        ctx->alloc_bytes.erase((void*)p);
+    }
+    p = nullptr;
+    cudaError_t e = cudaMalloc((void**)&p, count * sizeof(T));
+    if (e == cudaSuccess) {
+        ctx->bytes += count * sizeof(T);
+        ctx->alloc_bytes[(void*)p] = count * sizeof(T);
+    }
+    return e;
+}
+
+struct Levels {
+    int num_levels;
+    int offset[kMaxLevels];
+    int count[kMaxLevels];
+    int total;   // padded boxes over all levels
+};
+
+Levels plan_levels(int n) {
+    Levels lv{};
+    int cnt = n, off = 0, l = 0;
+    while (true) {
+        lv.offset[l] = off;
+        lv.count[l] = cnt;
+        off += ((cnt + kFan - 1) / kFan) * kFan;
+        ++l;
+        if (l >= 2 && cnt <= kFan) break;
+        cnt = (cnt + kFan - 1) / kFan;
+        if (l == kMaxLevels) break;
+    }
+    lv.num_levels = l;
+    lv.total = off;
+    return lv;
+}
+
+int ensure_workspace(rgx_ctx* ctx, int n_pad, int boxes) {
+    cudaError_t e = cudaSuccess;
+    if (!ctx->bounds) {
+        if ((e = regrow(ctx, ctx->bounds, 12)) != cudaSuccess) return cuda_fail(ctx, e, "workspace");
+        if ((e = regrow(ctx, ctx->box, 1)) != cudaSuccess) return cuda_fail(ctx, e, "workspace");
+        if ((e = regrow(ctx, ctx->counters, 1)) != cudaSuccess) return cuda_fail(ctx, e, "workspace");
+        cudaMemset(ctx->counters, 0, sizeof(DeviceCounters));
+        cudaMemset(ctx->box, 0, sizeof(SceneBox));
+    }
+    if (n_pad > ctx->cap_n_pad) {
+        size_t c = (size_t)n_pad + (size_t)n_pad / 8;   // head-room for densification
+        c = ((c + 31) / 32) * 32;
+#define RG(p) if ((e = regrow(ctx, ctx->p, c)) != cudaSuccess) return cuda_fail(ctx, e, "workspace " #p)
+        RG(keys_in); RG(keys_out); RG(vals_in); RG(vals_out);
+        RG(g0); RG(g1); RG(g2); RG(quat); RG(sdens); RG(rgba); RG(hk);
+#undef RG
+        if ((e = regrow(ctx, ctx->grad_rows, 4 * c)) != cudaSuccess) return cuda_fail(ctx, e, "workspace grad_rows");
+        ctx->cap_n_pad = (int)c;
+        size_t cub = build_cub_temp_bytes((int)c);
+        if ((e = regrow(ctx, ctx->cub_temp, cub)) != cudaSuccess)
+            return cuda_fail(ctx, e, "workspace cub");
+        ctx->cap_cub = cub;
+        ctx->cap_boxes = 0;
+    }
+    if (boxes > ctx->cap_boxes) {
+        size_t c = (size_t)plan_levels(ctx->cap_n_pad).total;
+        if ((size_t)boxes > c) c = boxes;
+        if ((e = regrow(ctx, ctx->bx, c)) != cudaSuccess) return cuda_fail(ctx, e, "workspace boxes");
+        if ((e = regrow(ctx, ctx->by, c)) != cudaSuccess) return cuda_fail(ctx, e, "workspace boxes");
+        if ((e = regrow(ctx, ctx->bz, c)) != cudaSuccess) return cuda_fail(ctx, e, "workspace boxes");
+        if ((e = regrow(ctx, ctx->refit_counters, c)) != cudaSuccess) return cuda_fail(ctx, e, "workspace boxes");
+        ctx->cap_boxes = (int)c;
+    }
+    return RGX_OK;
+}
+
+int check_scene(rgx_ctx* ctx, const rgx_scene* sc, bool need_color) {
+    if (!ctx) return RGX_E_INVALID;
+    if (!sc) return fail(ctx, RGX_E_INVALID, "scene is null");
+    if (sc->n < 0) return fail(ctx, RGX_E_INVALID, "negative Gaussian count");
+    if (sc->n > (1 << 30)) return fail(ctx, RGX_E_TOO_LARGE, "more than 2^30 Gaussians");
+    if (sc->n > 0 && (!sc->positions || !sc->scales || !sc->quaternions || !sc->densities))
+        return fail(ctx, RGX_E_INVALID, "null geometry tensor");
+    if (need_color) {
+        int k = sc->sh_coeffs;
+        if (k != 1 && k != 4 && k != 9 && k != 16) return fail(ctx, RGX_E_INVALID, "sh_coeffs must be 1, 4, 9 or 16");
+        if (sc->num_lobes < 0 || sc->num_lobes > kMaxLobes) return fail(ctx, RGX_E_INVALID, "num_lobes out of range");
+        if (sc->n > 0 && !sc->color_features) return fail(ctx, RGX_E_INVALID, "null color_features");
+        if (sc->n > 0 && sc->num_lobes > 0 && (!sc->sg_features || !sc->sharpness || !sc->lobe_axis))
+            return fail(ctx, RGX_E_INVALID, "null spherical-Gaussian tensor");
+    }
+    return RGX_OK;
+}
+
+int check_march(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m) {
+    if (!cam || !m) return fail(ctx, RGX_E_INVALID, "camera or march parameters null");
+    if (cam->width <= 0 || cam->height <= 0) return fail(ctx, RGX_E_INVALID, "empty image");
+    if ((long long)cam->width * cam->height > (1ll << 30)) return fail(ctx, RGX_E_TOO_LARGE, "more than 2^30 rays");
+    if (!(m->dt_step > 0.f)) return fail(ctx, RGX_E_INVALID, "dt_step must be positive");
+    if (m->max_prim_slice <= 0) return fail(ctx, RGX_E_INVALID, "max_prim_slice must be positive");
+    if (m->row_begin < 0 || m->row_end > cam->height || m->row_begin > m->row_end)
+        return fail(ctx, RGX_E_INVALID, "row range outside the image");
+    if (!(m->transmittance_eps >= 0.f)) return fail(ctx, RGX_E_INVALID, "transmittance_eps must be >= 0");
+    return RGX_OK;
+}
+
+void fill_sorted(const rgx_ctx* ctx, SortedGaussians& g) {
+    g.g0 = ctx->g0; g.g1 = ctx->g1; g.g2 = ctx->g2; g.hk = ctx->hk; g.rgba = ctx->rgba;
+    g.quat = ctx->quat; g.sdens = ctx->sdens; g.perm = ctx->vals_out;
+    g.n = ctx->n; g.n_pad = ctx->n_pad;
+}
+
+int run_colors(rgx_ctx* ctx, const rgx_scene* sc, const float eye[3], cudaStream_t s) {
+    ColorLaunch c{};
+    c.sc = *sc;
+    std::memcpy(c.eye, eye, sizeof(c.eye));
+    c.perm = ctx->vals_out;
+    c.rgba = ctx->rgba;
+    c.sigma_threshold = ctx->sigma_threshold;
+    cudaError_t e = launch_colors(c, s);
+    return e == cudaSuccess ? RGX_OK : cuda_fail(ctx, e, "colour kernel");
+}
+
+}  // namespace
+
+extern "C" {
+
+int rgx_create(int device, rgx_ctx** out) {
+    if (!out) return RGX_E_INVALID;
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || device < 0 || device >= count) return RGX_E_CUDA;
+    rgx_ctx* ctx = new (std::nothrow) rgx_ctx();
+    if (!ctx) return RGX_E_INVALID;
+    ctx->device = device;
+    *out = ctx;
+    return RGX_OK;
+}
+
+void rgx_destroy(rgx_ctx* ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    void* ptrs[] = {ctx->keys_in, ctx->keys_out, ctx->vals_in, ctx->vals_out, ctx->bx, ctx->by, ctx->bz, ctx->g0, ctx->g1,
+                    ctx->g2, ctx->quat, ctx->sdens, ctx->rgba, ctx->grad_rows, ctx->hk, ctx->refit_counters,
+                    ctx->cub_temp, ctx->bounds, ctx->box, ctx->counters};
+    for (void* p : ptrs)
+        if (p) cudaFree(p);
+    delete ctx;
+}
+
+const char* rgx_last_error(const rgx_ctx* ctx) { return ctx ? ctx->error.c_str() : "null context"; }
+
+size_t rgx_workspace_bytes(const rgx_ctx* ctx) { return ctx ? ctx->bytes : 0; }
+
+int rgx_build(rgx_ctx* ctx, const rgx_scene* scene, float sigma_threshold, int morton_bits, rgx_stream stream) {
+    int rc = check_scene(ctx, scene, false);
+    if (rc) return rc;
+    if (morton_bits != 10 && morton_bits != 20) return fail(ctx, RGX_E_INVALID, "morton_bits must be 10 or 20");
+    if (!(sigma_threshold > 0.f)) return fail(ctx, RGX_E_INVALID, "sigma_threshold must be positive");
+    cudaSetDevice(ctx->device);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int n = scene->n;
+    const int n_pad = ((n + kFan - 1) / kFan) * kFan;
+    Levels lv = plan_levels(n > 0 ? n : 1);
+    if ((rc = ensure_workspace(ctx, n_pad > 0 ? n_pad : kFan, lv.total))) return rc;
+    ctx->built = false;
+    ctx->n = n;
+    ctx->n_pad = n_pad;
+    ctx->sigma_threshold = sigma_threshold;
+    ctx->hier.bx = ctx->bx; ctx->hier.by = ctx->by; ctx->hier.bz = ctx->bz;
+    ctx->hier.num_levels = lv.num_levels;
+    for (int l = 0; l < kMaxLevels; ++l) { ctx->hier.offset[l] = lv.offset[l]; ctx->hier.count[l] = lv.count[l]; }
+    if (n == 0) {
+        ctx->hier.count[0] = 0;
+        ctx->hier.count[1] = 0;
+        cudaError_t e = cudaMemsetAsync(ctx->box, 0, sizeof(SceneBox), s);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "build");
+        ctx->built = true;
+        return RGX_OK;
+    }
+    BuildLaunch b{};
+    b.sc = *scene;
+    b.sigma_threshold = sigma_threshold;
+    b.morton_bits = morton_bits;
+    b.n_pad = n_pad;
+    b.keys_in = ctx->keys_in; b.keys_out = ctx->keys_out; b.vals_in = ctx->vals_in; b.vals_out = ctx->vals_out;
+    b.bx = ctx->bx; b.by = ctx->by; b.bz = ctx->bz;
+    b.g0 = ctx->g0; b.g1 = ctx->g1; b.g2 = ctx->g2; b.quat = ctx->quat; b.sdens = ctx->sdens; b.hk = ctx->hk;
+    b.bounds = ctx->bounds; b.box = ctx->box; b.refit_counters = ctx->refit_counters;
+    b.num_levels = lv.num_levels;
+    for (int l = 0; l < kMaxLevels; ++l) { b.offset[l] = lv.offset[l]; b.count[l] = lv.count[l]; }
+    b.cub_temp = ctx->cub_temp; b.cub_temp_bytes = ctx->cap_cub;
+    cudaError_t e = launch_build(b, s);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "build");
+    ctx->built = true;
+    return RGX_OK;
+}
+
+static int prepare_march(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, const rgx_march* march,
+                         MarchLaunch& L) {
+    int rc = check_scene(ctx, scene, true);
+    if (rc) return rc;
+    if ((rc = check_march(ctx, cam, march))) return rc;
+    if (!ctx->built || ctx->n != scene->n)
+        return fail(ctx, RGX_E_NOT_BUILT, "rgx_build has not been called for this Gaussian set");
+    L.h = ctx->hier;
+    fill_sorted(ctx, L.g);
+    L.cam = *cam;
+    L.m = *march;
+    L.box = ctx->box;
+    L.counters = (march->flags & RGX_FLAG_COUNT_WORK) ? ctx->counters : nullptr;
+    return RGX_OK;
+}
+
+int rgx_forward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, const rgx_march* march, float* rgb,
+                float* alpha, float* depth, rgx_stream stream) {
+    MarchLaunch L{};
+    int rc = prepare_march(ctx, scene, cam, march, L);
+    if (rc) return rc;
+    if (!rgb) return fail(ctx, RGX_E_INVALID, "rgb output is null");
+    cudaSetDevice(ctx->device);
+    cudaStream_t s = (cudaStream_t)stream;
+    if ((rc = run_colors(ctx, scene, cam->eye, s))) return rc;
+    L.rgb = rgb; L.alpha = alpha; L.depth = depth;
+    cudaError_t e = launch_march_forward(L, s);
+    return e == cudaSuccess ? RGX_OK : cuda_fail(ctx, e, "forward march");
+}
+
+int rgx_backward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, const rgx_march* march,
+                 const float* rgb, const float* dL_drgb, const rgx_grads* grads, rgx_stream stream) {
+    MarchLaunch L{};
+    int rc = prepare_march(ctx, scene, cam, march, L);
+    if (rc) return rc;
+    if (!rgb || !dL_drgb || !grads) return fail(ctx, RGX_E_INVALID, "null backward argument");
+    if (scene->n > 0 && (!grads->positions || !grads->scales || !grads->quaternions || !grads->densities ||
+                         !grads->color_features))
+        return fail(ctx, RGX_E_INVALID, "null gradient tensor");
+    if (scene->n > 0 && scene->num_lobes > 0 && (!grads->sg_features || !grads->sharpness || !grads->lobe_axis))
+        return fail(ctx, RGX_E_INVALID, "null spherical-Gaussian gradient tensor");
+    if (scene->n == 0) return RGX_OK;
+    cudaSetDevice(ctx->device);
+    cudaStream_t s = (cudaStream_t)stream;
+    if ((rc = run_colors(ctx, scene, cam->eye, s))) return rc;
+    cudaError_t e = cudaMemsetAsync(ctx->grad_rows, 0, sizeof(float4) * 4 * (size_t)ctx->n_pad, s);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "backward memset");
+    L.rgb_in = rgb; L.dl_drgb = dL_drgb; L.grad_rows = ctx->grad_rows;
+    if ((e = launch_march_backward(L, s)) != cudaSuccess) return cuda_fail(ctx, e, "backward march");
+    FinalizeLaunch f{};
+    f.sc = *scene;
+    f.gr = *grads;
+    std::memcpy(f.eye, cam->eye, sizeof(f.eye));
+    f.perm = ctx->vals_out;
+    f.grad_rows = ctx->grad_rows;
+    f.flags = march->flags;
+    e = launch_finalize(f, s);
+    return e == cudaSuccess ? RGX_OK : cuda_fail(ctx, e, "gradient finalise");
+}
+
+int rgx_gaussian_colors(rgx_ctx* ctx, const rgx_scene* scene, const float eye[3], float* rgb_out, rgx_stream stream) {
+    int rc = check_scene(ctx, scene, true);
+    if (rc) return rc;
+    if (!eye || (!rgb_out && scene->n > 0)) return fail(ctx, RGX_E_INVALID, "null argument");
+    cudaSetDevice(ctx->device);
+    ColorLaunch c{};
+    c.sc = *scene;
+    std::memcpy(c.eye, eye, sizeof(c.eye));
+    c.perm = nullptr;
+    c.rgb_out = rgb_out;
+    c.sigma_threshold = ctx->sigma_threshold;
+    cudaError_t e = launch_colors(c, (cudaStream_t)stream);
+    return e == cudaSuccess ? RGX_OK : cuda_fail(ctx, e, "colour kernel");
+}
+
+int rgx_scene_box(rgx_ctx* ctx, float bb_min[3], float bb_max[3], rgx_stream stream) {
+    if (!ctx || !bb_min || !bb_max) return RGX_E_INVALID;
+    if (!ctx->built) return fail(ctx, RGX_E_NOT_BUILT, "rgx_build has not been called");
+    cudaSetDevice(ctx->device);
+    SceneBox h;
+    cudaError_t e = cudaMemcpyAsync(&h, ctx->box, sizeof(h), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "scene box read-back");
+    std::memcpy(bb_min, h.lo, sizeof(h.lo));
+    std::memcpy(bb_max, h.hi, sizeof(h.hi));
+    return RGX_OK;
+}
+
+int rgx_reset_counters(rgx_ctx* ctx, rgx_stream stream) {
+    if (!ctx) return RGX_E_INVALID;
+    cudaSetDevice(ctx->device);
+    int rc = ensure_workspace(ctx, ctx->cap_n_pad, ctx->cap_boxes);
+    if (rc) return rc;
+    cudaError_t e = cudaMemsetAsync(ctx->counters, 0, sizeof(DeviceCounters), (cudaStream_t)stream);
+    return e == cudaSuccess ? RGX_OK : cuda_fail(ctx, e, "counter reset");
+}
+
+int rgx_read_counters(rgx_ctx* ctx, rgx_counters* out, rgx_stream stream) {
+    if (!ctx || !out) return RGX_E_INVALID;
+    cudaSetDevice(ctx->device);
+    int rc = ensure_workspace(ctx, ctx->cap_n_pad, ctx->cap_boxes);
+    if (rc) return rc;
+    static_assert(sizeof(rgx_counters) == sizeof(DeviceCounters), "counter layouts must match");
+    cudaError_t e = cudaMemcpyAsync(out, ctx->counters, sizeof(DeviceCounters), cudaMemcpyDeviceToHost,
+                                    (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+    return e == cudaSuccess ? RGX_OK : cuda_fail(ctx, e, "counter read-back");
+}
+
+}  // extern "C"

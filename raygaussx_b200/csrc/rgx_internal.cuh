@@ -1,0 +1,118 @@
+// Internal declarations shared by the translation units of librgx.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <float.h>
+#include "../../include/rgx.h"
+
+namespace rgx {
+
+constexpr int kFan = 32;          // children per hierarchy node = lanes per warp
+constexpr int kMaxLevels = 8;     // level 0 = Gaussians; 32^7 > 3e10 primitives
+constexpr int kSlab = 32;         // samples per slab  (BUFFER_SIZE, cuda_train/forward/gaussians_aabb.h:2)
+constexpr int kChunk = 16;        // samples per chunk (CHUNK_SIZE, :3)
+constexpr int kMaxLobes = 8;
+
+// Hierarchy over the Morton-sorted Gaussians.  Level 0 holds one box per Gaussian,
+// node j of level l+1 bounds boxes [32j, 32j+32) of level l.  All levels live in
+// one set of arrays; every level is padded to a multiple of 32 entries with
+// inverted (never hit) boxes.
+struct Hierarchy {
+    const float2* bx;  // per box: (min, max) along x
+    const float2* by;
+    const float2* bz;
+    int num_levels;            // including level 0
+    int offset[kMaxLevels];    // first box of each level
+    int count[kMaxLevels];     // valid boxes of each level (unpadded)
+};
+
+// Per-Gaussian data in sorted order (index j), n_pad = roundup(n, 32) entries.
+struct SortedGaussians {
+    // g0 = (p.x, p.y, p.z, m00), g1 = (m01, m02, m10, m11), g2 = (m12, m20, m21, m22)
+    // with M = S^-1 R^T / k, so that the truncation ellipsoid is |M (x - p)|^2 < 1.
+    const float4* g0;
+    const float4* g1;
+    const float4* g2;
+    const float* hk;     // log2(sigma / sigma_threshold): exp(-power/2) = exp2(-hk * |M(x-p)|^2)
+    const float4* rgba;  // per view: (r*sigma, g*sigma, b*sigma, sigma)
+    const float4* quat;  // raw quaternion (backward)
+    const float4* sdens; // (s.x, s.y, s.z, sigma) raw (backward)
+    const uint32_t* perm;// sorted index -> caller's index
+    int n;
+    int n_pad;
+};
+
+struct DeviceCounters {   // mirrors rgx_counters
+    unsigned long long v[12];
+};
+enum { C_RAYS, C_SLABS, C_SLABS_HIT, C_CLOSEST, C_HITS, C_PAIRS, C_OVF, C_NODE_TESTS, C_PRIM_TESTS, C_ELL_TESTS,
+       C_STACK_OVF, C_HASH };
+
+struct SceneBox {         // written by the build, read by the march kernels
+    float lo[3];
+    float hi[3];
+};
+
+struct MarchLaunch {
+    Hierarchy h;
+    SortedGaussians g;
+    rgx_camera cam;
+    rgx_march m;
+    const SceneBox* box;
+    DeviceCounters* counters;
+    // forward outputs / backward inputs
+    float* rgb;
+    float* alpha;
+    float* depth;
+    const float* rgb_in;
+    const float* dl_drgb;
+    float4* grad_rows;    // [n_pad,4] float4: (dpos.xyz, dscale.x) (dscale.yz, dquat.xy) (dquat.zw, dsigma, drgb.x) (drgb.yz, 0, 0)
+};
+
+struct ColorLaunch {
+    rgx_scene sc;
+    float eye[3];
+    const uint32_t* perm;  // null: identity order, write rgb_out [n,3]
+    float4* rgba;          // sorted order output (when perm != null)
+    float* rgb_out;
+    float sigma_threshold;
+};
+
+struct FinalizeLaunch {
+    rgx_scene sc;
+    rgx_grads gr;
+    float eye[3];
+    const uint32_t* perm;
+    const float4* grad_rows;
+    int flags;
+};
+
+struct BuildLaunch {
+    rgx_scene sc;
+    float sigma_threshold;
+    int morton_bits;
+    int n_pad;
+    // outputs
+    uint64_t* keys_in; uint64_t* keys_out;
+    uint32_t* vals_in; uint32_t* vals_out;
+    float2 *bx, *by, *bz;
+    float4 *g0, *g1, *g2, *quat, *sdens;
+    float* hk;
+    int* bounds;           // 12 ints: ordered-int encodings of scene box lo[3],hi[3], centre lo[3],hi[3]
+    SceneBox* box;
+    unsigned int* refit_counters;
+    int num_levels;
+    int offset[kMaxLevels];
+    int count[kMaxLevels];
+    void* cub_temp; size_t cub_temp_bytes;
+};
+
+// host launchers (each returns the cudaError_t of its last launch)
+cudaError_t launch_build(const BuildLaunch& b, cudaStream_t s);
+size_t build_cub_temp_bytes(int n_pad);
+cudaError_t launch_colors(const ColorLaunch& c, cudaStream_t s);
+cudaError_t launch_finalize(const FinalizeLaunch& f, cudaStream_t s);
+cudaError_t launch_march_forward(const MarchLaunch& m, cudaStream_t s);
+cudaError_t launch_march_backward(const MarchLaunch& m, cudaStream_t s);
+
+}  // namespace rgx

@@ -182,9 +182,10 @@ def unbounded_scene(seed=2, n=3_000_000, n_cameras=200, width=1256, height=828) 
     dirs = dirs / dirs.norm(dim=1, keepdim=True)
     rad = torch.rand(n_shell, 1, generator=g) * 45.0 + 5.0
     pos_shell = dirs * rad
+    # the drawn log-scale is the longest axis; the other two are shorter by a log-uniform factor of up to 10
     base = torch.exp(torch.randn(n_shell, 1, generator=g) * 0.5 - 1.0)
-    ratio = torch.exp(torch.rand(n_shell, 3, generator=g) * math.log(10.0))  # per-axis, so at most 10:1
-    sc_shell = base * ratio / ratio.min(dim=1, keepdim=True).values
+    ratio = torch.exp(torch.rand(n_shell, 3, generator=g) * math.log(10.0))
+    sc_shell = base * ratio.min(dim=1, keepdim=True).values / ratio
     pos = torch.cat([pos_core, pos_shell])
     scales = torch.cat([sc_core, sc_shell])
     perm = torch.randperm(n, generator=g)  # no spatial order in the input
