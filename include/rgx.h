@@ -85,7 +85,9 @@ enum {
     RGX_FLAG_COUNT_WORK = 1,     /* also accumulate the work counters read by rgx_read_counters */
     RGX_FLAG_BRUTE_FORCE = 2,    /* skip the hierarchy: test every Gaussian in every query (validation only) */
     RGX_FLAG_EXACT_SH_GRAD = 4,  /* backward: exact d(basis 9)/dy instead of the reference's term (utils/sh_utils.cu:367) */
-    RGX_FLAG_ACCUMULATE = 8      /* backward: add into the gradient tensors instead of overwriting them */
+    RGX_FLAG_ACCUMULATE = 8,     /* backward: add into the gradient tensors instead of overwriting them */
+    RGX_FLAG_PER_RAY_SEARCH = 16 /* search the hierarchy once per ray and slab instead of once per 8x8 tile and depth
+                                    window (same results; the general path, kept for validation) */
 };
 
 /* Gradient tensors, shaped like the inputs (what RenderOptixFunction.backward
@@ -115,6 +117,10 @@ typedef struct rgx_counters {
     uint64_t ellipsoid_tests;/* exact ray/ellipsoid tests */
     uint64_t stack_overflows;/* traversal-stack overflows (results invalid if non-zero) */
     uint64_t hits_hash;     /* order-independent hash of every (ray, slab, Gaussian) hit triple */
+    uint64_t windows;       /* tiled march: depth windows processed (summed over tiles) */
+    uint64_t window_retries;/* tiled march: candidate searches repeated with a shallower window */
+    uint64_t fallback_windows;/* tiled march: windows advanced by per-ray searches because the candidates did not fit */
+    uint64_t candidates;    /* tiled march: candidate-list entries summed over windows */
 } rgx_counters;
 
 /* Replaces: ox.DeviceContext / module / pipeline creation (optix_utils.py:154-210). */
@@ -123,14 +129,21 @@ RGX_API void rgx_destroy(rgx_ctx* ctx);
 /* Host string describing the last failure on this context (never NULL). */
 RGX_API const char* rgx_last_error(const rgx_ctx* ctx);
 
+enum {
+    RGX_CURVE_MORTON = 0, /* Z-order keys */
+    RGX_CURVE_HILBERT = 1 /* Hilbert-curve keys: same cost to sort, tighter groups */
+};
+
 /* Replaces: ellipsoids_bbox_from_quat + create_acceleration_structure
  * (optix_utils.py:82-109,139-142; called from render_optix.py:109-117).
  * Computes per-Gaussian boxes of the sigma_threshold iso-ellipsoid, the scene box,
- * 3*morton_bits-bit Morton keys of the centres (morton_bits 10 or 20), sorts them
- * (CUB radix sort) and refits a 32-ary hierarchy bottom-up.  Only positions,
+ * 3*key_bits-bit space-filling-curve keys of the centres (key_bits per axis: 10
+ * or 20; curve: RGX_CURVE_*), sorts them (CUB radix sort) and refits a 32-ary
+ * hierarchy bottom-up.  Only positions,
  * scales, quaternions and densities of `scene` are read.  Must be called again
  * whenever one of those four tensors changes. */
-RGX_API int rgx_build(rgx_ctx* ctx, const rgx_scene* scene, float sigma_threshold, int morton_bits, rgx_stream stream);
+RGX_API int rgx_build(rgx_ctx* ctx, const rgx_scene* scene, float sigma_threshold, int key_bits, int curve,
+                      rgx_stream stream);
 
 /* Replaces: compute_cupy_rgb + launch_pipeline_forward (render_optix.py:121-131;
  * device code cuda_train/forward/gaussians_aabb.cu, utils/sh_utils.cu:122-216).

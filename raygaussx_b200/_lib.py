@@ -12,7 +12,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "librgx.so")
 
 RGX_OK, RGX_E_INVALID, RGX_E_CUDA, RGX_E_NOT_BUILT, RGX_E_TOO_LARGE = 0, -1, -2, -3, -4
-FLAG_COUNT_WORK, FLAG_BRUTE_FORCE, FLAG_EXACT_SH_GRAD, FLAG_ACCUMULATE = 1, 2, 4, 8
+CURVE_MORTON, CURVE_HILBERT = 0, 1
+FLAG_COUNT_WORK, FLAG_BRUTE_FORCE, FLAG_EXACT_SH_GRAD, FLAG_ACCUMULATE, FLAG_PER_RAY_SEARCH = 1, 2, 4, 8, 16
 
 _fp = C.c_void_p  # device pointers travel as integers
 
@@ -42,7 +43,8 @@ class Grads(C.Structure):
 class Counters(C.Structure):
     _fields_ = [(k, C.c_uint64) for k in ("rays", "slabs", "slabs_hit", "closest_queries", "hits", "pairs_inside",
                                           "overflow_slabs", "node_tests", "prim_tests", "ellipsoid_tests",
-                                          "stack_overflows", "hits_hash")]
+                                          "stack_overflows", "hits_hash", "windows", "window_retries",
+                                          "fallback_windows", "candidates")]
 
     def as_dict(self):
         return {k: int(getattr(self, k)) for k, _ in self._fields_}
@@ -53,7 +55,7 @@ SYMBOLS = {
     "rgx_create": (C.c_int, [C.c_int, C.POINTER(C.c_void_p)]),
     "rgx_destroy": (None, [C.c_void_p]),
     "rgx_last_error": (C.c_char_p, [C.c_void_p]),
-    "rgx_build": (C.c_int, [C.c_void_p, C.POINTER(Scene), C.c_float, C.c_int, C.c_void_p]),
+    "rgx_build": (C.c_int, [C.c_void_p, C.POINTER(Scene), C.c_float, C.c_int, C.c_int, C.c_void_p]),
     "rgx_forward": (C.c_int, [C.c_void_p, C.POINTER(Scene), C.POINTER(Camera), C.POINTER(March), _fp, _fp, _fp,
                               C.c_void_p]),
     "rgx_backward": (C.c_int, [C.c_void_p, C.POINTER(Scene), C.POINTER(Camera), C.POINTER(March), _fp, _fp,

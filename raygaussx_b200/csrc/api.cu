@@ -201,10 +201,12 @@ const char* rgx_last_error(const rgx_ctx* ctx) { return ctx ? ctx->error.c_str()
 
 size_t rgx_workspace_bytes(const rgx_ctx* ctx) { return ctx ? ctx->bytes : 0; }
 
-int rgx_build(rgx_ctx* ctx, const rgx_scene* scene, float sigma_threshold, int morton_bits, rgx_stream stream) {
+int rgx_build(rgx_ctx* ctx, const rgx_scene* scene, float sigma_threshold, int morton_bits, int curve,
+              rgx_stream stream) {
     int rc = check_scene(ctx, scene, false);
     if (rc) return rc;
-    if (morton_bits != 10 && morton_bits != 20) return fail(ctx, RGX_E_INVALID, "morton_bits must be 10 or 20");
+    if (morton_bits != 10 && morton_bits != 20) return fail(ctx, RGX_E_INVALID, "key_bits must be 10 or 20");
+    if (curve != RGX_CURVE_MORTON && curve != RGX_CURVE_HILBERT) return fail(ctx, RGX_E_INVALID, "unknown curve");
     if (!(sigma_threshold > 0.f)) return fail(ctx, RGX_E_INVALID, "sigma_threshold must be positive");
     cudaSetDevice(ctx->device);
     cudaStream_t s = (cudaStream_t)stream;
@@ -231,6 +233,7 @@ int rgx_build(rgx_ctx* ctx, const rgx_scene* scene, float sigma_threshold, int m
     b.sc = *scene;
     b.sigma_threshold = sigma_threshold;
     b.morton_bits = morton_bits;
+    b.curve = curve;
     b.n_pad = n_pad;
     b.keys_in = ctx->keys_in; b.keys_out = ctx->keys_out; b.vals_in = ctx->vals_in; b.vals_out = ctx->vals_out;
     b.bx = ctx->bx; b.by = ctx->by; b.bz = ctx->bz;

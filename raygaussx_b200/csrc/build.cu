@@ -86,6 +86,29 @@ __device__ __forceinline__ uint64_t spread3(uint64_t x) {
     return x;
 }
 
+// Cell coordinates -> "transposed" Hilbert index (J. Skilling, "Programming the
+// Hilbert curve", AIP Conf. Proc. 707, 2004): after the call, interleaving the bits
+// of q[0], q[1], q[2] (q[0] most significant) gives the position along the curve.
+// Unlike a Morton curve, a run of consecutive Hilbert indices is always a connected
+// set of cells, so fixed-size groups of sorted Gaussians get tighter boxes.
+__device__ __forceinline__ void hilbert_transpose(uint32_t* q, int bits) {
+    const uint32_t top = 1u << (bits - 1);
+    for (uint32_t Q = top; Q > 1; Q >>= 1) {
+        const uint32_t P = Q - 1;
+#pragma unroll
+        for (int i = 0; i < 3; ++i) {
+            if (q[i] & Q) q[0] ^= P;
+            else { uint32_t t = (q[0] ^ q[i]) & P; q[0] ^= t; q[i] ^= t; }
+        }
+    }
+    q[1] ^= q[0];
+    q[2] ^= q[1];
+    uint32_t t = 0;
+    for (uint32_t Q = top; Q > 1; Q >>= 1)
+        if (q[2] & Q) t ^= Q - 1;
+    q[0] ^= t; q[1] ^= t; q[2] ^= t;
+}
+
 __global__ void __launch_bounds__(256) morton_kernel(BuildLaunch b) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i == 0) {
@@ -96,7 +119,7 @@ __global__ void __launch_bounds__(256) morton_kernel(BuildLaunch b) {
     }
     if (i >= b.sc.n) return;
     const float cells = (float)(1u << b.morton_bits);
-    uint64_t key = 0;
+    uint32_t q[3];
 #pragma unroll
     for (int a = 0; a < 3; ++a) {
         float lo = ordered_to_float(b.bounds[6 + a]), hi = ordered_to_float(b.bounds[9 + a]);
@@ -104,7 +127,14 @@ __global__ void __launch_bounds__(256) morton_kernel(BuildLaunch b) {
         float u = ext > 0.f ? (b.sc.positions[3 * i + a] - lo) / ext : 0.f;
         u = fminf(fmaxf(u * cells, 0.f), cells - 1.f);
         if (!(u == u)) u = 0.f;
-        key |= spread3((uint64_t)(unsigned int)u) << a;
+        q[a] = (uint32_t)u;
+    }
+    uint64_t key;
+    if (b.curve == RGX_CURVE_HILBERT) {
+        hilbert_transpose(q, b.morton_bits);
+        key = (spread3(q[0]) << 2) | (spread3(q[1]) << 1) | spread3(q[2]);
+    } else {
+        key = spread3(q[0]) | (spread3(q[1]) << 1) | (spread3(q[2]) << 2);
     }
     b.keys_in[i] = key;
     b.vals_in[i] = (uint32_t)i;

@@ -1,0 +1,665 @@
+// Device helpers shared by the march kernels: ray set-up, ray/box and
+// ray/ellipsoid tests, the three ways of enumerating the Gaussians of a query
+// (exhaustive, per-ray hierarchy search, shared candidate list), the slab
+// schedule and the per-sample evaluation.
+#pragma once
+#include "rgx_internal.cuh"
+#include "device_math.cuh"
+
+namespace rgx {
+
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kStack = 192;
+constexpr int kStage = 64;
+constexpr unsigned kFull = 0xffffffffu;
+constexpr int kTile = 8;   // CTA = 8x8 pixels; warp w marches column w of the tile
+constexpr int kMaxSlabs = 1 << 22;   // hard bound on slab iterations per ray
+
+struct WarpShared {
+    float4 recA[kStage];
+    float4 recB[kStage];
+    float4 recC[kStage];
+    uint32_t stack[kStack];
+    float stack_t[kStack];
+};
+
+struct Ray {
+    float3 o, d, inv;
+};
+
+struct Tally {   // per-warp work counters (uniform across lanes)
+    unsigned long long v[C_NUM];
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(kFull, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_min_f(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(kFull, v, o));
+    return v;
+}
+// inclusive prefix sum over lanes
+__device__ __forceinline__ float warp_scan(float v, int lane) {
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        float t = __shfl_up_sync(kFull, v, o);
+        if (lane >= o) v = __fadd_rn(v, t);
+    }
+    return v;
+}
+__device__ __forceinline__ float exp_neg(float x) {   // exp(-x), x >= 0
+    return ex2_approx(__fmul_rn(x, -1.4426950408889634f));
+}
+
+// cuda_train/forward/gaussians_aabb.cu:95-110
+__device__ __forceinline__ void make_ray(const rgx_camera& c, int px, int py, Ray& r) {
+    float ix = __fdiv_rn((float)px + 0.5f, (float)c.width);
+    float iy = __fdiv_rn((float)py + 0.5f, (float)c.height);
+    float a = __fmul_rn(__fmul_rn(2.0f, ix - c.pp[0]), c.tan_half_fov[0]);
+    float b = __fmul_rn(__fmul_rn(2.0f, iy - c.pp[1]), c.tan_half_fov[1]);
+    float3 d = make_float3(__fadd_rn(__fadd_rn(__fmul_rn(a, c.u[0]), __fmul_rn(b, c.v[0])), c.w[0]),
+                           __fadd_rn(__fadd_rn(__fmul_rn(a, c.u[1]), __fmul_rn(b, c.v[1])), c.w[1]),
+                           __fadd_rn(__fadd_rn(__fmul_rn(a, c.u[2]), __fmul_rn(b, c.v[2])), c.w[2]));
+    float inv_len = __fdiv_rn(1.0f, __fsqrt_rn(dot3(d, d)));
+    r.d = make_float3(__fmul_rn(d.x, inv_len), __fmul_rn(d.y, inv_len), __fmul_rn(d.z, inv_len));
+    r.o = make_float3(c.eye[0], c.eye[1], c.eye[2]);
+    r.inv = make_float3(__frcp_rn(r.d.x), __frcp_rn(r.d.y), __frcp_rn(r.d.z));
+}
+
+// Ray/box overlap restricted to [tmin,tmax].  The near/far planes are chosen by the
+// sign of the direction (no min/max swap), so an inverted box is never hit, and
+// the result is monotone in the box: a box containing a hit box is hit.
+__device__ __forceinline__ bool box_hit(const Ray& r, float2 bx, float2 by, float2 bz, float tmin, float tmax,
+                                        float& tnear) {
+    float x0 = __fmul_rn(bx.x - r.o.x, r.inv.x), x1 = __fmul_rn(bx.y - r.o.x, r.inv.x);
+    float y0 = __fmul_rn(by.x - r.o.y, r.inv.y), y1 = __fmul_rn(by.y - r.o.y, r.inv.y);
+    float z0 = __fmul_rn(bz.x - r.o.z, r.inv.z), z1 = __fmul_rn(bz.y - r.o.z, r.inv.z);
+    bool px = r.inv.x >= 0.f, py = r.inv.y >= 0.f, pz = r.inv.z >= 0.f;
+    float nx = px ? x0 : x1, fx = px ? x1 : x0;
+    float ny = py ? y0 : y1, fy = py ? y1 : y0;
+    float nz = pz ? z0 : z1, fz = pz ? z1 : z0;
+    tnear = fmaxf(fmaxf(nx, ny), fmaxf(nz, tmin));
+    float tfar = fminf(fminf(fx, fy), fminf(fz, tmax));
+    return tnear <= tfar;
+}
+
+// Interval of the ray inside the truncation ellipsoid
+// (cuda_train/forward/gaussians_aabb.cu:43-91 with M = S^-1 R^T / k folded into g0..g2).
+__device__ __forceinline__ bool ellipsoid_interval(const Ray& r, float4 g0, float4 g1, float4 g2, float3& Oe,
+                                                   float3& de, float& r1, float& r2) {
+    float3 O = make_float3(r.o.x - g0.x, r.o.y - g0.y, r.o.z - g0.z);
+    Oe.x = fmaf(g0.w, O.x, fmaf(g1.x, O.y, __fmul_rn(g1.y, O.z)));
+    Oe.y = fmaf(g1.z, O.x, fmaf(g1.w, O.y, __fmul_rn(g2.x, O.z)));
+    Oe.z = fmaf(g2.y, O.x, fmaf(g2.z, O.y, __fmul_rn(g2.w, O.z)));
+    de.x = fmaf(g0.w, r.d.x, fmaf(g1.x, r.d.y, __fmul_rn(g1.y, r.d.z)));
+    de.y = fmaf(g1.z, r.d.x, fmaf(g1.w, r.d.y, __fmul_rn(g2.x, r.d.z)));
+    de.z = fmaf(g2.y, r.d.x, fmaf(g2.z, r.d.y, __fmul_rn(g2.w, r.d.z)));
+    float a = dot3(de, de);
+    float b = -dot3(Oe, de);
+    float c = fmaf(Oe.x, Oe.x, fmaf(Oe.y, Oe.y, fmaf(Oe.z, Oe.z, -1.0f)));
+    float inv_a = __fdividef(1.0f, a);
+    float bia = __fmul_rn(b, inv_a);
+    float3 P = make_float3(fmaf(bia, de.x, Oe.x), fmaf(bia, de.y, Oe.y), fmaf(bia, de.z, Oe.z));
+    float disc = 1.0f - dot3(P, P);
+    if (!(disc > 1e-7f)) return false;
+    float sd = __fsqrt_rn(__fmul_rn(disc, a));
+    float q = b + copysignf(sd, b);
+    r1 = __fdiv_rn(c, q);
+    r2 = __fmul_rn(q, inv_a);
+    return true;
+}
+
+struct LeafTest {
+    bool hit;
+    float t_hit;     // max(tmin, root1, box entry) when hit
+    float3 Oe, de;
+};
+
+__device__ __forceinline__ LeafTest test_gaussian(const MarchLaunch& L, const Ray& r, int j, bool valid, float tmin,
+                                                  float tmax, Tally& tl, bool count) {
+    LeafTest out;
+    out.hit = false;
+    out.t_hit = INFINITY;
+    bool bh = false;
+    float tnear = 0.f;
+    if (valid) {
+        float2 bx = __ldg(&L.h.bx[j]), by = __ldg(&L.h.by[j]), bz = __ldg(&L.h.bz[j]);
+        bh = box_hit(r, bx, by, bz, tmin, tmax, tnear);
+    }
+    if (bh) {
+        float4 g0 = __ldg(&L.g.g0[j]), g1 = __ldg(&L.g.g1[j]), g2 = __ldg(&L.g.g2[j]);
+        float r1, r2;
+        if (ellipsoid_interval(r, g0, g1, g2, out.Oe, out.de, r1, r2)) {
+            float lo = fmaxf(tmin, r1), hi = fminf(tmax, r2);
+            out.hit = lo <= hi;
+            out.t_hit = fmaxf(lo, tnear);
+        }
+    }
+    if (count) {
+        tl.v[C_PRIM_TESTS] += __popc(__ballot_sync(kFull, valid));
+        tl.v[C_ELL_TESTS] += __popc(__ballot_sync(kFull, bh));
+    }
+    return out;
+}
+
+// Any-hit search: calls leaf(LeafTest, j) once per group of 32 Gaussians whose
+// parent box is hit, with all lanes converged; leaf returns false to stop.
+template <bool COUNT, bool BRUTE, class LeafFn>
+__device__ __forceinline__ void search_all(const MarchLaunch& L, const Ray& r, float tmin, float tmax, WarpShared& ws,
+                                           int lane, Tally& tl, LeafFn&& leaf) {
+    if (BRUTE) {
+        for (int base = 0; base < L.g.n_pad; base += kFan) {
+            int j = base + lane;
+            LeafTest t = test_gaussian(L, r, j, j < L.g.n, tmin, tmax, tl, COUNT);
+            if (!leaf(t, j)) return;
+        }
+        return;
+    }
+    const Hierarchy& h = L.h;
+    const int top = h.num_levels - 1;
+    int sp = 0;
+    {
+        bool bh = false;
+        float tn;
+        if (lane < h.count[top]) {
+            int idx = h.offset[top] + lane;
+            bh = box_hit(r, __ldg(&h.bx[idx]), __ldg(&h.by[idx]), __ldg(&h.bz[idx]), tmin, tmax, tn);
+        }
+        unsigned m = __ballot_sync(kFull, bh);
+        sp = __popc(m);
+        // lowest index on top: groups are then visited in ascending (Morton) order, as in the exhaustive scan
+        if (bh) ws.stack[sp - 1 - __popc(m & ((1u << lane) - 1u))] = ((uint32_t)top << 26) | (uint32_t)lane;
+        if (COUNT) tl.v[C_NODE_TESTS] += h.count[top];
+        __syncwarp();
+    }
+    while (sp > 0) {
+        uint32_t e = ws.stack[--sp];
+        int level = (int)(e >> 26) - 1;          // level of the children
+        int c = (int)(e & 0x3ffffffu) * kFan + lane;
+        bool valid = c < h.count[level];
+        if (level == 0) {
+            LeafTest t = test_gaussian(L, r, c, valid, tmin, tmax, tl, COUNT);
+            if (!leaf(t, c)) return;
+        } else {
+            bool bh = false;
+            float tn;
+            if (valid) {
+                int idx = h.offset[level] + c;
+                bh = box_hit(r, __ldg(&h.bx[idx]), __ldg(&h.by[idx]), __ldg(&h.bz[idx]), tmin, tmax, tn);
+            }
+            unsigned m = __ballot_sync(kFull, bh);
+            int rank = __popc(m & ((1u << lane) - 1u));
+            int n = __popc(m);
+            if (sp + n > kStack) {               // never expected; drop the excess and report
+                tl.v[C_STACK_OVF] += 1;
+                n = kStack - sp;
+            }
+            if (bh && rank < n) ws.stack[sp + n - 1 - rank] = ((uint32_t)level << 26) | (uint32_t)c;
+            sp += n;
+            if (COUNT) tl.v[C_NODE_TESTS] += 32;
+            __syncwarp();
+        }
+    }
+}
+
+// Closest-hit search over [tmin,tmax]: smallest t_hit, or +inf on a miss.
+template <bool COUNT, bool BRUTE>
+__device__ __forceinline__ float search_closest(const MarchLaunch& L, const Ray& r, float tmin, float tmax,
+                                                WarpShared& ws, int lane, Tally& tl) {
+    float best = INFINITY;
+    if (COUNT) tl.v[C_CLOSEST] += 1;
+    if (!(tmin <= tmax)) return best;
+    if (BRUTE) {
+        for (int base = 0; base < L.g.n_pad; base += kFan) {
+            int j = base + lane;
+            LeafTest t = test_gaussian(L, r, j, j < L.g.n, tmin, tmax, tl, COUNT);
+            best = fminf(best, warp_min_f(t.hit ? t.t_hit : INFINITY));
+        }
+        return best;
+    }
+    const Hierarchy& h = L.h;
+    const int top = h.num_levels - 1;
+    int sp = 0;
+    // pushes the hit children so that the nearest one is popped first
+    auto push = [&](bool bh, float tn, int level, int c) {
+        unsigned key = bh ? __float_as_uint(tn) : 0xffffffffu;      // tn >= tmin >= 0: order-preserving
+        unsigned mn = __reduce_min_sync(kFull, key);
+        unsigned near_mask = __ballot_sync(kFull, bh && key == mn);
+        int near_lane = __ffs(near_mask) - 1;
+        bool other = bh && lane != near_lane;
+        unsigned m = __ballot_sync(kFull, other);
+        int n = __popc(m), total = n + (near_lane >= 0 ? 1 : 0);
+        if (sp + total > kStack) { tl.v[C_STACK_OVF] += 1; return; }
+        if (other) {
+            int s = sp + __popc(m & ((1u << lane) - 1u));
+            ws.stack[s] = ((uint32_t)level << 26) | (uint32_t)c;
+            ws.stack_t[s] = tn;
+        }
+        if (lane == near_lane) {
+            ws.stack[sp + n] = ((uint32_t)level << 26) | (uint32_t)c;
+            ws.stack_t[sp + n] = tn;
+        }
+        sp += total;
+        __syncwarp();
+    };
+    {
+        bool bh = false;
+        float tn = 0.f;
+        if (lane < h.count[top]) {
+            int idx = h.offset[top] + lane;
+            bh = box_hit(r, __ldg(&h.bx[idx]), __ldg(&h.by[idx]), __ldg(&h.bz[idx]), tmin, tmax, tn);
+        }
+        if (COUNT) tl.v[C_NODE_TESTS] += h.count[top];
+        push(bh, tn, top, lane);
+    }
+    while (sp > 0) {
+        --sp;
+        uint32_t e = ws.stack[sp];
+        float te = ws.stack_t[sp];
+        if (te > best) continue;                 // nothing below this node can start earlier
+        int level = (int)(e >> 26) - 1;
+        int c = (int)(e & 0x3ffffffu) * kFan + lane;
+        bool valid = c < h.count[level];
+        if (level == 0) {
+            LeafTest t = test_gaussian(L, r, c, valid, tmin, fminf(tmax, best), tl, COUNT);
+            best = fminf(best, warp_min_f(t.hit ? t.t_hit : INFINITY));
+            if (best <= tmin) return best;       // cannot improve on the interval start
+        } else {
+            bool bh = false;
+            float tn = 0.f;
+            if (valid) {
+                int idx = h.offset[level] + c;
+                bh = box_hit(r, __ldg(&h.bx[idx]), __ldg(&h.by[idx]), __ldg(&h.bz[idx]), tmin, fminf(tmax, best), tn);
+            }
+            if (COUNT) tl.v[C_NODE_TESTS] += 32;
+            push(bh, tn, level, c);
+        }
+    }
+    return best;
+}
+
+// Candidate list of a tile window: ascending sorted indices with, per entry, a
+// conservative range of distances from the eye (= ray parameters) that its box spans.
+struct CandList {
+    const int* id;
+    const float* lo;
+    const float* hi;
+    int n;
+    int* pend;      // per-warp scratch, 2 * kFan ints
+};
+
+// Any-hit search over a candidate list that is known to contain every Gaussian the
+// query can hit.  Entries are first filtered by their depth range (shared memory
+// only); survivors are compacted, in order, into full groups of 32 for the exact test.
+template <bool COUNT, class LeafFn>
+__device__ __forceinline__ void search_list(const MarchLaunch& L, const Ray& r, float tmin, float tmax,
+                                            const CandList& c, int lane, Tally& tl, LeafFn&& leaf) {
+    int npend = 0;
+    for (int base = 0; base < c.n; base += kFan) {
+        int k = base + lane;
+        bool pass = k < c.n && c.lo[k] <= tmax && c.hi[k] >= tmin;
+        unsigned m = __ballot_sync(kFull, pass);
+        if (pass) c.pend[npend + __popc(m & ((1u << lane) - 1u))] = c.id[k];
+        npend += __popc(m);
+        __syncwarp();
+        if (npend >= kFan) {
+            int j = c.pend[lane];
+            LeafTest t = test_gaussian(L, r, j, true, tmin, tmax, tl, COUNT);
+            bool go = leaf(t, j);
+            int moved = (lane + kFan < npend) ? c.pend[lane + kFan] : 0;
+            __syncwarp();
+            c.pend[lane] = moved;
+            npend -= kFan;
+            __syncwarp();
+            if (!go) return;
+        }
+    }
+    if (npend > 0) {
+        bool valid = lane < npend;
+        int j = valid ? c.pend[lane] : 0;
+        LeafTest t = test_gaussian(L, r, j, valid, tmin, tmax, tl, COUNT);
+        leaf(t, j);
+        __syncwarp();
+    }
+}
+
+// Closest hit among the candidates, +inf if none.
+template <bool COUNT>
+__device__ __forceinline__ float closest_in_list(const MarchLaunch& L, const Ray& r, float tmin, float tmax,
+                                                 const CandList& c, int lane, Tally& tl) {
+    float best = INFINITY;
+    if (!(tmin <= tmax)) return best;
+    search_list<COUNT>(L, r, tmin, tmax, c, lane, tl, [&](const LeafTest& t, int) {
+        if (t.hit) best = fminf(best, t.t_hit);
+        return true;
+    });
+    return warp_min_f(best);
+}
+
+// ---------------------------------------------------------------- per-ray state machine shared by both passes
+struct SlabPlan {
+    float dt, slab, tmin, tmax;
+    bool traced;
+};
+
+// cuda_train/forward/gaussians_aabb.cu:267-280
+__device__ __forceinline__ SlabPlan plan_slab(const rgx_march& m, float tbuffer, float T, float tenter, float texit) {
+    SlabPlan p;
+    p.dt = m.dt_step;
+    if (m.dynamic_sampling) {
+        float dt_dist = fmaxf(__fdiv_rn(tbuffer, 1024.0f), m.dt_step);
+        p.dt = fminf(__fmul_rn(dt_dist, rcbrtf(T)), __fmul_rn(4.0f, m.dt_step));
+    }
+    p.slab = __fmul_rn(p.dt, (float)kSlab);
+    p.tmin = fmaxf(tenter, tbuffer);
+    p.tmax = fminf(texit, __fadd_rn(tbuffer, p.slab));
+    p.traced = p.tmax > tenter;
+    return p;
+}
+
+// Scene-box clip, cuda_train/forward/gaussians_aabb.cu:212-224.
+__device__ __forceinline__ void clip_scene(const SceneBox& b, const Ray& r, float& tenter, float& texit) {
+    float t0x = __fmul_rn(b.lo[0] - r.o.x, r.inv.x), t1x = __fmul_rn(b.hi[0] - r.o.x, r.inv.x);
+    float t0y = __fmul_rn(b.lo[1] - r.o.y, r.inv.y), t1y = __fmul_rn(b.hi[1] - r.o.y, r.inv.y);
+    float t0z = __fmul_rn(b.lo[2] - r.o.z, r.inv.z), t1z = __fmul_rn(b.hi[2] - r.o.z, r.inv.z);
+    tenter = fmaxf(0.0f, fmaxf(fminf(t0x, t1x), fmaxf(fminf(t0y, t1y), fminf(t0z, t1z))));
+    texit = fminf(fmaxf(t0x, t1x), fminf(fmaxf(t0y, t1y), fmaxf(t0z, t1z)));
+}
+
+// Evaluate `count` staged Gaussians at this lane's sample: sums of sigma*g and of
+// (payload)*g, payload being rgb*sigma in the forward (cuda_train/forward/gaussians_aabb.cu:166-178).
+template <bool COUNT>
+__device__ __forceinline__ void eval_forward(const WarpShared& ws, int count, float tau, float& s, float& cr,
+                                             float& cg, float& cb, Tally& tl) {
+#pragma unroll 2
+    for (int j = 0; j < count; ++j) {
+        float4 A = ws.recA[j], B = ws.recB[j], C = ws.recC[j];
+        float yx = fmaf(tau, B.x, A.x), yy = fmaf(tau, B.y, A.y), yz = fmaf(tau, B.z, A.z);
+        float q = fmaf(yx, yx, fmaf(yy, yy, __fmul_rn(yz, yz)));
+        bool in = q < 1.0f;
+        float e = in ? ex2_approx(__fmul_rn(-A.w, q)) : 0.0f;
+        s = fmaf(B.w, e, s);
+        cr = fmaf(C.x, e, cr);
+        cg = fmaf(C.y, e, cg);
+        cb = fmaf(C.z, e, cb);
+        if (COUNT) tl.v[C_PAIRS] += __popc(__ballot_sync(kFull, in));
+    }
+}
+
+__device__ __forceinline__ void flush_tally(const MarchLaunch& L, const Tally& tl, int lane) {
+    if (L.counters && lane < C_NUM && tl.v[lane]) atomicAdd(&L.counters->v[lane], tl.v[lane]);
+}
+
+__device__ __forceinline__ unsigned long long mix64(unsigned long long x) {
+    x ^= x >> 33; x *= 0xff51afd7ed558ccdull; x ^= x >> 33; x *= 0xc4ceb9fe1a85ec53ull; x ^= x >> 33;
+    return x;
+}
+
+
+__device__ __forceinline__ void red_add_v4(float4* addr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+                 : "memory");
+}
+
+// Pass 2 over `count` staged Gaussians: each lane forms its sample's share of the
+// four per-Gaussian sums, the warp adds them up, and lane j keeps the totals of
+// staged Gaussian j.
+//   recA = (y_c.xyz, hk)  recB = (de.xyz, tbuffer - t_c)  recC = (chat_i, -, -, -)
+__device__ __forceinline__ void eval_backward(const WarpShared& ws, int count, float tau, float beta, float gamma,
+                                              int lane, float& o_sb, float& o_n0, float& o_n1, float& o_n2) {
+    for (int j = 0; j < count; ++j) {
+        float4 A = ws.recA[j], B = ws.recB[j], C = ws.recC[j];
+        float tc = __fadd_rn(tau, B.w);
+        float yx = fmaf(tc, B.x, A.x), yy = fmaf(tc, B.y, A.y), yz = fmaf(tc, B.z, A.z);
+        float q = fmaf(yx, yx, fmaf(yy, yy, __fmul_rn(yz, yz)));
+        float e = q < 1.0f ? ex2_approx(__fmul_rn(-A.w, q)) : 0.0f;
+        float ga = __fmul_rn(e, fmaf(C.x, beta, gamma));      // g * (alpha + beta*(chat_i - chat_s))
+        float sb = warp_sum(__fmul_rn(e, beta));
+        float n0 = warp_sum(ga);
+        float g1 = __fmul_rn(ga, tc);
+        float n1 = warp_sum(g1);
+        float n2 = warp_sum(__fmul_rn(g1, tc));
+        if (lane == j) { o_sb = sb; o_n0 = n0; o_n1 = n1; o_n2 = n2; }
+    }
+}
+
+// ---------------------------------------------------------------- one slab, generic over how Gaussians are enumerated
+//
+// `enumerate(leaf)` must call leaf(LeafTest, j) for groups of up to 32 Gaussians in
+// ascending sorted index j, all lanes converged, until leaf returns false.  The
+// three enumerations (exhaustive, per-ray hierarchy search, candidate list) give
+// the same hits in the same order, hence bit-identical sums.
+
+// Per-sample sums of sigma*g (s) and payload*g (c0..c2); payload is rgb*sigma in
+// the forward and (dl . rgb*sigma, 0, 0) in the backward.  Returns the hit count.
+template <bool COUNT, bool BWD, class Enum>
+__device__ __forceinline__ int slab_sums(const MarchLaunch& L, const rgx_march& m, float tbuffer, float tau,
+                                         int ray_id, int slab_index, float3 dl, WarpShared& ws, int lane, Tally& tl,
+                                         Enum&& enumerate, float& s, float& c0, float& c1, float& c2,
+                                         bool& overflow) {
+    int nstage = 0, nhit = 0;
+    bool ovf = false;
+    s = c0 = c1 = c2 = 0.f;
+    enumerate([&](const LeafTest& t, int j) {
+        unsigned mask = __ballot_sync(kFull, t.hit);
+        if (mask == 0u) return true;
+        int rank = __popc(mask & ((1u << lane) - 1u)), n = __popc(mask);
+        bool take = t.hit;
+        if (nhit + n > m.max_prim_slice) {            // cuda_train/forward/gaussians_aabb.cu:352-356
+            n = m.max_prim_slice - nhit;
+            take = take && rank < n;
+            ovf = true;
+        }
+        if (take) {
+            int slot = nstage + rank;
+            float4 c = __ldg(&L.g.rgba[j]);
+            ws.recA[slot] = make_float4(fmaf(tbuffer, t.de.x, t.Oe.x), fmaf(tbuffer, t.de.y, t.Oe.y),
+                                        fmaf(tbuffer, t.de.z, t.Oe.z), __ldg(&L.g.hk[j]));
+            ws.recB[slot] = make_float4(t.de.x, t.de.y, t.de.z, c.w);
+            ws.recC[slot] = BWD ? make_float4(fmaf(dl.x, c.x, fmaf(dl.y, c.y, __fmul_rn(dl.z, c.z))), 0.f, 0.f, 0.f)
+                                : make_float4(c.x, c.y, c.z, 0.f);
+        }
+        if (COUNT) {
+            unsigned long long hsh = take ? mix64(((unsigned long long)ray_id << 40) ^
+                                                  ((unsigned long long)slab_index << 24) ^
+                                                  (unsigned long long)__ldg(&L.g.perm[j])) : 0ull;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) hsh += __shfl_xor_sync(kFull, hsh, o);
+            tl.v[C_HASH] += hsh;
+        }
+        nstage += n;
+        nhit += n;
+        __syncwarp();
+        if (nstage > kStage - kFan) {
+            eval_forward<COUNT>(ws, nstage, tau, s, c0, c1, c2, tl);
+            nstage = 0;
+            __syncwarp();
+        }
+        return !ovf;
+    });
+    if (nstage > 0) {
+        eval_forward<COUNT>(ws, nstage, tau, s, c0, c1, c2, tl);
+        __syncwarp();
+    }
+    overflow = ovf;
+    return nhit;
+}
+
+// Transmittance bookkeeping of one slab (cuda_train/forward/gaussians_aabb.cu:190-201):
+// lanes are samples, the transmittance before sample s is a prefix product, and the
+// second chunk of 16 samples only counts if T is still above the threshold after the first.
+struct SlabTrans {
+    float x, w, Ts, incl, T16, T32;
+    bool live;
+};
+__device__ __forceinline__ SlabTrans slab_transmittance(float s, float dt, float T, float eps, int lane) {
+    SlabTrans o;
+    o.x = __fmul_rn(s, dt);
+    o.incl = warp_scan(o.x, lane);
+    float excl = __fadd_rn(o.incl, -o.x);
+    o.w = exp_neg(o.x);
+    o.Ts = __fmul_rn(T, exp_neg(excl));
+    o.T16 = __shfl_sync(kFull, o.Ts, kChunk);
+    o.live = lane < kChunk || o.T16 > eps;
+    o.T32 = __fmul_rn(T, exp_neg(__shfl_sync(kFull, o.incl, 31)));
+    return o;
+}
+__device__ __forceinline__ float slab_exit_T(const SlabTrans& o, float eps) { return (o.T16 > eps) ? o.T32 : o.T16; }
+
+struct RayColor {
+    float T, Cr, Cg, Cb, depth;
+};
+
+__device__ __forceinline__ void composite_forward(const SlabPlan& p, float tbuffer, float tau, float eps, int lane,
+                                                  float s, float cr, float cg, float cb, bool want_depth,
+                                                  RayColor& st) {
+    SlabTrans tr = slab_transmittance(s, p.dt, st.T, eps, lane);
+    float one_m_w = 1.0f - tr.w;
+    float f = tr.live ? __fmul_rn(tr.Ts, __fmul_rn(p.dt, __fdividef(one_m_w, fmaxf(tr.x, 1e-6f)))) : 0.f;
+    st.Cr = __fadd_rn(st.Cr, warp_sum(__fmul_rn(f, cr)));
+    st.Cg = __fadd_rn(st.Cg, warp_sum(__fmul_rn(f, cg)));
+    st.Cb = __fadd_rn(st.Cb, warp_sum(__fmul_rn(f, cb)));
+    if (want_depth) {
+        float ts = __fadd_rn(tbuffer, tau);
+        st.depth = __fadd_rn(st.depth, warp_sum(tr.live ? __fmul_rn(__fmul_rn(tr.Ts, one_m_w), ts) : 0.f));
+    }
+    st.T = slab_exit_T(tr, eps);
+}
+
+// Per-sample terms of the backward (cuda_train/backward/gaussians_aabb.cu:330-352).
+struct SlabBackTerms {
+    float beta, gamma, d_total;
+    SlabTrans tr;
+};
+__device__ __forceinline__ SlabBackTerms slab_back_terms(float s, float dc, float dt, float T, float D, float eps,
+                                                         int lane) {
+    SlabBackTerms o;
+    o.tr = slab_transmittance(s, dt, T, eps, lane);
+    float inv_s = s > 0.f ? __fdividef(1.0f, s) : 0.f;
+    float chat = __fmul_rn(dc, inv_s);
+    float one_m_w = 1.0f - o.tr.w;
+    float step = __fmul_rn(__fmul_rn(o.tr.Ts, one_m_w), chat);                 // T_s (1-w_s) chat_s
+    float sincl = warp_scan(step, lane);
+    float Ds = __fadd_rn(D, -__fadd_rn(sincl, -step));
+    o.beta = o.tr.live ? __fmul_rn(__fmul_rn(o.tr.Ts, one_m_w), inv_s) : 0.f;
+    float alpha = __fmul_rn(fmaf(o.tr.Ts, chat, -Ds), dt);
+    o.gamma = o.tr.live ? fmaf(-o.beta, chat, alpha) : 0.f;
+    o.d_total = __shfl_sync(kFull, sincl, 31);
+    return o;
+}
+
+// Gradient of one (ray, slab, Gaussian) triple from its four moment sums; the
+// sample-wise sums of cuda_train/backward/gaussians_aabb.cu:401-441 collapse to
+// these because the whitened offset is affine in the sample position.
+struct GaussGrad {
+    float3 dpos;
+    float dscale[3];
+    float4 dquat;
+    float dsigma;
+    float drgb_scale;   // dL/drgb = dl * drgb_scale
+};
+__device__ __forceinline__ GaussGrad expand_gradient(const MarchLaunch& L, const Ray& r, int j, float4 A, float4 B,
+                                                     float tbuffer, float sb, float n0, float n1, float n2) {
+    const float4 sd = __ldg(&L.g.sdens[j]);
+    const float4 qq = __ldg(&L.g.quat[j]);
+    const float4 g0 = __ldg(&L.g.g0[j]);
+    const float sigma = sd.w;
+    const float kk = __fsqrt_rn(__fmul_rn(2.0f * 0.6931471805599453f, A.w));   // k = sqrt(2 ln(sigma/sigma_t))
+    const float m0 = sigma * n0, m1 = sigma * n1, m2 = sigma * n2;
+    const float tc = __fadd_rn(tbuffer, -B.w);                                 // reference point t_c
+    const float3 xc = make_float3(fmaf(tc, r.d.x, r.o.x - g0.x), fmaf(tc, r.d.y, r.o.y - g0.y),
+                                  fmaf(tc, r.d.z, r.o.z - g0.z));
+    const float inv_sc[3] = {1.0f / sd.x, 1.0f / sd.y, 1.0f / sd.z};
+    const float ycv[3] = {A.x, A.y, A.z}, dev[3] = {B.x, B.y, B.z};
+    float3 U, V, Wc;
+    quat_to_columns(qq, U, V, Wc);
+    const float3 cols[3] = {U, V, Wc};
+    GaussGrad g;
+    g.dpos = make_float3(0.f, 0.f, 0.f);
+    float3 dcol[3];
+    const float k2 = kk * kk;
+#pragma unroll
+    for (int a = 0; a < 3; ++a) {
+        // sum_s omega y_a^2 / s_a,  y = k (y_c + t' de)
+        g.dscale[a] = k2 * (m0 * ycv[a] * ycv[a] + 2.0f * m1 * ycv[a] * dev[a] + m2 * dev[a] * dev[a]) * inv_sc[a];
+        const float coef = kk * (m0 * ycv[a] + m1 * dev[a]) * inv_sc[a];
+        g.dpos = g.dpos + cols[a] * coef;
+        // -(1/s_a) sum_s omega y_a (x_c + t' d)
+        const float cx = kk * (m0 * ycv[a]) + kk * (m1 * dev[a]);
+        const float cd = kk * (m1 * ycv[a]) + kk * (m2 * dev[a]);
+        dcol[a] = (xc * cx + r.d * cd) * (-inv_sc[a]);
+    }
+    g.dquat = quat_grad_from_columns(qq, dcol[0], dcol[1], dcol[2]);
+    g.dsigma = n0;
+    g.drgb_scale = sigma * sb;
+    return g;
+}
+
+// Pass 2 of the backward for one slab: enumerate the same hits again and hand the
+// gradient of every (slab, Gaussian) pair to emit(j, GaussGrad) on the owning lane.
+template <class Enum, class Emit>
+__device__ __forceinline__ void slab_gradients(const MarchLaunch& L, const rgx_march& m, const Ray& r,
+                                               const SlabPlan& p, float tbuffer, float tau, float3 dl, float beta,
+                                               float gamma, WarpShared& ws, int* prim_of, int lane,
+                                               Enum&& enumerate, Emit&& emit) {
+    int nstage = 0, nhit = 0;
+    auto drain = [&]() {
+        float sb = 0.f, n0 = 0.f, n1 = 0.f, n2 = 0.f;
+        eval_backward(ws, nstage, tau, beta, gamma, lane, sb, n0, n1, n2);
+        if (lane < nstage) {
+            const int j = prim_of[lane];
+            emit(j, expand_gradient(L, r, j, ws.recA[lane], ws.recB[lane], tbuffer, sb, n0, n1, n2));
+        }
+        nstage = 0;
+        __syncwarp();
+    };
+    enumerate([&](const LeafTest& t, int j) {
+        unsigned mask = __ballot_sync(kFull, t.hit);
+        if (mask == 0u) return true;
+        int rank = __popc(mask & ((1u << lane) - 1u)), n = __popc(mask);
+        bool take = t.hit;
+        bool stop = false;
+        if (nhit + n > m.max_prim_slice) {
+            n = m.max_prim_slice - nhit;
+            take = take && rank < n;
+            stop = true;
+        }
+        if (nstage + n > kFan) drain();          // one staged Gaussian per lane
+        if (take) {
+            int slot = nstage + rank;
+            float4 c = __ldg(&L.g.rgba[j]);
+            // reference point: closest approach clamped to the slab, so that the moments stay small
+            float a = dot3(t.de, t.de);
+            float tca = __fdividef(-dot3(t.Oe, t.de), a);
+            tca = fminf(fmaxf(tca, tbuffer), __fadd_rn(tbuffer, p.slab));
+            ws.recA[slot] = make_float4(fmaf(tca, t.de.x, t.Oe.x), fmaf(tca, t.de.y, t.Oe.y),
+                                        fmaf(tca, t.de.z, t.Oe.z), __ldg(&L.g.hk[j]));
+            ws.recB[slot] = make_float4(t.de.x, t.de.y, t.de.z, __fadd_rn(tbuffer, -tca));
+            float ci = __fdividef(fmaf(dl.x, c.x, fmaf(dl.y, c.y, __fmul_rn(dl.z, c.z))), c.w);
+            ws.recC[slot] = make_float4(ci, 0.f, 0.f, 0.f);
+            prim_of[slot] = j;
+        }
+        nstage += n;
+        nhit += n;
+        __syncwarp();
+        return !stop;
+    });
+    if (nstage > 0) drain();
+}
+
+__device__ __forceinline__ void emit_global(const MarchLaunch& L, float3 dl, int j, const GaussGrad& g) {
+    float4* row = L.grad_rows + 4 * (size_t)j;
+    red_add_v4(row, g.dpos.x, g.dpos.y, g.dpos.z, g.dscale[0]);
+    red_add_v4(row + 1, g.dscale[1], g.dscale[2], g.dquat.x, g.dquat.y);
+    red_add_v4(row + 2, g.dquat.z, g.dquat.w, g.dsigma, dl.x * g.drgb_scale);
+    red_add_v4(row + 3, dl.y * g.drgb_scale, dl.z * g.drgb_scale, 0.f, 0.f);
+}
+
+}  // namespace
+
+}  // namespace rgx

@@ -43,10 +43,10 @@ struct SortedGaussians {
 };
 
 struct DeviceCounters {   // mirrors rgx_counters
-    unsigned long long v[12];
+    unsigned long long v[16];
 };
 enum { C_RAYS, C_SLABS, C_SLABS_HIT, C_CLOSEST, C_HITS, C_PAIRS, C_OVF, C_NODE_TESTS, C_PRIM_TESTS, C_ELL_TESTS,
-       C_STACK_OVF, C_HASH };
+       C_STACK_OVF, C_HASH, C_WINDOWS, C_RETRIES, C_FALLBACKS, C_CANDS, C_NUM };
 
 struct SceneBox {         // written by the build, read by the march kernels
     float lo[3];
@@ -91,6 +91,7 @@ struct BuildLaunch {
     rgx_scene sc;
     float sigma_threshold;
     int morton_bits;
+    int curve;
     int n_pad;
     // outputs
     uint64_t* keys_in; uint64_t* keys_out;

@@ -166,7 +166,8 @@ class Renderer:
         return m
 
     # -- API
-    def build(self, positions, scales, quaternions, densities, sigma_threshold=SIGMA_THRESHOLD, morton_bits=10):
+    def build(self, positions, scales, quaternions, densities, sigma_threshold=SIGMA_THRESHOLD, morton_bits=10,
+              curve=_lib.CURVE_HILBERT):
         """Boxes, Morton sort and hierarchy refit for the current parameters
         (replaces ellipsoids_bbox_from_quat + create_acceleration_structure)."""
         positions, scales, quaternions, densities = (_as_input(positions, "positions"), _as_input(scales, "scales"),
@@ -174,7 +175,7 @@ class Renderer:
                                                      _as_input(densities, "densities"))
         sc = self._scene(positions, scales, quaternions, densities)
         _lib.check(self._ctx, self._lib.rgx_build(self._ctx, C.byref(sc), float(sigma_threshold), int(morton_bits),
-                                                  self._stream()))
+                                                  int(curve), self._stream()))
         self._n_built = positions.shape[0]
 
     def forward(self, positions, scales, quaternions, densities, color_features, sg_features, sharpness, lobe_axis,
