@@ -1,0 +1,385 @@
+#!/usr/bin/env python
+"""Benchmark of the differentiable Gaussian ray-marching path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload ("unbounded-3M"): the seeded 3,000,000-Gaussian unbounded scene,
+1256x828 pinhole cameras on a ring, SH degree 3, dynamic sampling, hit cap 512 --
+synthetic, with the shape of a Mip-NeRF-360 scene.  One *step* is one training
+step with gradient accumulation over 20 views: acceleration-structure build, then
+per view colour evaluation, forward march, L1 loss gradient, backward march and
+gradient finalise, accumulated into one flat gradient buffer.  With N GPUs the 20
+views' image rows are split evenly over the ranks (every rank holds all Gaussians)
+and one NCCL all-reduce of the gradient buffer ends the step, so total work is
+fixed (strong scaling).
+
+Printed JSON line (rank 0): ``value`` = forward+backward Mrays/s of the whole job
+with all inputs resident in HBM; ``e2e`` = the same through the reference-facing
+autograd entry point with the target images copied from pinned host memory and the
+loss read back every step; ``roofline`` for the backward march kernel;
+``cpu_baseline`` = the reference's own device code compiled for the host CPU
+(oracle/_ref) on a bounded sample of the same workload.
+
+``--impl reference`` times that CPU build alone, on all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_VIEWS = 20
+WORKLOAD = "unbounded-3M"
+METRIC = "fwd+bwd Mrays/s (3M Gaussians, 1256x828)"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="rgx", choices=["rgx", "reference"])
+    ap.add_argument("--gaussians", type=int, default=3_000_000, help="for quick runs only; the headline is 3,000,000")
+    ap.add_argument("--width", type=int, default=1256)
+    ap.add_argument("--height", type=int, default=828)
+    ap.add_argument("--views", type=int, default=N_VIEWS)
+    ap.add_argument("--cpu-sample", type=str, default="20x13", help="image size of the CPU-baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """nvidia-smi clock/throttle samples during the timed region."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu)], stdout=open(self.path, "w"),
+                                         stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1])); mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            sm.sort()
+            out.update(sm_mhz=sm[len(sm) // 2], sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ----------------------------------------------------------------------------- CPU reference arm
+def cpu_reference_sample(scene, n_threads=0, size=(20, 13), repeats=1):
+    """Forward+backward of the reference's own device code (compiled for the CPU,
+    OptiX traversal replaced by an exhaustive loop) on a low-resolution image of the
+    same scene from the same camera.  Returns (rays, seconds per repeat)."""
+    import numpy as np
+    from oracle import ref_shim
+    from raygaussx_b200 import scenes as S
+    cam0 = scene.cameras[0]
+    cam = S.SimpleCamera(tuple(cam0.camera_center.cpu().tolist()), fovx=cam0.FoVx, fovy=cam0.FoVy, width=size[0],
+                         height=size[1])
+    rays = size[0] * size[1]
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        col, _, ctx = ref_shim.render_forward(*scene.tensors(), cam, scene.march, n_threads=n_threads)
+        tgt = S.l1_target(rays).numpy()
+        dl = (np.sign(col - tgt) / (3 * rays)).astype(np.float32)
+        ref_shim.render_backward(ctx, dl, n_threads=n_threads)
+        times.append(time.perf_counter() - t0)
+    return rays, times
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import ref_shim
+    from raygaussx_b200 import scenes as S
+    if not ref_shim.available():
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref is not built (run `make -C oracle` where "
+                                                              "the reference checkout is present)"}))
+        return
+    scene = S.unbounded_scene(n=args.gaussians, n_cameras=1, width=args.width, height=args.height)
+    w, h = (int(x) for x in args.cpu_sample.split("x"))
+    cores = os.cpu_count() or 1
+    for _ in range(args.warmup):
+        cpu_reference_sample(scene, size=(w, h))
+    rays, times = cpu_reference_sample(scene, size=(w, h), repeats=max(1, args.steps))
+    sec = sum(times) / len(times)
+    val = rays / sec / 1e6
+    sample = f"{w}x{h} rays of one view, forward+backward, all {args.gaussians} Gaussians"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "Mrays/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "gaussians": args.gaussians, "image": f"{args.width}x{args.height}",
+                   "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "Mrays/s", "cores": cores, "kind": "reference", "sample": sample},
+        "e2e": {"value": val, "unit": "Mrays/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from raygaussx_b200 import _lib, scenes as S
+    from raygaussx_b200 import render_optix as ro
+    from raygaussx_b200.dist import GradBuffer, accumulation_step, shard_rows
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the ray-marching path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    # ---- inputs (identical on every rank: seeded CPU generators)
+    scene = S.unbounded_scene(n=args.gaussians, n_cameras=200, width=args.width, height=args.height)
+    cams_py = scene.cameras[:args.views]
+    host_scene = scene
+    R = args.width * args.height
+    targets_host = [S.l1_target(R, seed=1000 + v).pin_memory() for v in range(args.views)]
+    scene_dev_tensors = [t.to(dev).contiguous() for t in host_scene.tensors()]
+    for c in cams_py:
+        c.to(dev)
+    cams = [ro.camera_struct(c) for c in cams_py]
+    targets = [t.to(dev, non_blocking=True) for t in targets_host]
+    mp = scene.march
+    renderer = ro.get_renderer(dev)
+    k_sh = scene_dev_tensors[4].shape[2]
+    grads = GradBuffer(args.gaussians, k_sh, dev)
+
+    def march_of(cam, rows, flags):
+        return ro.Renderer._march(mp.dt_step, mp.dynamic_sampling, mp.max_prim_slice, mp.white_background,
+                                  mp.transmittance_eps, rows, cam.height, flags)
+
+    def step():
+        accumulation_step(renderer, scene_dev_tensors, cams, targets, march_of, grads, rank=rank, world=world)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    renderer.set_profiling(True)
+    renderer.read_kernel_times()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    clocks = sampler.stop() if rank == 0 else None
+    ktimes = renderer.read_kernel_times()
+    renderer.set_profiling(False)
+    t_ms = torch.tensor([ms], device=dev)
+    if world > 1:
+        dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
+    ms = float(t_ms.item())
+    ms_per_step = ms / args.steps
+    rays_per_step = args.views * R
+    value = rays_per_step / (ms_per_step * 1e-3) / 1e6
+
+    # ---- end to end through the reference-facing autograd entry point
+    e2e = None
+    if not args.no_e2e:
+        params = [t.clone().requires_grad_(True) for t in scene_dev_tensors[:5]] + list(scene_dev_tensors[5:])
+        my_blocks = shard_rows(args.views, args.height, rank, world)
+        my_views = sorted({b.view for b in my_blocks})           # whole views for the autograd path
+        share = {v: sum((b.row_end - b.row_begin) for b in my_blocks if b.view == v) / args.height for v in my_views}
+        loss_host = torch.zeros(1).pin_memory()
+
+        def e2e_step():
+            for p in params[:5]:
+                p.grad = None
+            total = torch.zeros((), device=dev)
+            for v in my_views:
+                tgt = targets_host[v].to(dev, non_blocking=True)                 # H2D of this view's target
+                st = ro.RenderOptixSettings(None, False, None, None, None, None, None, mp.dt_step, mp.dynamic_sampling,
+                                            cams_py[v], mp.max_prim_slice, 0, white_background=mp.white_background,
+                                            transmittance_eps=mp.transmittance_eps)
+                img = ro.RenderOptixFunction.apply(*params, st)
+                # a view shared between ranks is weighted by this rank's share of its rows
+                loss = (img - tgt).abs().mean() * (share[v] / args.views)
+                loss.backward()
+                total = total + loss.detach()
+            if world > 1:
+                flat = torch.cat([p.grad.reshape(-1) for p in params[:5]])
+                dist.all_reduce(flat)
+            loss_host.copy_(total.reshape(1), non_blocking=True)                 # D2H of the step's loss
+            torch.cuda.synchronize()
+            return float(loss_host.item())
+
+        e2e_step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n_e2e = max(1, min(2, args.steps))
+        e0.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        e1.record()
+        barrier()
+        t_e = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(t_e, op=dist.ReduceOp.MAX)
+        e_ms = float(t_e.item()) / n_e2e
+        e2e = {"value": rays_per_step / (e_ms * 1e-3) / 1e6, "unit": "Mrays/s",
+               "h2d_bytes_per_step": int(sum(targets_host[v].numel() * 4 for v in my_views)),
+               "d2h_bytes_per_step": 4, "ms_per_step": e_ms, "steps": n_e2e,
+               "api": "RenderOptixFunction.apply + L1 loss + backward, acceleration structure rebuilt every view "
+                      "as the reference does; views that straddle ranks are rendered whole on both"}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- roofline of the dominant kernel (backward march), from live CUDA-event timings
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+    peak_src = "measured" if "hbm_gbs" in peaks else "fallback"
+    sm_max_mhz = float(peaks.get("sm_max_mhz", 1965.0))
+    n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
+    bwd_launches = max(1, ktimes["backward_launches"])
+    bwd_ms = ktimes["backward_ms"] / bwd_launches
+    fwd_ms = ktimes["forward_ms"] / max(1, ktimes["forward_launches"])
+    rows_per_launch = sum(b.row_end - b.row_begin for b in shard_rows(args.views, args.height, 0, world)) / max(
+        1, len(shard_rows(args.views, args.height, 0, world)))
+    rays_per_launch = rows_per_launch * args.width
+    alg_bytes = 536.0 * args.gaussians + 28.0 * rays_per_launch          # backward: per Gaussian, per ray
+    achieved = alg_bytes / (bwd_ms * 1e-3) / 1e9
+    # work counters of one view (outside the timed region) for the FP32 / MUFU figures
+    renderer.reset_counters()
+    renderer.forward(*scene_dev_tensors, cams[0], march_of(cams[0], None, _lib.FLAG_COUNT_WORK))
+    cn = renderer.read_counters()
+    P, E, Sh = cn["hits"], cn["pairs_inside"], cn["slabs_hit"]
+    frac_view = rays_per_launch / R
+    f_bwd = (290.0 * P + 22.0 * E + 640.0 * Sh) * frac_view
+    mufu_bwd = (2.0 * E + 96.0 * Sh) * frac_view
+    fp32_peak = 2.0 * 128 * n_sm * sm_max_mhz * 1e6
+    mufu_peak = 16.0 * n_sm * sm_max_mhz * 1e6
+    roofline = {"kernel": "march_backward_tiled_kernel", "bound": "hbm", "achieved": achieved, "peak": hbm_peak,
+                "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_src, "traffic": None,
+                "ms_per_launch": bwd_ms, "launches_timed": ktimes["backward_launches"],
+                "forward_ms_per_launch": fwd_ms,
+                "algorithmic_bytes_per_launch": alg_bytes,
+                "fp32_frac": f_bwd / (bwd_ms * 1e-3) / fp32_peak, "mufu_frac": mufu_bwd / (bwd_ms * 1e-3) / mufu_peak,
+                "note": "the march kernels are issue/latency bound, not HBM bound: fp32_frac and mufu_frac are useful "
+                        "flops and ex2 per second over the derived peaks (2*128*SMs*f, 16*SMs*f)",
+                "counters_per_view": {k: cn[k] for k in ("rays", "slabs", "slabs_hit", "closest_queries", "hits",
+                                                         "pairs_inside", "overflow_slabs", "windows",
+                                                         "fallback_windows", "candidates")}}
+
+    # ---- CPU baseline on a bounded sample (rank 0, N = 1 only)
+    cpu_baseline = None
+    if world == 1 and not args.no_cpu_baseline:
+        try:
+            from oracle import ref_shim
+            if ref_shim.available():
+                w, h = (int(x) for x in args.cpu_sample.split("x"))
+                rays, times = cpu_reference_sample(host_scene_cpu(scene), size=(w, h))
+                cpu_baseline = {"value": rays / times[0] / 1e6, "unit": "Mrays/s", "cores": os.cpu_count() or 1,
+                                "kind": "reference",
+                                "sample": f"{w}x{h} rays of view 0, forward+backward, all {args.gaussians} Gaussians "
+                                          f"({times[0]:.1f} s)"}
+        except Exception as exc:  # the baseline is a report, never a reason to lose the bench line
+            cpu_baseline = {"value": None, "unit": "Mrays/s", "cores": os.cpu_count() or 1, "kind": "reference",
+                            "sample": f"failed: {exc}"}
+
+    launches_per_step = 6 + 5 * len(shard_rows(args.views, args.height, 0, world))
+    out = {
+        "metric": METRIC, "value": value, "unit": "Mrays/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "gaussians": args.gaussians, "image": f"{args.width}x{args.height}",
+                   "views_per_step": args.views, "sh_degree": 3, "sharding": f"rows/{world}",
+                   "l2": "inputs larger than L2 (Gaussian records 0.5 GB, gradients 0.7 GB)"},
+        "views_per_s": args.views / (ms_per_step * 1e-3),
+        "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
+        "roofline": roofline, "cpu_baseline": cpu_baseline,
+    }
+    print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def host_scene_cpu(scene):
+    """A CPU copy of the scene for the host-side baseline."""
+    import copy
+    sc = copy.copy(scene)
+    for k in ("positions", "scales", "quaternions", "densities", "color_features", "sph_gauss_features",
+              "bandwidth_sharpness", "lobe_axis"):
+        setattr(sc, k, getattr(scene, k).detach().cpu())
+    sc.cameras = [c for c in scene.cameras]
+    return sc
+
+
+if __name__ == "__main__":
+    main()

@@ -171,6 +171,14 @@ RGX_API int rgx_scene_box(rgx_ctx* ctx, float bb_min[3], float bb_max[3], rgx_st
 RGX_API int rgx_reset_counters(rgx_ctx* ctx, rgx_stream stream);
 RGX_API int rgx_read_counters(rgx_ctx* ctx, rgx_counters* out, rgx_stream stream);
 
+/* Kernel timing for roofline reports.  While enabled, every rgx_forward /
+ * rgx_backward brackets its march kernel with CUDA events on the launching stream.
+ * rgx_read_kernel_times waits for the recorded events, returns the summed
+ * durations (milliseconds) and launch counts since the last read, and clears them. */
+RGX_API int rgx_set_profiling(rgx_ctx* ctx, int enable);
+RGX_API int rgx_read_kernel_times(rgx_ctx* ctx, float* forward_ms, int* forward_launches, float* backward_ms,
+                                  int* backward_launches);
+
 /* Bytes of device memory currently held by the context's workspace. */
 RGX_API size_t rgx_workspace_bytes(const rgx_ctx* ctx);
 

@@ -180,6 +180,9 @@ def ellipsoid_aabbs(positions, scales, quaternions, densities, sigma_threshold):
     # rows of R are (U_a, V_a, W_a); half extent along world axis a
     h = d[:, None] * ((scales[:, 0:1] * U) ** 2 + (scales[:, 1:2] * V) ** 2 + (scales[:, 2:3] * W) ** 2).sqrt()
     lo, hi = positions - h, positions + h
+    if positions.shape[0] == 0:
+        z = torch.zeros(3, dtype=positions.dtype)
+        return lo, hi, z, z.clone()
     return lo, hi, lo.min(dim=0).values, hi.max(dim=0).values
 
 

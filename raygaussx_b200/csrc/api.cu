@@ -5,6 +5,7 @@
 #include <new>
 #include <string>
 #include <unordered_map>
+#include <vector>
 
 using namespace rgx;
 
@@ -33,6 +34,11 @@ struct rgx_ctx {
     int n = 0, n_pad = 0;
     float sigma_threshold = 0.1f;
     Hierarchy hier{};
+    // optional kernel timing
+    bool profiling = false;
+    struct Timed { cudaEvent_t a, b; int kind; };
+    std::vector<Timed> timed;       // recorded, not yet read
+    std::vector<Timed> spare;       // event pairs ready for reuse
 };
 
 namespace {
@@ -169,6 +175,25 @@ int run_colors(rgx_ctx* ctx, const rgx_scene* sc, const float eye[3], cudaStream
     return e == cudaSuccess ? RGX_OK : cuda_fail(ctx, e, "colour kernel");
 }
 
+struct ScopedTimer {   // brackets one kernel launch with events when profiling is on
+    rgx_ctx* ctx;
+    cudaStream_t s;
+    rgx_ctx::Timed t{};
+    bool on = false;
+    ScopedTimer(rgx_ctx* c, cudaStream_t st, int kind) : ctx(c), s(st) {
+        if (!c->profiling || c->timed.size() >= 65536) return;
+        if (!c->spare.empty()) { t = c->spare.back(); c->spare.pop_back(); }
+        else if (cudaEventCreate(&t.a) != cudaSuccess || cudaEventCreate(&t.b) != cudaSuccess) return;
+        t.kind = kind;
+        on = cudaEventRecord(t.a, s) == cudaSuccess;
+    }
+    ~ScopedTimer() {
+        if (!on) return;
+        cudaEventRecord(t.b, s);
+        ctx->timed.push_back(t);
+    }
+};
+
 }  // namespace
 
 extern "C" {
@@ -194,6 +219,8 @@ void rgx_destroy(rgx_ctx* ctx) {
                     ctx->cub_temp, ctx->bounds, ctx->box, ctx->counters};
     for (void* p : ptrs)
         if (p) cudaFree(p);
+    for (auto* v : {&ctx->timed, &ctx->spare})
+        for (auto& t : *v) { cudaEventDestroy(t.a); cudaEventDestroy(t.b); }
     delete ctx;
 }
 
@@ -274,7 +301,11 @@ int rgx_forward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, con
     cudaStream_t s = (cudaStream_t)stream;
     if ((rc = run_colors(ctx, scene, cam->eye, s))) return rc;
     L.rgb = rgb; L.alpha = alpha; L.depth = depth;
-    cudaError_t e = launch_march_forward(L, s);
+    cudaError_t e;
+    {
+        ScopedTimer timer(ctx, s, 0);
+        e = launch_march_forward(L, s);
+    }
     return e == cudaSuccess ? RGX_OK : cuda_fail(ctx, e, "forward march");
 }
 
@@ -296,7 +327,11 @@ int rgx_backward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, co
     cudaError_t e = cudaMemsetAsync(ctx->grad_rows, 0, sizeof(float4) * 4 * (size_t)ctx->n_pad, s);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "backward memset");
     L.rgb_in = rgb; L.dl_drgb = dL_drgb; L.grad_rows = ctx->grad_rows;
-    if ((e = launch_march_backward(L, s)) != cudaSuccess) return cuda_fail(ctx, e, "backward march");
+    {
+        ScopedTimer timer(ctx, s, 1);
+        e = launch_march_backward(L, s);
+    }
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "backward march");
     FinalizeLaunch f{};
     f.sc = *scene;
     f.gr = *grads;
@@ -333,6 +368,32 @@ int rgx_scene_box(rgx_ctx* ctx, float bb_min[3], float bb_max[3], rgx_stream str
     if (e != cudaSuccess) return cuda_fail(ctx, e, "scene box read-back");
     std::memcpy(bb_min, h.lo, sizeof(h.lo));
     std::memcpy(bb_max, h.hi, sizeof(h.hi));
+    return RGX_OK;
+}
+
+int rgx_set_profiling(rgx_ctx* ctx, int enable) {
+    if (!ctx) return RGX_E_INVALID;
+    ctx->profiling = enable != 0;
+    return RGX_OK;
+}
+
+int rgx_read_kernel_times(rgx_ctx* ctx, float* forward_ms, int* forward_launches, float* backward_ms,
+                          int* backward_launches) {
+    if (!ctx || !forward_ms || !forward_launches || !backward_ms || !backward_launches) return RGX_E_INVALID;
+    cudaSetDevice(ctx->device);
+    float sum[2] = {0.f, 0.f};
+    int cnt[2] = {0, 0};
+    for (auto& t : ctx->timed) {
+        float ms = 0.f;
+        if (cudaEventSynchronize(t.b) == cudaSuccess && cudaEventElapsedTime(&ms, t.a, t.b) == cudaSuccess) {
+            sum[t.kind] += ms;
+            cnt[t.kind] += 1;
+        }
+        ctx->spare.push_back(t);
+    }
+    ctx->timed.clear();
+    *forward_ms = sum[0]; *forward_launches = cnt[0];
+    *backward_ms = sum[1]; *backward_launches = cnt[1];
     return RGX_OK;
 }
 

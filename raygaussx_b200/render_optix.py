@@ -223,6 +223,18 @@ class Renderer:
         _lib.check(self._ctx, self._lib.rgx_read_counters(self._ctx, C.byref(c), self._stream()))
         return c.as_dict()
 
+    def set_profiling(self, enable: bool):
+        """Bracket every march kernel with CUDA events (see :meth:`read_kernel_times`)."""
+        _lib.check(self._ctx, self._lib.rgx_set_profiling(self._ctx, 1 if enable else 0))
+
+    def read_kernel_times(self) -> dict:
+        """Summed march-kernel durations (ms) and launch counts since the last read."""
+        f, b = C.c_float(), C.c_float()
+        nf, nb = C.c_int(), C.c_int()
+        _lib.check(self._ctx, self._lib.rgx_read_kernel_times(self._ctx, C.byref(f), C.byref(nf), C.byref(b),
+                                                              C.byref(nb)))
+        return dict(forward_ms=f.value, forward_launches=nf.value, backward_ms=b.value, backward_launches=nb.value)
+
     def workspace_bytes(self) -> int:
         return int(self._lib.rgx_workspace_bytes(self._ctx))
 

@@ -1,0 +1,241 @@
+"""Parity of the CUDA path with the oracle and the reference's golden vectors (B200, `-m gpu`).
+
+Every call goes through the C ABI of librgx.so (ctypes), the same way the autograd
+entry point does.  Tolerances: max abs error 1e-4 on RGB and alpha, relative error
+1e-3 on gradients (max |a-b| / max |a| per tensor), identical hit sets between the
+tiled, per-ray and exhaustive searches.  Colour comparisons skip rays whose discrete
+decisions sit within 1e-4 (relative) of flipping in the float64 oracle; the number of
+skipped rays is asserted to stay small.
+"""
+import numpy as np
+import pytest
+import torch
+
+from raygaussx_b200 import _lib, scenes
+from tests.helpers import CASES, GRAD_NAMES, SMALL_CASES, input_checksum, load_golden, loss_gradient, make_scene, rel_max
+
+pytestmark = pytest.mark.gpu
+
+RGB_TOL = 1e-4
+GRAD_TOL = 1e-3
+MARGIN = 1e-4
+
+
+@pytest.fixture(scope="module")
+def ro():
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device: there is no CPU path")
+    from raygaussx_b200 import render_optix
+    _lib.lib()      # fails loudly if librgx.so is missing
+    return render_optix
+
+
+def settings_for(ro, sc, cam, **kw):
+    m = sc.march
+    return ro.RenderOptixSettings(None, False, None, None, None, None, None, m.dt_step, m.dynamic_sampling, cam,
+                                  m.max_prim_slice, sc.sph_gauss_features.shape[2],
+                                  white_background=m.white_background, transmittance_eps=m.transmittance_eps, **kw)
+
+
+def render(ro, sc, flags=0, rows=None, want=True, curve=None, bits=10):
+    dev = torch.device("cuda")
+    tens = [t.to(dev).contiguous() for t in sc.tensors()]
+    cam = sc.cameras[0]
+    cam.to(dev)
+    cs = ro.camera_struct(cam)
+    r = ro.get_renderer()
+    r.build(*tens[:4], morton_bits=bits, **({} if curve is None else {"curve": curve}))
+    march = ro._settings_march(settings_for(ro, sc, cam), cs, flags=flags, rows=rows)
+    rgb, alpha, depth = r.forward(*tens, cs, march, want_alpha=want, want_depth=want)
+    return r, tens, cs, rgb, alpha, depth
+
+
+def backward(ro, r, sc, tens, cs, rgb, dl, flags=0, rows=None, grads=None):
+    march = ro._settings_march(settings_for(ro, sc, sc.cameras[0]), cs, flags=flags, rows=rows)
+    if grads is None:
+        grads = [torch.full_like(t, float("nan")) for t in tens]       # must be overwritten, not added to
+    r.backward(*tens, cs, march, rgb, dl.to(rgb.device, torch.float32).contiguous(), tuple(grads))
+    torch.cuda.synchronize()
+    return grads
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_forward_and_backward_match_golden(ro, name):
+    g = load_golden(name)
+    sc = make_scene(name)
+    assert input_checksum(sc) == pytest.approx(float(g["input_sum"]), rel=1e-12)
+    r, tens, cs, rgb, alpha, depth = render(ro, sc)
+    steady = g["oracle_margin"] > MARGIN
+    assert steady.mean() > 0.75
+    err = np.abs(rgb.cpu().numpy().astype(np.float64) - g["oracle_rgb"]).max(axis=1)
+    assert err[steady].max() <= RGB_TOL
+    assert np.abs(alpha.cpu().numpy() - g["oracle_alpha"])[steady].max() <= RGB_TOL
+    assert np.abs(depth.cpu().numpy() - g["oracle_depth"])[steady].max() <= 5e-4
+    # against the reference's own device code (fp32): same tolerance
+    assert np.abs(rgb.cpu().numpy() - g["ref_rgb"]).max(axis=1)[steady].max() <= RGB_TOL
+    grads = backward(ro, r, sc, tens, cs, rgb, torch.from_numpy(g["dl"]))
+    for nm, gr in zip(GRAD_NAMES, grads):
+        if "oracle_grad_" + nm in g.files:
+            assert rel_max(g["oracle_grad_" + nm], gr.cpu()) <= GRAD_TOL, nm
+            assert rel_max(g["ref_grad_" + nm], gr.cpu()) <= GRAD_TOL, nm
+
+
+@pytest.mark.parametrize("name", ["small_static", "small_dynamic_white", "config1"])
+def test_search_variants_give_identical_hits_and_images(ro, name):
+    sc = make_scene(name)
+    results = {}
+    for label, flags in (("tiled", 0), ("per_ray", _lib.FLAG_PER_RAY_SEARCH), ("exhaustive", _lib.FLAG_BRUTE_FORCE)):
+        r = ro.get_renderer()
+        r.reset_counters()
+        _, tens, cs, rgb, alpha, _ = render(ro, sc, flags=flags | _lib.FLAG_COUNT_WORK)
+        c = r.read_counters()
+        assert c["stack_overflows"] == 0
+        results[label] = (rgb.clone(), c)
+    base_rgb, base_c = results["exhaustive"]
+    g = load_golden(name)
+    oc = dict(zip(("S", "S_h", "Q_c", "P", "E_in", "OVF"), g["oracle_counters"].tolist()))
+    for label in ("tiled", "per_ray"):
+        rgb, c = results[label]
+        assert c["hits_hash"] == base_c["hits_hash"], f"{label}: hit sets differ from the exhaustive search"
+        for k in ("rays", "slabs", "slabs_hit", "hits", "pairs_inside", "overflow_slabs"):
+            assert c[k] == base_c[k], (label, k)
+        assert torch.equal(rgb, base_rgb), f"{label}: image differs bitwise from the exhaustive search"
+    # work counters agree with the oracle's up to the handful of marginal predicates
+    assert base_c["slabs"] == pytest.approx(oc["S"], rel=2e-3)
+    assert base_c["hits"] == pytest.approx(oc["P"], rel=2e-3)
+    assert base_c["pairs_inside"] == pytest.approx(oc["E_in"], rel=5e-3)
+
+
+def test_backward_variants_agree(ro):
+    sc = make_scene("small_dynamic_white")
+    r, tens, cs, rgb, _, _ = render(ro, sc)
+    dl = loss_gradient(rgb.cpu().double(), rgb.shape[0])
+    base = backward(ro, r, sc, tens, cs, rgb, dl, flags=_lib.FLAG_BRUTE_FORCE)
+    for flags in (0, _lib.FLAG_PER_RAY_SEARCH):
+        other = backward(ro, r, sc, tens, cs, rgb, dl, flags=flags)
+        for a, b in zip(base[:5], other[:5]):
+            assert rel_max(a.cpu(), b.cpu()) < 1e-5      # only the order of atomic additions differs
+
+
+def test_autograd_function_is_a_drop_in(ro):
+    sc = make_scene("small_lobes_deg2")
+    g = load_golden("small_lobes_deg2")
+    dev = torch.device("cuda")
+    sc.to(dev)
+    leaves = [t.clone().requires_grad_(True) for t in sc.tensors()]
+    st = settings_for(ro, sc, sc.cameras[0])
+    from optix_raycasting import render_optix as r_ox          # the reference's import path
+    out = r_ox.RenderOptixFunction.apply(*leaves, st)
+    assert out.shape == (144, 3) and out.is_contiguous() and out.dtype == torch.float32
+    (out * torch.from_numpy(g["dl"]).to(dev, torch.float32)).sum().backward()
+    for nm, leaf in zip(GRAD_NAMES, leaves):
+        assert rel_max(g["oracle_grad_" + nm], leaf.grad.cpu()) <= GRAD_TOL, nm
+    # without lobes the three lobe gradients are None, as in the reference (render_optix.py:190-197)
+    sc2 = make_scene("small_deg0")
+    sc2.to(dev)
+    st2 = settings_for(ro, sc2, sc2.cameras[0])
+    ctx_out = ro.RenderOptixFunction.apply(*[t.clone().requires_grad_(i < 5) for i, t in enumerate(sc2.tensors())], st2)
+    grads = ro.RenderOptixFunction.backward
+    assert ctx_out.grad_fn is not None
+
+
+def test_exact_sh_gradient_switch(ro):
+    sc = make_scene("small_static")
+    from oracle import oracle
+    r, tens, cs, rgb, _, _ = render(ro, sc)
+    dl = loss_gradient(rgb.cpu().double(), rgb.shape[0])
+    exact = backward(ro, r, sc, tens, cs, rgb, dl, flags=_lib.FLAG_EXACT_SH_GRAD)
+    ref = oracle.render_backward(*[t.cpu() for t in tens], sc.cameras[0], sc.march, dl, reference_quirk=False)
+    assert rel_max(ref["positions"], exact[0].cpu()) <= GRAD_TOL
+    quirk = backward(ro, r, sc, tens, cs, rgb, dl)
+    assert not torch.equal(quirk[0], exact[0]) and torch.equal(quirk[1], exact[1])
+
+
+def test_row_ranges_and_accumulation(ro):
+    sc = make_scene("small_static")
+    r, tens, cs, full, _, _ = render(ro, sc)
+    dl = loss_gradient(full.cpu().double(), full.shape[0])
+    whole = backward(ro, r, sc, tens, cs, full, dl)
+    # two row ranges, rendered separately into one image, gradients accumulated
+    img = torch.full_like(full, -7.0)
+    for rows in ((0, 5), (5, 16)):
+        march = ro._settings_march(settings_for(ro, sc, sc.cameras[0]), cs, rows=rows)
+        r.forward(*tens, cs, march, out=img)
+    assert torch.equal(img, full)
+    acc = [torch.zeros_like(t) for t in tens]
+    for rows in ((0, 5), (5, 16)):
+        backward(ro, r, sc, tens, cs, full, dl, flags=_lib.FLAG_ACCUMULATE, rows=rows, grads=acc)
+    for a, b in zip(whole[:5], acc[:5]):
+        assert rel_max(a.cpu(), b.cpu()) < 1e-5
+    # rays outside the range are left untouched
+    img2 = torch.full_like(full, -7.0)
+    r.forward(*tens, cs, ro._settings_march(settings_for(ro, sc, sc.cameras[0]), cs, rows=(3, 4)), out=img2)
+    assert (img2[:3 * 16] == -7.0).all() and (img2[4 * 16:] == -7.0).all() and torch.equal(img2[48:64], full[48:64])
+
+
+def test_unhit_and_subthreshold_gaussians_get_zero_gradient(ro):
+    sc = make_scene("small_static")
+    sc.densities[::7] = 0.05
+    sc.positions[3] = torch.tensor([50.0, 50.0, 50.0])          # far outside the view
+    r, tens, cs, rgb, _, _ = render(ro, sc)
+    dl = loss_gradient(rgb.cpu().double(), rgb.shape[0])
+    grads = backward(ro, r, sc, tens, cs, rgb, dl)
+    idx = torch.arange(0, sc.n, 7).tolist() + [3]
+    for gten in grads[:5]:
+        assert torch.isfinite(gten).all()
+        assert gten[idx].abs().sum() == 0
+
+
+def test_degenerate_inputs(ro):
+    dev = torch.device("cuda")
+    # no Gaussians: background only, backward is a no-op
+    sc = scenes.tiny_scene(n=0, width=4, height=4, white_background=True)
+    r, tens, cs, rgb, alpha, _ = render(ro, sc)
+    assert (rgb == 1).all() and (alpha == 0).all()
+    backward(ro, r, sc, tens, cs, rgb, torch.zeros(16, 3))
+    # one Gaussian, and non-unit quaternions, against the oracle
+    from oracle import oracle
+    for n in (1, 40):
+        sc = scenes.tiny_scene(n=n, width=8, height=8, log_scale_mean=-1.5, seed=5)
+        sc.quaternions *= 1.1
+        ref, _ = oracle.render_forward(*sc.tensors(), sc.cameras[0], sc.march)
+        _, _, _, rgb, _, _ = render(ro, sc)
+        ok = ref.margin > MARGIN
+        assert (rgb.cpu().double() - ref.rgb).abs().max(dim=1).values[ok].max() <= RGB_TOL
+
+
+def test_hit_cap_truncates_and_is_counted(ro):
+    sc = scenes.tiny_scene(n=600, width=8, height=8, log_scale_mean=-1.6, seed=6, max_prim_slice=8)
+    r = ro.get_renderer()
+    r.reset_counters()
+    _, _, _, rgb, _, _ = render(ro, sc, flags=_lib.FLAG_COUNT_WORK)
+    c = r.read_counters()
+    assert c["overflow_slabs"] > 0 and c["hits"] <= 8 * c["slabs_hit"]
+    assert torch.isfinite(rgb).all()
+
+
+def test_keys_and_curves_do_not_change_the_image_beyond_rounding(ro):
+    sc = make_scene("small_static")
+    imgs = []
+    for curve in (_lib.CURVE_MORTON, _lib.CURVE_HILBERT):
+        for bits in (10, 20):
+            imgs.append(render(ro, sc, curve=curve, bits=bits)[3].clone())
+    for im in imgs[1:]:
+        assert (im - imgs[0]).abs().max() < 5e-6          # summation order follows the sort order
+
+
+def test_c_abi_rejects_bad_arguments(ro):
+    sc = make_scene("small_deg0")
+    r, tens, cs, rgb, _, _ = render(ro, sc)
+    st = settings_for(ro, sc, sc.cameras[0])
+    with pytest.raises(_lib.RgxError) as e:
+        r.forward(*tens, cs, ro._settings_march(st, cs, rows=(0, 999)))
+    assert e.value.code == _lib.RGX_E_INVALID
+    bad = ro.RenderOptixSettings(None, False, None, None, None, None, None, 0.0, False, sc.cameras[0], 16, 0)
+    with pytest.raises(_lib.RgxError):
+        r.forward(*tens, cs, ro._settings_march(bad, cs))
+    other = scenes.tiny_scene(n=10, width=4, height=4)
+    t2 = [t.cuda() for t in other.tensors()]
+    with pytest.raises(_lib.RgxError) as e:
+        r.forward(*t2, cs, ro._settings_march(st, cs))          # built for a different Gaussian count
+    assert e.value.code == _lib.RGX_E_NOT_BUILT
