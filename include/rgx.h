@@ -121,6 +121,15 @@ typedef struct rgx_counters {
     uint64_t window_retries;/* tiled march: candidate searches repeated with a shallower window */
     uint64_t fallback_windows;/* tiled march: windows advanced by per-ray searches because the candidates did not fit */
     uint64_t candidates;    /* tiled march: candidate-list entries summed over windows */
+    /* tiled forward march: warp-cycles spent per phase (clock64 differences summed over warps) */
+    uint64_t cycles_window;   /* opening windows: hierarchy sweep, scans, barriers inside it */
+    uint64_t cycles_seek;     /* closest-hit scans of the candidate list */
+    uint64_t cycles_search;   /* slab queries: candidate filtering, exact tests, staging */
+    uint64_t cycles_eval;     /* per-sample evaluation of staged Gaussians */
+    uint64_t cycles_composite;/* compositing and ray bookkeeping */
+    uint64_t cycles_wait;     /* waiting for the other warps of the tile at the end of a window */
+    uint64_t cycles_total;    /* whole kernel, per warp */
+    uint64_t reserved;
 } rgx_counters;
 
 /* Replaces: ox.DeviceContext / module / pipeline creation (optix_utils.py:154-210). */

@@ -44,7 +44,9 @@ class Counters(C.Structure):
     _fields_ = [(k, C.c_uint64) for k in ("rays", "slabs", "slabs_hit", "closest_queries", "hits", "pairs_inside",
                                           "overflow_slabs", "node_tests", "prim_tests", "ellipsoid_tests",
                                           "stack_overflows", "hits_hash", "windows", "window_retries",
-                                          "fallback_windows", "candidates")]
+                                          "fallback_windows", "candidates", "cycles_window", "cycles_seek",
+                                          "cycles_search", "cycles_eval", "cycles_composite", "cycles_wait",
+                                          "cycles_total", "reserved")]
 
     def as_dict(self):
         return {k: int(getattr(self, k)) for k, _ in self._fields_}

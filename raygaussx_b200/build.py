@@ -36,6 +36,7 @@ def needs_build():
 
 
 def build(force=False, verbose=False, extra=()):
+    extra = tuple(extra) + tuple(os.environ.get("RGX_NVCC_FLAGS", "").split())
     """Compile every .cu of the package into librgx.so.  Returns the library path."""
     if not force and not needs_build():
         return LIB

@@ -476,15 +476,19 @@ __device__ __forceinline__ int slab_sums(const MarchLaunch& L, const rgx_march& 
         nhit += n;
         __syncwarp();
         if (nstage > kStage - kFan) {
+            long long c_a = COUNT ? clock64() : 0;
             eval_forward<COUNT>(ws, nstage, tau, s, c0, c1, c2, tl);
             nstage = 0;
             __syncwarp();
+            if (COUNT) tl.v[C_CYC_EVAL] += clock64() - c_a;
         }
         return !ovf;
     });
     if (nstage > 0) {
+        long long c_a = COUNT ? clock64() : 0;
         eval_forward<COUNT>(ws, nstage, tau, s, c0, c1, c2, tl);
         __syncwarp();
+        if (COUNT) tl.v[C_CYC_EVAL] += clock64() - c_a;
     }
     overflow = ovf;
     return nhit;

@@ -1,6 +1,6 @@
 // Tiled forward and backward ray march: the default path.
 //
-// A CTA owns an 8x8 pixel tile.  All rays of a tile start at the eye and stay
+// A CTA owns a 16x16 pixel tile.  All rays of a tile start at the eye and stay
 // inside a thin pyramid, so instead of searching the hierarchy once per ray and
 // per slab, the CTA searches it once per *depth window*: all eight warps sweep
 // the hierarchy level by level with the tile's pyramid, cut to the window's
@@ -8,7 +8,7 @@
 // Every ray of the tile then marches the slabs that lie inside the window against
 // that list -- one warp per ray, lanes = samples, exactly as in the per-ray
 // kernels -- and the CTA moves on to the next window.  The search cost is thus
-// shared by 64 rays and several slabs.
+// shared by 256 rays and several slabs.
 //
 // The candidate list is a superset of what any ray of the tile can hit inside the
 // window; the per-ray test that decides a hit is the same as in the per-ray and
@@ -20,11 +20,19 @@
 // cuda_train/backward/gaussians_aabb.cu:209-497 (see march_common.cuh).
 #include "march_common.cuh"
 
+#ifndef RGX_TILE_X
+#define RGX_TILE_X 16
+#endif
+#ifndef RGX_TILE_Y
+#define RGX_TILE_Y 16
+#endif
+
 namespace rgx {
 
 namespace {
 
-constexpr int kRays = kTile * kTile;
+constexpr int kTileX = RGX_TILE_X, kTileY = RGX_TILE_Y;   // pixels per CTA tile
+constexpr int kRays = kTileX * kTileY;
 constexpr int kCand = 2048;       // candidate Gaussians per window
 constexpr int kFront = 512;       // hierarchy nodes per level per window
 constexpr int kMaxWindows = 1 << 20;
@@ -305,15 +313,15 @@ __device__ __forceinline__ bool tile_rays_begin(const MarchLaunch& L, TileShared
                                                 int& py0) {
     const int tid = threadIdx.x;
     const int W = L.cam.width;
-    px0 = tile_x * kTile;
-    py0 = L.m.row_begin + tile_y * kTile;
-    const int px1 = min(px0 + kTile, W) - 1, py1 = min(py0 + kTile, L.m.row_end) - 1;
+    px0 = tile_x * kTileX;
+    py0 = L.m.row_begin + tile_y * kTileY;
+    const int px1 = min(px0 + kTileX, W) - 1, py1 = min(py0 + kTileY, L.m.row_end) - 1;
     if (tid == 0) {
         tile_pyramid(L.cam, px0, px1, py0, py1, sh);
         sh.mult = 2;
     }
-    if (tid < kRays) {
-        const int px = px0 + (tid & (kTile - 1)), py = py0 + (tid >> 3);
+    for (int ray = tid; ray < kRays; ray += kThreads) {
+        const int px = px0 + ray % kTileX, py = py0 + ray / kTileX;
         int mode = M_DONE;
         float tenter = 0.f, texit = 0.f;
         if (px < W && py < L.m.row_end) {
@@ -323,13 +331,13 @@ __device__ __forceinline__ bool tile_rays_begin(const MarchLaunch& L, TileShared
             clip_scene(box, r, tenter, texit);
             mode = (L.g.n > 0 && tenter <= texit) ? M_SEEK_FIRST : M_DONE;   // an empty first query is a miss
         }
-        sh.mode[tid] = mode;
-        sh.t[tid] = tenter;
-        sh.tenter[tid] = tenter;
-        sh.texit[tid] = texit;
-        sh.T[tid] = 1.0f;
-        sh.Cr[tid] = sh.Cg[tid] = sh.Cb[tid] = sh.depth[tid] = sh.D[tid] = 0.f;
-        sh.slab_index[tid] = 0;
+        sh.mode[ray] = mode;
+        sh.t[ray] = tenter;
+        sh.tenter[ray] = tenter;
+        sh.texit[ray] = texit;
+        sh.T[ray] = 1.0f;
+        sh.Cr[ray] = sh.Cg[ray] = sh.Cb[ray] = sh.depth[ray] = sh.D[ray] = 0.f;
+        sh.slab_index[ray] = 0;
     }
     __syncthreads();
     return true;
@@ -347,14 +355,15 @@ __device__ __forceinline__ bool window_begin(const MarchLaunch& L, TileShared& s
         sh.next_ray = 0;
     }
     __syncthreads();
-    if (tid < kRays && sh.mode[tid] != M_DONE) {
-        float t = sh.t[tid];
-        float T = sh.mode[tid] == M_MARCH ? sh.T[tid] : 1.0f;
+    for (int ray = tid; ray < kRays; ray += kThreads) {
+        if (sh.mode[ray] == M_DONE) continue;
+        float t = sh.t[ray];
+        float T = sh.mode[ray] == M_MARCH ? sh.T[ray] : 1.0f;
         SlabPlan p = plan_slab(L.m, t, T, t, INFINITY);
         atomicMin(&sh.lo_bits, __float_as_uint(fmaxf(t, 0.f)));
         atomicMax(&sh.slab_bits, __float_as_uint(p.slab));
         atomicAdd(&sh.n_active, 1);
-        if (sh.mode[tid] == M_MARCH) atomicAdd(&sh.n_march, 1);
+        if (sh.mode[ray] == M_MARCH) atomicAdd(&sh.n_march, 1);
     }
     __syncthreads();
     return sh.n_active > 0;
@@ -368,7 +377,7 @@ __global__ void __launch_bounds__(kThreads) march_forward_tiled_kernel(const __g
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     WarpShared& ws = sh.ws[warp];
     const int W = L.cam.width;
-    const int tiles_x = (W + kTile - 1) / kTile;
+    const int tiles_x = (W + kTileX - 1) / kTileX;
     const int tile_x = blockIdx.x % tiles_x, tile_y = blockIdx.x / tiles_x;
     const float eps = L.m.transmittance_eps;
     const float bg = L.m.white_background ? 1.0f : 0.0f;
@@ -377,14 +386,18 @@ __global__ void __launch_bounds__(kThreads) march_forward_tiled_kernel(const __g
 #pragma unroll
     for (int i = 0; i < C_NUM; ++i) tl.v[i] = 0;
     int px0, py0;
+    const long long c_k0 = COUNT ? clock64() : 0;
     tile_rays_begin(L, sh, tile_x, tile_y, px0, py0);
 
     for (int win = 0; win < kMaxWindows; ++win) {
         if (!window_begin(L, sh)) break;
+        const long long c_w0 = COUNT ? clock64() : 0;
         const bool something_left = open_window<COUNT>(L, sh, eye, tl);
         const bool overflow = something_left && sh.overflow != 0;
+        if (COUNT) tl.v[C_CYC_WINDOW] += clock64() - c_w0;
         if (COUNT && warp == 0) {       // tallies are per warp: every lane keeps the same value
             tl.v[C_WINDOWS] += 1;
+            tl.v[C_RESERVED] += sh.n_active;
             if (overflow) tl.v[sh.mult > 1 ? C_RETRIES : C_FALLBACKS] += 1;
             else if (something_left) tl.v[C_CANDS] += sh.n_cand;
         }
@@ -406,7 +419,7 @@ __global__ void __launch_bounds__(kThreads) march_forward_tiled_kernel(const __g
             if (ray >= kRays) break;
             int mode = sh.mode[ray];
             if (mode == M_DONE) continue;
-            const int px = px0 + (ray & (kTile - 1)), py = py0 + (ray >> 3);
+            const int px = px0 + ray % kTileX, py = py0 + ray / kTileX;
             const int ray_id = py * W + px;
             Ray r;
             make_ray(L.cam, px, py, r);
@@ -426,11 +439,16 @@ __global__ void __launch_bounds__(kThreads) march_forward_tiled_kernel(const __g
                             found = search_closest<COUNT, false>(L, r, t, texit, ws, lane, tl);
                             if (!(found < INFINITY)) { mode = M_DONE; break; }
                         } else {
+                            const long long c_s0 = COUNT ? clock64() : 0;
                             found = closest_in_list<COUNT>(L, r, t, texit, cl, lane, tl);
-                            if (!(found <= w_hi)) {  // the list is only complete up to w_hi
-                                t = fmaxf(t, w_hi);
-                                break;
+                            if (!(found <= w_hi)) {
+                                // The list is only complete up to w_hi and this ray's next hit lies beyond it:
+                                // look it up with a search of its own instead of trailing the windows through
+                                // what may be a long stretch of empty space.
+                                found = search_closest<COUNT, false>(L, r, t, texit, ws, lane, tl);
+                                if (!(found < INFINITY)) { mode = M_DONE; break; }
                             }
+                            if (COUNT) tl.v[C_CYC_SEEK] += clock64() - c_s0;
                         }
                         if (COUNT) tl.v[C_CLOSEST] += 1;
                         if (mode == M_SEEK_FIRST) {
@@ -455,11 +473,15 @@ __global__ void __launch_bounds__(kThreads) march_forward_tiled_kernel(const __g
                         const float tau = __fmul_rn((float)lane + 0.5f, p.dt);
                         float s, cr, cg, cb;
                         bool ovf;
+                        const long long c_q0 = COUNT ? clock64() : 0;
+                        const unsigned long long ev0 = tl.v[C_CYC_EVAL];
                         int nhit = slab_sums<COUNT, false>(L, L.m, t, tau, ray_id, slab_index, make_float3(0.f, 0.f, 0.f),
                                                            ws, lane, tl, [&](auto&& leaf) {
                             if (overflow) search_all<COUNT, false>(L, r, p.tmin, p.tmax, ws, lane, tl, leaf);
                             else search_list<COUNT>(L, r, p.tmin, p.tmax, cl, lane, tl, leaf);
                         }, s, cr, cg, cb, ovf);
+                        const long long c_q1 = COUNT ? clock64() : 0;
+                        if (COUNT) tl.v[C_CYC_SEARCH] += (c_q1 - c_q0) - (tl.v[C_CYC_EVAL] - ev0);
                         if (COUNT) { tl.v[C_HITS] += nhit; tl.v[C_OVF] += ovf ? 1 : 0; }
                         if (nhit == 0) {                                              // :297-319
                             t = __fadd_rn(t, p.slab);
@@ -469,6 +491,7 @@ __global__ void __launch_bounds__(kThreads) march_forward_tiled_kernel(const __g
                         if (COUNT) tl.v[C_SLABS_HIT] += 1;
                         composite_forward(p, t, tau, eps, lane, s, cr, cg, cb, L.depth != nullptr, st);
                         t = __fadd_rn(t, p.slab);                                     // :324
+                        if (COUNT) tl.v[C_CYC_COMP] += clock64() - c_q1;
                     }
                 }
             }
@@ -477,7 +500,9 @@ __global__ void __launch_bounds__(kThreads) march_forward_tiled_kernel(const __g
                 sh.T[ray] = st.T; sh.Cr[ray] = st.Cr; sh.Cg[ray] = st.Cg; sh.Cb[ray] = st.Cb; sh.depth[ray] = st.depth;
             }
         }
+        const long long c_b0 = COUNT ? clock64() : 0;
         __syncthreads();
+        if (COUNT) tl.v[C_CYC_WAIT] += clock64() - c_b0;
         if (tid == 0) {        // adapt the window depth to the candidate density
             // deeper windows pay off when few rays are left to scan the list
             const int na = sh.n_active;
@@ -488,20 +513,23 @@ __global__ void __launch_bounds__(kThreads) march_forward_tiled_kernel(const __g
         }
         __syncthreads();
     }
-    if (tid < kRays) {                                                                 // :326-339
-        const int px = px0 + (tid & (kTile - 1)), py = py0 + (tid >> 3);
+    for (int ray = tid; ray < kRays; ray += kThreads) {                                // :326-339
+        const int px = px0 + ray % kTileX, py = py0 + ray / kTileX;
         if (px < W && py < L.m.row_end) {
             const size_t ray_id = (size_t)py * W + px;
-            const float T = sh.T[tid];
-            L.rgb[3 * ray_id] = fmaf(T, bg, sh.Cr[tid]);
-            L.rgb[3 * ray_id + 1] = fmaf(T, bg, sh.Cg[tid]);
-            L.rgb[3 * ray_id + 2] = fmaf(T, bg, sh.Cb[tid]);
+            const float T = sh.T[ray];
+            L.rgb[3 * ray_id] = fmaf(T, bg, sh.Cr[ray]);
+            L.rgb[3 * ray_id + 1] = fmaf(T, bg, sh.Cg[ray]);
+            L.rgb[3 * ray_id + 2] = fmaf(T, bg, sh.Cb[ray]);
             if (L.alpha) L.alpha[ray_id] = 1.0f - T;
-            if (L.depth) L.depth[ray_id] = sh.depth[tid];
+            if (L.depth) L.depth[ray_id] = sh.depth[ray];
             if (COUNT) atomicAdd(&L.counters->v[C_RAYS], 1ull);
         }
     }
-    if (COUNT) flush_tally(L, tl, lane);
+    if (COUNT) {
+        tl.v[C_CYC_TOTAL] += clock64() - c_k0;
+        flush_tally(L, tl, lane);
+    }
 }
 
 // ---------------------------------------------------------------- backward
@@ -511,7 +539,7 @@ __global__ void __launch_bounds__(kThreads) march_backward_tiled_kernel(const __
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     WarpShared& ws = sh.ws[warp];
     const int W = L.cam.width;
-    const int tiles_x = (W + kTile - 1) / kTile;
+    const int tiles_x = (W + kTileX - 1) / kTileX;
     const int tile_x = blockIdx.x % tiles_x, tile_y = blockIdx.x / tiles_x;
     const float eps = L.m.transmittance_eps;
     const float3 eye = make_float3(L.cam.eye[0], L.cam.eye[1], L.cam.eye[2]);
@@ -520,10 +548,11 @@ __global__ void __launch_bounds__(kThreads) march_backward_tiled_kernel(const __
     for (int i = 0; i < C_NUM; ++i) tl.v[i] = 0;
     int px0, py0;
     tile_rays_begin(L, sh, tile_x, tile_y, px0, py0);
-    if (tid < kRays && sh.mode[tid] != M_DONE) {
-        const int px = px0 + (tid & (kTile - 1)), py = py0 + (tid >> 3);
+    for (int ray = tid; ray < kRays; ray += kThreads) {
+        if (sh.mode[ray] == M_DONE) continue;
+        const int px = px0 + ray % kTileX, py = py0 + ray / kTileX;
         const size_t ray_id = (size_t)py * W + px;
-        sh.D[tid] = fmaf(L.dl_drgb[3 * ray_id], L.rgb_in[3 * ray_id],
+        sh.D[ray] = fmaf(L.dl_drgb[3 * ray_id], L.rgb_in[3 * ray_id],
                          fmaf(L.dl_drgb[3 * ray_id + 1], L.rgb_in[3 * ray_id + 1],
                               __fmul_rn(L.dl_drgb[3 * ray_id + 2], L.rgb_in[3 * ray_id + 2])));
     }
@@ -550,7 +579,7 @@ __global__ void __launch_bounds__(kThreads) march_backward_tiled_kernel(const __
             if (ray >= kRays) break;
             int mode = sh.mode[ray];
             if (mode == M_DONE) continue;
-            const int px = px0 + (ray & (kTile - 1)), py = py0 + (ray >> 3);
+            const int px = px0 + ray % kTileX, py = py0 + ray / kTileX;
             const int ray_id = py * W + px;
             Ray r;
             make_ray(L.cam, px, py, r);
@@ -572,7 +601,10 @@ __global__ void __launch_bounds__(kThreads) march_backward_tiled_kernel(const __
                             if (!(found < INFINITY)) { mode = M_DONE; break; }
                         } else {
                             found = closest_in_list<false>(L, r, t, texit, cl, lane, tl);
-                            if (!(found <= w_hi)) { t = fmaxf(t, w_hi); break; }
+                            if (!(found <= w_hi)) {
+                                found = search_closest<false, false>(L, r, t, texit, ws, lane, tl);
+                                if (!(found < INFINITY)) { mode = M_DONE; break; }
+                            }
                         }
                         if (mode == M_SEEK_FIRST) {
                             if (!(found < texit)) { mode = M_DONE; break; }
@@ -631,7 +663,7 @@ __global__ void __launch_bounds__(kThreads) march_backward_tiled_kernel(const __
 int tiled_grid(const MarchLaunch& m) {
     int rows = m.m.row_end - m.m.row_begin;
     if (rows <= 0 || m.cam.width <= 0) return 0;
-    return ((m.cam.width + kTile - 1) / kTile) * ((rows + kTile - 1) / kTile);
+    return ((m.cam.width + kTileX - 1) / kTileX) * ((rows + kTileY - 1) / kTileY);
 }
 
 }  // namespace

@@ -43,10 +43,11 @@ struct SortedGaussians {
 };
 
 struct DeviceCounters {   // mirrors rgx_counters
-    unsigned long long v[16];
+    unsigned long long v[24];
 };
 enum { C_RAYS, C_SLABS, C_SLABS_HIT, C_CLOSEST, C_HITS, C_PAIRS, C_OVF, C_NODE_TESTS, C_PRIM_TESTS, C_ELL_TESTS,
-       C_STACK_OVF, C_HASH, C_WINDOWS, C_RETRIES, C_FALLBACKS, C_CANDS, C_NUM };
+       C_STACK_OVF, C_HASH, C_WINDOWS, C_RETRIES, C_FALLBACKS, C_CANDS, C_CYC_WINDOW, C_CYC_SEEK, C_CYC_SEARCH,
+       C_CYC_EVAL, C_CYC_COMP, C_CYC_WAIT, C_CYC_TOTAL, C_RESERVED, C_NUM };
 
 struct SceneBox {         // written by the build, read by the march kernels
     float lo[3];

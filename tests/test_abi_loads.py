@@ -31,7 +31,7 @@ def test_struct_layouts_match_the_header():
     assert ctypes.sizeof(_lib.Camera) == (3 * 4 + 2 + 2) * 4 + 2 * 4
     assert ctypes.sizeof(_lib.March) == 8 * 4
     assert ctypes.sizeof(_lib.Grads) == 8 * 8
-    assert ctypes.sizeof(_lib.Counters) == 16 * 8
+    assert ctypes.sizeof(_lib.Counters) == 24 * 8
 
 
 def test_error_paths_without_a_gpu():
