@@ -1,6 +1,6 @@
 // Tiled forward and backward ray march: the default path.
 //
-// A CTA owns a 16x16 pixel tile.  All rays of a tile start at the eye and stay
+// A CTA owns an 8x8 pixel tile (RGX_TILE_X x RGX_TILE_Y).  All rays of a tile start at the eye and stay
 // inside a thin pyramid, so instead of searching the hierarchy once per ray and
 // per slab, the CTA searches it once per *depth window*: all eight warps sweep
 // the hierarchy level by level with the tile's pyramid, cut to the window's
@@ -8,7 +8,7 @@
 // Every ray of the tile then marches the slabs that lie inside the window against
 // that list -- one warp per ray, lanes = samples, exactly as in the per-ray
 // kernels -- and the CTA moves on to the next window.  The search cost is thus
-// shared by 256 rays and several slabs.
+// shared by 64 rays and several slabs.
 //
 // The candidate list is a superset of what any ray of the tile can hit inside the
 // window; the per-ray test that decides a hit is the same as in the per-ray and
@@ -21,10 +21,10 @@
 #include "march_common.cuh"
 
 #ifndef RGX_TILE_X
-#define RGX_TILE_X 16
+#define RGX_TILE_X 8
 #endif
 #ifndef RGX_TILE_Y
-#define RGX_TILE_Y 16
+#define RGX_TILE_Y 8
 #endif
 
 namespace rgx {
