@@ -188,6 +188,22 @@ RGX_API int rgx_set_profiling(rgx_ctx* ctx, int enable);
 RGX_API int rgx_read_kernel_times(rgx_ctx* ctx, float* forward_ms, int* forward_launches, float* backward_ms,
                                   int* backward_launches);
 
+/* Forward render without any allocation (no counterpart in the reference, which
+ * allocates freely through cupy).  For callers that cannot call cudaMalloc when
+ * they need a frame -- a viewer thread beside a trainer whose caching allocator
+ * owns the device memory, a plug-in in a process that forbids allocations after
+ * start-up, a latency path that cannot afford an allocation's implicit device
+ * synchronisation.  Does what rgx_build + rgx_forward do (same kernels, same
+ * results) with all scratch in a fixed 8 MiB array inside the library image, so it
+ * needs no context and calls neither cudaMalloc nor cudaFree nor any allocating
+ * library routine.  Limit: scene->n <= 32768, else RGX_E_TOO_LARGE;
+ * RGX_FLAG_COUNT_WORK is rejected.  The first call on a device resolves the
+ * array's device address (cudaGetSymbolAddress) and should come before any stream
+ * capture.  All calls on a device share the array: calls whose GPU work overlaps
+ * race; serialise them (same stream, or an event between them). */
+RGX_API int rgx_forward_static(int device, const rgx_scene* scene, const rgx_camera* cam, const rgx_march* march,
+                               float sigma_threshold, float* rgb, float* alpha, float* depth, rgx_stream stream);
+
 /* Bytes of device memory currently held by the context's workspace. */
 RGX_API size_t rgx_workspace_bytes(const rgx_ctx* ctx);
 

@@ -67,6 +67,8 @@ SYMBOLS = {
     "rgx_reset_counters": (C.c_int, [C.c_void_p, C.c_void_p]),
     "rgx_read_counters": (C.c_int, [C.c_void_p, C.POINTER(Counters), C.c_void_p]),
     "rgx_workspace_bytes": (C.c_size_t, [C.c_void_p]),
+    "rgx_forward_static": (C.c_int, [C.c_int, C.POINTER(Scene), C.POINTER(Camera), C.POINTER(March), C.c_float, _fp, _fp,
+                                     _fp, C.c_void_p]),
     "rgx_set_profiling": (C.c_int, [C.c_void_p, C.c_int]),
     "rgx_read_kernel_times": (C.c_int, [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_int), C.POINTER(C.c_float),
                                         C.POINTER(C.c_int)]),
