@@ -34,6 +34,28 @@ struct rgx_ctx {
     int n = 0, n_pad = 0;
     float sigma_threshold = 0.1f;
     Hierarchy hier{};
+    unsigned long long build_id = 0;   // bumped by every rgx_build
+    // per-view tile lists (binning.cu)
+    int bin_n_pad = 0, bin_tiles_cap = 0;
+    size_t bin_pair_cap = 0, bin_ent_cap = 0, bin_cub_cap = 0;
+    int *bin_counts = nullptr, *bin_offsets = nullptr;
+    uint2* bin_rect = nullptr;
+    float2* bin_depth = nullptr;
+    uint64_t *bin_keys_in = nullptr, *bin_keys_out = nullptr;
+    uint32_t *bin_vals_in = nullptr, *bin_vals_out = nullptr;
+    int *tile_first = nullptr, *tile_last = nullptr, *tile_cnt = nullptr, *tile_pcnt = nullptr, *tile_pbegin = nullptr;
+    int* ent_id = nullptr;
+    float2 *ent_range = nullptr, *ent_blk = nullptr;
+    unsigned char* bin_cub = nullptr;
+    int* bin_total_dev = nullptr;
+    int* bin_total_host = nullptr;      // pinned
+    // what the current lists were made for
+    int last_pairs = 0;
+    bool lists_valid = false;
+    unsigned long long lists_build_id = 0;
+    rgx_camera lists_cam{};
+    int lists_row_begin = 0, lists_row_end = 0;
+    TileLists lists{};
     // optional kernel timing
     bool profiling = false;
     struct Timed { cudaEvent_t a, b; int kind; };
@@ -216,9 +238,13 @@ void rgx_destroy(rgx_ctx* ctx) {
     cudaSetDevice(ctx->device);
     void* ptrs[] = {ctx->keys_in, ctx->keys_out, ctx->vals_in, ctx->vals_out, ctx->bx, ctx->by, ctx->bz, ctx->g0, ctx->g1,
                     ctx->g2, ctx->quat, ctx->sdens, ctx->rgba, ctx->grad_rows, ctx->hk, ctx->refit_counters,
-                    ctx->cub_temp, ctx->bounds, ctx->box, ctx->counters};
+                    ctx->cub_temp, ctx->bounds, ctx->box, ctx->counters, ctx->bin_counts, ctx->bin_offsets, ctx->bin_rect,
+                    ctx->bin_depth, ctx->bin_keys_in, ctx->bin_keys_out, ctx->bin_vals_in, ctx->bin_vals_out,
+                    ctx->tile_first, ctx->tile_last, ctx->tile_cnt, ctx->tile_pcnt, ctx->tile_pbegin, ctx->ent_id,
+                    ctx->ent_range, ctx->ent_blk, ctx->bin_cub, ctx->bin_total_dev};
     for (void* p : ptrs)
         if (p) cudaFree(p);
+    if (ctx->bin_total_host) cudaFreeHost(ctx->bin_total_host);
     for (auto* v : {&ctx->timed, &ctx->spare})
         for (auto& t : *v) { cudaEventDestroy(t.a); cudaEventDestroy(t.b); }
     delete ctx;
@@ -242,6 +268,7 @@ int rgx_build(rgx_ctx* ctx, const rgx_scene* scene, float sigma_threshold, int m
     Levels lv = plan_levels(n > 0 ? n : 1);
     if ((rc = ensure_workspace(ctx, n_pad > 0 ? n_pad : kFan, lv.total))) return rc;
     ctx->built = false;
+    ctx->build_id++;
     ctx->n = n;
     ctx->n_pad = n_pad;
     ctx->sigma_threshold = sigma_threshold;
@@ -275,6 +302,108 @@ int rgx_build(rgx_ctx* ctx, const rgx_scene* scene, float sigma_threshold, int m
     return RGX_OK;
 }
 
+// Dual basis of the camera axes (rows u*, v*, w* with u*.u = 1, u*.v = 0, ...), in double.
+static bool camera_dual(const rgx_camera& c, float dual[3][3]) {
+    const double u[3] = {c.u[0], c.u[1], c.u[2]}, v[3] = {c.v[0], c.v[1], c.v[2]}, w[3] = {c.w[0], c.w[1], c.w[2]};
+    auto cross = [](const double* a, const double* b, double* o) {
+        o[0] = a[1] * b[2] - a[2] * b[1]; o[1] = a[2] * b[0] - a[0] * b[2]; o[2] = a[0] * b[1] - a[1] * b[0];
+    };
+    double vw[3], wu[3], uv[3];
+    cross(v, w, vw); cross(w, u, wu); cross(u, v, uv);
+    const double det = u[0] * vw[0] + u[1] * vw[1] + u[2] * vw[2];
+    if (!(det > 1e-12 || det < -1e-12)) return false;
+    for (int k = 0; k < 3; ++k) { dual[0][k] = (float)(vw[k] / det); dual[1][k] = (float)(wu[k] / det); dual[2][k] = (float)(uv[k] / det); }
+    return true;
+}
+
+// Makes ctx->lists valid for this camera and row range (no-op if they already are).
+static int ensure_lists(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, cudaStream_t s) {
+    if (ctx->lists_valid && ctx->lists_build_id == ctx->build_id && ctx->lists_row_begin == m->row_begin &&
+        ctx->lists_row_end == m->row_end && std::memcmp(&ctx->lists_cam, cam, sizeof(rgx_camera)) == 0)
+        return RGX_OK;
+    ctx->lists_valid = false;
+    if (m->row_end <= m->row_begin || ctx->n == 0) return RGX_OK;   // nothing to march
+    cudaError_t e = cudaSuccess;
+    const int tiles_x = (cam->width + kBinTile - 1) / kBinTile;
+    if (tiles_x > 65535) return fail(ctx, RGX_E_TOO_LARGE, "image wider than 65535 tiles");
+    const int ty_first = m->row_begin / kBinTile, ty_last = (m->row_end - 1) / kBinTile;
+    const int tiles_y = ty_last - ty_first + 1;
+    const int ntiles = tiles_x * tiles_y;
+#define RGB_(p, cnt) if ((e = regrow(ctx, ctx->p, (cnt))) != cudaSuccess) return cuda_fail(ctx, e, "tile-list workspace " #p)
+    if (!ctx->bin_total_dev) {
+        RGB_(bin_total_dev, 4);
+        if ((e = cudaMallocHost((void**)&ctx->bin_total_host, 4 * sizeof(int))) != cudaSuccess)
+            return cuda_fail(ctx, e, "pinned scalar");
+    }
+    if (ctx->n_pad > ctx->bin_n_pad) {
+        size_t c = (size_t)ctx->cap_n_pad > (size_t)ctx->n_pad ? ctx->cap_n_pad : ctx->n_pad;
+        RGB_(bin_counts, c); RGB_(bin_offsets, c); RGB_(bin_rect, c); RGB_(bin_depth, c);
+        ctx->bin_n_pad = (int)c;
+    }
+    if (ntiles + 1 > ctx->bin_tiles_cap) {
+        size_t c = (size_t)ntiles + 1 + 64;
+        RGB_(tile_first, c); RGB_(tile_last, c); RGB_(tile_cnt, c); RGB_(tile_pcnt, c); RGB_(tile_pbegin, c);
+        ctx->bin_tiles_cap = (int)c;
+    }
+    auto need_cub = [&](size_t pairs) { return binning_cub_temp_bytes(pairs > 0 ? pairs : 1, ctx->bin_n_pad, ntiles); };
+    if (need_cub(ctx->bin_pair_cap) > ctx->bin_cub_cap) {
+        size_t c = need_cub(ctx->bin_pair_cap);
+        RGB_(bin_cub, c);
+        ctx->bin_cub_cap = c;
+    }
+    BinLaunch b{};
+    b.n = ctx->n; b.n_pad = ctx->n_pad;
+    b.bx = ctx->bx; b.by = ctx->by; b.bz = ctx->bz;
+    b.g0 = ctx->g0; b.quat = ctx->quat; b.sdens = ctx->sdens; b.hk = ctx->hk;
+    b.cam = *cam;
+    if (!camera_dual(*cam, b.dual)) return fail(ctx, RGX_E_INVALID, "camera axes are not linearly independent");
+    b.row_begin = m->row_begin; b.row_end = m->row_end; b.tile = kBinTile;
+    b.tiles_x = tiles_x; b.tiles_y = tiles_y; b.ty_first = ty_first;
+    b.counts = ctx->bin_counts; b.offsets = ctx->bin_offsets; b.rect = ctx->bin_rect; b.depth = ctx->bin_depth;
+    b.cub_temp = ctx->bin_cub; b.cub_bytes = ctx->bin_cub_cap;
+    b.total_dev = ctx->bin_total_dev;
+    if ((e = launch_bin_count(b, s)) != cudaSuccess) return cuda_fail(ctx, e, "tile-list count");
+    // the one host round trip of a view: the sort needs the number of pairs
+    if ((e = cudaMemcpyAsync(ctx->bin_total_host, ctx->bin_total_dev, sizeof(int), cudaMemcpyDeviceToHost, s)) != cudaSuccess ||
+        (e = cudaStreamSynchronize(s)) != cudaSuccess)
+        return cuda_fail(ctx, e, "tile-list count read-back");
+    const int total = ctx->bin_total_host[0];
+    if (total < 0 || total > (1 << 30)) return fail(ctx, RGX_E_TOO_LARGE, "more than 2^30 (tile, Gaussian) pairs in this view");
+    if ((size_t)total > ctx->bin_pair_cap) {
+        size_t c = (size_t)total + (size_t)total / 4 + 1024;
+        RGB_(bin_keys_in, c); RGB_(bin_keys_out, c); RGB_(bin_vals_in, c); RGB_(bin_vals_out, c);
+        ctx->bin_pair_cap = c;
+    }
+    const size_t ent_need = (((size_t)total + 32u * (size_t)ntiles + 31) / 32) * 32 + 32;
+    if (ent_need > ctx->bin_ent_cap) {
+        size_t c = ent_need + ent_need / 4;
+        c = ((c + 31) / 32) * 32;
+        RGB_(ent_id, c); RGB_(ent_range, c); RGB_(ent_blk, c / 32 + 1);
+        ctx->bin_ent_cap = c;
+    }
+    if (need_cub(ctx->bin_pair_cap) > ctx->bin_cub_cap) {
+        size_t c = need_cub(ctx->bin_pair_cap);
+        RGB_(bin_cub, c);
+        ctx->bin_cub_cap = c;
+    }
+#undef RGB_
+    b.keys_in = ctx->bin_keys_in; b.keys_out = ctx->bin_keys_out; b.vals_in = ctx->bin_vals_in; b.vals_out = ctx->bin_vals_out;
+    b.tile_first = ctx->tile_first; b.tile_last = ctx->tile_last; b.tile_cnt = ctx->tile_cnt; b.tile_pcnt = ctx->tile_pcnt;
+    b.tile_pbegin = ctx->tile_pbegin;
+    b.ent_id = ctx->ent_id; b.ent_range = ctx->ent_range; b.blk = ctx->ent_blk;
+    b.cub_temp = ctx->bin_cub; b.cub_bytes = ctx->bin_cub_cap;
+    if ((e = launch_bin_fill(b, total, s)) != cudaSuccess) return cuda_fail(ctx, e, "tile-list fill");
+    ctx->lists.ent_id = ctx->ent_id; ctx->lists.ent_range = ctx->ent_range; ctx->lists.blk = ctx->ent_blk;
+    ctx->lists.tile_pbegin = ctx->tile_pbegin; ctx->lists.tile_cnt = ctx->tile_cnt;
+    ctx->lists.tiles_x = tiles_x; ctx->lists.tiles_y = tiles_y; ctx->lists.ty_first = ty_first;
+    ctx->lists_cam = *cam;
+    ctx->lists_row_begin = m->row_begin; ctx->lists_row_end = m->row_end;
+    ctx->lists_build_id = ctx->build_id;
+    ctx->lists_valid = true;
+    ctx->last_pairs = total;
+    return RGX_OK;
+}
+
 static int prepare_march(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, const rgx_march* march,
                          MarchLaunch& L) {
     int rc = check_scene(ctx, scene, true);
@@ -300,6 +429,10 @@ int rgx_forward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, con
     cudaSetDevice(ctx->device);
     cudaStream_t s = (cudaStream_t)stream;
     if ((rc = run_colors(ctx, scene, cam->eye, s))) return rc;
+    if (!(march->flags & (RGX_FLAG_BRUTE_FORCE | RGX_FLAG_PER_RAY_SEARCH))) {
+        if ((rc = ensure_lists(ctx, cam, march, s))) return rc;
+        L.lists = ctx->lists;
+    }
     L.rgb = rgb; L.alpha = alpha; L.depth = depth;
     cudaError_t e;
     {
@@ -326,6 +459,10 @@ int rgx_backward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, co
     if ((rc = run_colors(ctx, scene, cam->eye, s))) return rc;
     cudaError_t e = cudaMemsetAsync(ctx->grad_rows, 0, sizeof(float4) * 4 * (size_t)ctx->n_pad, s);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "backward memset");
+    if (!(march->flags & (RGX_FLAG_BRUTE_FORCE | RGX_FLAG_PER_RAY_SEARCH))) {
+        if ((rc = ensure_lists(ctx, cam, march, s))) return rc;
+        L.lists = ctx->lists;
+    }
     L.rgb_in = rgb; L.dl_drgb = dL_drgb; L.grad_rows = ctx->grad_rows;
     {
         ScopedTimer timer(ctx, s, 1);

@@ -54,9 +54,43 @@ struct SceneBox {         // written by the build, read by the march kernels
     float hi[3];
 };
 
+constexpr int kBinTile = 16;      // pixels per side of a binning tile
+
+// Per-view, per-tile candidate lists (binning.cu).  Tile t owns entries
+// [tile_pbegin[t], tile_pbegin[t] + roundup32(tile_cnt[t])), sorted by near distance;
+// padding entries have the empty range (+inf, -inf).
+struct TileLists {
+    const int* ent_id;         // sorted slot of the candidate
+    const float2* ent_range;   // (near, far) distance of its box from the eye, conservative
+    const float2* blk;         // per 32 entries: (smallest near, largest far)
+    const int* tile_pbegin;
+    const int* tile_cnt;
+    int tiles_x, tiles_y, ty_first;
+};
+
+struct BinLaunch {
+    int n, n_pad;
+    const float2 *bx, *by, *bz;            // level-0 boxes
+    const float4 *g0, *quat, *sdens;
+    const float* hk;
+    rgx_camera cam;
+    float dual[3][3];                      // dual basis of (u, v, w): rows u*, v*, w*
+    int row_begin, row_end, tile, tiles_x, tiles_y, ty_first;
+    int *counts, *offsets;                 // [n_pad]
+    uint2* rect;                           // [n_pad] tile rectangle (x0 | x1 << 16, y0 | y1 << 16)
+    float2* depth;                         // [n_pad] (near, far)
+    uint64_t *keys_in, *keys_out;          // [pair capacity]
+    uint32_t *vals_in, *vals_out;
+    int *tile_first, *tile_last, *tile_cnt, *tile_pcnt, *tile_pbegin;   // [tiles + 1]
+    int* ent_id; float2* ent_range; float2* blk;
+    void* cub_temp; size_t cub_bytes;
+    int* total_dev;
+};
+
 struct MarchLaunch {
     Hierarchy h;
     SortedGaussians g;
+    TileLists lists;
     rgx_camera cam;
     rgx_march m;
     const SceneBox* box;
@@ -114,6 +148,9 @@ cudaError_t launch_build(const BuildLaunch& b, cudaStream_t s);
 size_t build_cub_temp_bytes(int n_pad);
 cudaError_t launch_colors(const ColorLaunch& c, cudaStream_t s);
 cudaError_t launch_finalize(const FinalizeLaunch& f, cudaStream_t s);
+size_t binning_cub_temp_bytes(size_t pair_cap, int n_pad, int ntiles);
+cudaError_t launch_bin_count(const BinLaunch& b, cudaStream_t s);
+cudaError_t launch_bin_fill(const BinLaunch& b, int total, cudaStream_t s);
 cudaError_t launch_march_forward(const MarchLaunch& m, cudaStream_t s);
 cudaError_t launch_march_backward(const MarchLaunch& m, cudaStream_t s);
 

@@ -6,7 +6,7 @@
 // process that forbids driver allocations after start-up, or code on a latency
 // path where an allocation's implicit device synchronisation is not acceptable.
 // For them this file offers one entry point that does the whole forward --
-// boxes, keys, sort, hierarchy refit, per-view colours, march -- with every byte
+// boxes, keys, sort, hierarchy refit, per-view colours, per-ray march -- with every byte
 // of scratch taken from one fixed array that is part of the library image.
 //
 // The array is a file-scope `static __device__` object.  Its name is only a
@@ -173,6 +173,7 @@ extern "C" RGX_API int rgx_forward_static(int device, const rgx_scene* scene, co
     L.g.n = n; L.g.n_pad = n_pad;
     L.cam = *cam;
     L.m = *march;
+    L.m.flags |= RGX_FLAG_PER_RAY_SEARCH;      // per-view tile lists would need a workspace sized by the view
     L.box = b.box;
     L.counters = nullptr;
     L.rgb = rgb; L.alpha = alpha; L.depth = depth;

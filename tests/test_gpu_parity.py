@@ -99,7 +99,10 @@ def test_search_variants_give_identical_hits_and_images(ro, name):
         assert c["hits_hash"] == base_c["hits_hash"], f"{label}: hit sets differ from the exhaustive search"
         for k in ("rays", "slabs", "slabs_hit", "hits", "pairs_inside", "overflow_slabs"):
             assert c[k] == base_c[k], (label, k)
-        assert torch.equal(rgb, base_rgb), f"{label}: image differs bitwise from the exhaustive search"
+        if label == "per_ray":      # same order of hits as the exhaustive search: same bits
+            assert torch.equal(rgb, base_rgb), f"{label}: image differs bitwise from the exhaustive search"
+        else:                       # tile lists meet the same hits front to back: only the summation order differs
+            assert (rgb - base_rgb).abs().max().item() < 2e-6
     # work counters agree with the oracle's up to the handful of marginal predicates
     assert base_c["slabs"] == pytest.approx(oc["S"], rel=2e-3)
     assert base_c["hits"] == pytest.approx(oc["P"], rel=2e-3)

@@ -45,14 +45,15 @@ def test_full_size_forward_properties(big):
     # white minus black background equals the final transmittance
     white, _, _ = r.forward(*tens, cs, march(ro, sc, cs, white=True))
     assert ((white - rgb) - (1 - alpha)[:, None]).abs().max() < 2e-6
-    # a crop of rows: tiled and per-ray searches agree bitwise; sharded rows equal the whole
+    # a crop of rows: list march and per-ray search agree to rounding; sharded rows equal the whole
     rows = (400, 408)
     lo, hi = rows[0] * cs.width, rows[1] * cs.width
     a = torch.zeros_like(rgb)
     b = torch.zeros_like(rgb)
     r.forward(*tens, cs, march(ro, sc, cs, rows=rows), out=a)
     r.forward(*tens, cs, march(ro, sc, cs, rows=rows, flags=_lib.FLAG_PER_RAY_SEARCH), out=b)
-    assert torch.equal(a[lo:hi], b[lo:hi]) and torch.equal(a[lo:hi], rgb[lo:hi])
+    assert torch.equal(a[lo:hi], rgb[lo:hi])                       # a row shard equals the whole image bit for bit
+    assert (a[lo:hi] - b[lo:hi]).abs().max().item() < 1e-5          # list march vs per-ray search: summation order only
     r.reset_counters()
     r.forward(*tens, cs, march(ro, sc, cs, flags=_lib.FLAG_COUNT_WORK))
     c = r.read_counters()

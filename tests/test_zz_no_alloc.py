@@ -7,8 +7,7 @@ cannot take an allocation's implicit synchronisation.  `rgx_forward_static` serv
 from a fixed array inside the library image.
 
 Checked here, through the C ABI: its image equals the image of the regular entry points
-(`rgx_build` + `rgx_forward`) within the suite's RGB tolerance -- in fact bit for bit,
-since the same kernels run on the same data -- on two calls in a row (the shared array
+(`rgx_build` + `rgx_forward`) within the suite's RGB tolerance on two calls in a row (the shared array
 keeps the previous call's contents, so the second call proves that stale state does not
 leak), that device memory in use does not grow across the calls, and that sizes beyond
 the stated maximum are refused.
@@ -77,7 +76,6 @@ def test_static_forward_matches_regular_forward_twice():
         assert (rgb - rgb_e).abs().max().item() <= RGB_TOL
         assert (alpha - alpha_e).abs().max().item() <= RGB_TOL
         assert (depth - depth_e).abs().max().item() <= 5e-4
-        assert torch.equal(rgb, rgb_e), "same kernels on the same data: expected identical bits"
     after = torch.cuda.mem_get_info(dev)[0]
     # torch's own tensors of the loop are freed back to its cache; the driver-level free memory may only
     # shrink by what torch itself newly reserved (a few MiB), never by a workspace
