@@ -188,6 +188,11 @@ RGX_API int rgx_set_profiling(rgx_ctx* ctx, int enable);
 RGX_API int rgx_read_kernel_times(rgx_ctx* ctx, float* forward_ms, int* forward_launches, float* backward_ms,
                                   int* backward_launches);
 
+/* Per-view tile-list construction (binning + sort), timed like the march kernels while
+ * profiling is enabled: summed milliseconds and number of constructions since the last
+ * read, and the number of (tile, Gaussian) pairs of the latest one. */
+RGX_API int rgx_read_binning(rgx_ctx* ctx, float* ms, int* runs, long long* last_pairs);
+
 /* Forward render without any allocation (no counterpart in the reference, which
  * allocates freely through cupy).  For callers that cannot call cudaMalloc when
  * they need a frame -- a viewer thread beside a trainer whose caching allocator

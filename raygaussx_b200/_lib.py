@@ -70,6 +70,7 @@ SYMBOLS = {
     "rgx_forward_static": (C.c_int, [C.c_int, C.POINTER(Scene), C.POINTER(Camera), C.POINTER(March), C.c_float, _fp, _fp,
                                      _fp, C.c_void_p]),
     "rgx_set_profiling": (C.c_int, [C.c_void_p, C.c_int]),
+    "rgx_read_binning": (C.c_int, [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_int), C.POINTER(C.c_longlong)]),
     "rgx_read_kernel_times": (C.c_int, [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_int), C.POINTER(C.c_float),
                                         C.POINTER(C.c_int)]),
 }

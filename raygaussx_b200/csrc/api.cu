@@ -51,6 +51,8 @@ struct rgx_ctx {
     int* bin_total_host = nullptr;      // pinned
     // what the current lists were made for
     int last_pairs = 0;
+    float binning_ms = 0.f; int binning_runs = 0;
+    float kept_ms[2] = {0.f, 0.f}; int kept_n[2] = {0, 0};
     bool lists_valid = false;
     unsigned long long lists_build_id = 0;
     rgx_camera lists_cam{};
@@ -362,6 +364,7 @@ static int ensure_lists(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m,
     b.counts = ctx->bin_counts; b.offsets = ctx->bin_offsets; b.rect = ctx->bin_rect; b.depth = ctx->bin_depth;
     b.cub_temp = ctx->bin_cub; b.cub_bytes = ctx->bin_cub_cap;
     b.total_dev = ctx->bin_total_dev;
+    ScopedTimer timer(ctx, s, 2);
     if ((e = launch_bin_count(b, s)) != cudaSuccess) return cuda_fail(ctx, e, "tile-list count");
     // the one host round trip of a view: the sort needs the number of pairs
     if ((e = cudaMemcpyAsync(ctx->bin_total_host, ctx->bin_total_dev, sizeof(int), cudaMemcpyDeviceToHost, s)) != cudaSuccess ||
@@ -518,8 +521,8 @@ int rgx_read_kernel_times(rgx_ctx* ctx, float* forward_ms, int* forward_launches
                           int* backward_launches) {
     if (!ctx || !forward_ms || !forward_launches || !backward_ms || !backward_launches) return RGX_E_INVALID;
     cudaSetDevice(ctx->device);
-    float sum[2] = {0.f, 0.f};
-    int cnt[2] = {0, 0};
+    float sum[3] = {0.f, 0.f, 0.f};
+    int cnt[3] = {0, 0, 0};
     for (auto& t : ctx->timed) {
         float ms = 0.f;
         if (cudaEventSynchronize(t.b) == cudaSuccess && cudaEventElapsedTime(&ms, t.a, t.b) == cudaSuccess) {
@@ -529,8 +532,22 @@ int rgx_read_kernel_times(rgx_ctx* ctx, float* forward_ms, int* forward_launches
         ctx->spare.push_back(t);
     }
     ctx->timed.clear();
+    sum[0] += ctx->kept_ms[0]; cnt[0] += ctx->kept_n[0]; sum[1] += ctx->kept_ms[1]; cnt[1] += ctx->kept_n[1];
+    ctx->kept_ms[0] = ctx->kept_ms[1] = 0.f; ctx->kept_n[0] = ctx->kept_n[1] = 0;
     *forward_ms = sum[0]; *forward_launches = cnt[0];
     *backward_ms = sum[1]; *backward_launches = cnt[1];
+    ctx->binning_ms += sum[2]; ctx->binning_runs += cnt[2];
+    return RGX_OK;
+}
+
+int rgx_read_binning(rgx_ctx* ctx, float* ms, int* runs, long long* last_pairs) {
+    if (!ctx || !ms || !runs || !last_pairs) return RGX_E_INVALID;
+    float f, b; int nf, nb;
+    int rc = rgx_read_kernel_times(ctx, &f, &nf, &b, &nb);   // drains the events; forward/backward sums are put back below
+    if (rc) return rc;
+    ctx->kept_ms[0] += f; ctx->kept_n[0] += nf; ctx->kept_ms[1] += b; ctx->kept_n[1] += nb;
+    *ms = ctx->binning_ms; *runs = ctx->binning_runs; *last_pairs = ctx->last_pairs;
+    ctx->binning_ms = 0.f; ctx->binning_runs = 0;
     return RGX_OK;
 }
 

@@ -406,25 +406,60 @@ __device__ __forceinline__ void red_add_v4(float4* addr, float a, float b, float
                  : "memory");
 }
 
-// Pass 2 over `count` staged Gaussians: each lane forms its sample's share of the
-// four per-Gaussian sums, the warp adds them up, and lane j keeps the totals of
-// staged Gaussian j.
+// Sums eight per-lane values over the warp at once: on return every lane holds the
+// warp total of v[(lane >> 2) & 7].  9 shuffles instead of 8 x 5.
+__device__ __forceinline__ float reduce8(const float (&v)[8], int lane) {
+    float a[4], b[2];
+    bool up = (lane & 16) != 0;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+        float recv = __shfl_xor_sync(kFull, up ? v[t] : v[t + 4], 16);
+        a[t] = __fadd_rn(up ? v[t + 4] : v[t], recv);
+    }
+    up = (lane & 8) != 0;
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        float recv = __shfl_xor_sync(kFull, up ? a[t] : a[t + 2], 8);
+        b[t] = __fadd_rn(up ? a[t + 2] : a[t], recv);
+    }
+    up = (lane & 4) != 0;
+    float recv = __shfl_xor_sync(kFull, up ? b[0] : b[1], 4);
+    float c = __fadd_rn(up ? b[1] : b[0], recv);
+    c = __fadd_rn(c, __shfl_xor_sync(kFull, c, 2));
+    c = __fadd_rn(c, __shfl_xor_sync(kFull, c, 1));
+    return c;
+}
+
+// Pass 2 over `count` (<= 32) staged Gaussians: each lane forms its sample's share of
+// the four per-Gaussian sums, the warp adds them up eight Gaussians at a time, and
+// lane j keeps the totals of staged Gaussian j.
 //   recA = (y_c.xyz, hk)  recB = (de.xyz, tbuffer - t_c)  recC = (chat_i, -, -, -)
 __device__ __forceinline__ void eval_backward(const WarpShared& ws, int count, float tau, float beta, float gamma,
                                               int lane, float& o_sb, float& o_n0, float& o_n1, float& o_n2) {
-    for (int j = 0; j < count; ++j) {
-        float4 A = ws.recA[j], B = ws.recB[j], C = ws.recC[j];
-        float tc = __fadd_rn(tau, B.w);
-        float yx = fmaf(tc, B.x, A.x), yy = fmaf(tc, B.y, A.y), yz = fmaf(tc, B.z, A.z);
-        float q = fmaf(yx, yx, fmaf(yy, yy, __fmul_rn(yz, yz)));
-        float e = q < 1.0f ? ex2_approx(__fmul_rn(-A.w, q)) : 0.0f;
-        float ga = __fmul_rn(e, fmaf(C.x, beta, gamma));      // g * (alpha + beta*(chat_i - chat_s))
-        float sb = warp_sum(__fmul_rn(e, beta));
-        float n0 = warp_sum(ga);
-        float g1 = __fmul_rn(ga, tc);
-        float n1 = warp_sum(g1);
-        float n2 = warp_sum(__fmul_rn(g1, tc));
-        if (lane == j) { o_sb = sb; o_n0 = n0; o_n1 = n1; o_n2 = n2; }
+    for (int j0 = 0; j0 < count; j0 += 8) {
+        float vb[8], v0[8], v1[8], v2[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int j = j0 + e;
+            if (j < count) {
+                float4 A = ws.recA[j], B = ws.recB[j], C = ws.recC[j];
+                float tc = __fadd_rn(tau, B.w);
+                float yx = fmaf(tc, B.x, A.x), yy = fmaf(tc, B.y, A.y), yz = fmaf(tc, B.z, A.z);
+                float q = fmaf(yx, yx, fmaf(yy, yy, __fmul_rn(yz, yz)));
+                float ex = q < 1.0f ? ex2_approx(__fmul_rn(-A.w, q)) : 0.0f;
+                float ga = __fmul_rn(ex, fmaf(C.x, beta, gamma));      // g * (alpha + beta*(chat_i - chat_s))
+                float g1 = __fmul_rn(ga, tc);
+                vb[e] = __fmul_rn(ex, beta); v0[e] = ga; v1[e] = g1; v2[e] = __fmul_rn(g1, tc);
+            } else {
+                vb[e] = v0[e] = v1[e] = v2[e] = 0.f;
+            }
+        }
+        const float rb = reduce8(vb, lane), r0 = reduce8(v0, lane), r1 = reduce8(v1, lane), r2 = reduce8(v2, lane);
+        // the totals of staged Gaussian j0 + e sit in lanes 4e .. 4e+3; hand them to lane j0 + e
+        const int src = 4 * ((lane - j0) & 7);
+        const float tb = __shfl_sync(kFull, rb, src), t0 = __shfl_sync(kFull, r0, src), t1 = __shfl_sync(kFull, r1, src),
+                    t2 = __shfl_sync(kFull, r2, src);
+        if (lane >= j0 && lane < j0 + 8) { o_sb = tb; o_n0 = t0; o_n1 = t1; o_n2 = t2; }
     }
 }
 
@@ -441,7 +476,7 @@ template <bool COUNT, bool BWD, class Enum>
 __device__ __forceinline__ int slab_sums(const MarchLaunch& L, const rgx_march& m, float tbuffer, float tau,
                                          int ray_id, int slab_index, float3 dl, WarpShared& ws, int lane, Tally& tl,
                                          Enum&& enumerate, float& s, float& c0, float& c1, float& c2,
-                                         bool& overflow) {
+                                         bool& overflow, int* hit_list = nullptr, int hit_cap = 0) {
     int nstage = 0, nhit = 0;
     bool ovf = false;
     s = c0 = c1 = c2 = 0.f;
@@ -457,6 +492,7 @@ __device__ __forceinline__ int slab_sums(const MarchLaunch& L, const rgx_march& 
         }
         if (take) {
             int slot = nstage + rank;
+            if (hit_list && nhit + rank < hit_cap) hit_list[nhit + rank] = j;    // remembered for the second pass
             float4 c = __ldg(&L.g.rgba[j]);
             ws.recA[slot] = make_float4(fmaf(tbuffer, t.de.x, t.Oe.x), fmaf(tbuffer, t.de.y, t.Oe.y),
                                         fmaf(tbuffer, t.de.z, t.Oe.z), __ldg(&L.g.hk[j]));

@@ -27,6 +27,8 @@ namespace {
 constexpr int kRaysPerTile = kBinTile * kBinTile;
 constexpr int kThreads = kWarps * 32;
 
+constexpr int kHitList = 256;      // hits of a slab remembered between the two passes of the backward
+
 struct ListShared {
     int next_ray;
     int pend[kWarps][2 * kFan];
@@ -239,6 +241,7 @@ __global__ void __launch_bounds__(kThreads) march_forward_lists_kernel(const __g
 // ---------------------------------------------------------------- backward
 __global__ void __launch_bounds__(kThreads) march_backward_lists_kernel(const __grid_constant__ MarchLaunch L) {
     __shared__ ListShared sh;
+    __shared__ int hit_lists[kWarps][kHitList];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     WarpShared& ws = sh.ws[warp];
     int* pend = sh.pend[warp];
@@ -284,8 +287,9 @@ __global__ void __launch_bounds__(kThreads) march_backward_lists_kernel(const __
             auto enumerate = [&](auto&& leaf) { search_tile<false>(L, r, p.tmin, p.tmax, tv, cursor, pend, lane, tl, leaf); };
             float s, dc, u0, u1;
             bool overflow;
+            int* hits = hit_lists[warp];
             int nhit = slab_sums<false, true>(L, L.m, tbuffer, tau, ray_id, slab_index, dl, ws, lane, tl, enumerate, s, dc,
-                                              u0, u1, overflow);
+                                              u0, u1, overflow, hits, kHitList);
             if (nhit == 0) {
                 tbuffer = __fadd_rn(tbuffer, p.slab);
                 float nxt = closest_in_tile<false>(L, r, tbuffer, texit, tv, cursor, pend, lane, tl);
@@ -294,8 +298,22 @@ __global__ void __launch_bounds__(kThreads) march_backward_lists_kernel(const __
                 continue;
             }
             SlabBackTerms bt = slab_back_terms(s, dc, p.dt, T, D, eps, lane);
-            slab_gradients(L, L.m, r, p, tbuffer, tau, dl, bt.beta, bt.gamma, ws, sh.prim_of[warp], lane, enumerate,
-                           [&](int j, const GaussGrad& g) { emit_global(L, dl, j, g); });
+            // pass 2: the hits again -- from the remembered list when it held them all, else by a second query
+            auto emit = [&](int j, const GaussGrad& g) { emit_global(L, dl, j, g); };
+            if (nhit <= kHitList) {
+                __syncwarp();
+                slab_gradients(L, L.m, r, p, tbuffer, tau, dl, bt.beta, bt.gamma, ws, sh.prim_of[warp], lane,
+                               [&](auto&& leaf) {
+                                   for (int base = 0; base < nhit; base += kFan) {
+                                       const bool valid = base + lane < nhit;
+                                       const int j = valid ? hits[base + lane] : 0;
+                                       LeafTest t = test_gaussian(L, r, j, valid, p.tmin, p.tmax, tl, false);
+                                       if (!leaf(t, j)) return;
+                                   }
+                               }, emit);
+            } else {
+                slab_gradients(L, L.m, r, p, tbuffer, tau, dl, bt.beta, bt.gamma, ws, sh.prim_of[warp], lane, enumerate, emit);
+            }
             D = __fadd_rn(D, -bt.d_total);
             T = slab_exit_T(bt.tr, eps);
             tbuffer = __fadd_rn(tbuffer, p.slab);

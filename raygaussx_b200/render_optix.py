@@ -235,6 +235,12 @@ class Renderer:
                                                               C.byref(nb)))
         return dict(forward_ms=f.value, forward_launches=nf.value, backward_ms=b.value, backward_launches=nb.value)
 
+    def read_binning(self) -> dict:
+        """Tile-list construction: summed ms and runs since the last read (profiling on), pairs of the latest view."""
+        ms, runs, pairs = C.c_float(), C.c_int(), C.c_longlong()
+        _lib.check(self._ctx, self._lib.rgx_read_binning(self._ctx, C.byref(ms), C.byref(runs), C.byref(pairs)))
+        return dict(ms=ms.value, runs=runs.value, pairs=pairs.value)
+
     def workspace_bytes(self) -> int:
         return int(self._lib.rgx_workspace_bytes(self._ctx))
 
