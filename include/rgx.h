@@ -86,6 +86,9 @@ enum {
     RGX_FLAG_BRUTE_FORCE = 2,    /* skip the hierarchy: test every Gaussian in every query (validation only) */
     RGX_FLAG_EXACT_SH_GRAD = 4,  /* backward: exact d(basis 9)/dy instead of the reference's term (utils/sh_utils.cu:367) */
     RGX_FLAG_ACCUMULATE = 8,     /* backward: add into the gradient tensors instead of overwriting them */
+    RGX_FLAG_SAVE_HITS = 32,     /* forward: keep, per ray and slab, the Gaussians that were hit (in the context's
+                                    workspace) so that a backward for the same view reads them back instead of
+                                    searching again; the backward falls back to searching where nothing was kept */
     RGX_FLAG_PER_RAY_SEARCH = 16 /* search the hierarchy once per ray and slab instead of once per 8x8 tile and depth
                                     window (same results; the general path, kept for validation) */
 };

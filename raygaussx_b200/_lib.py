@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(_HERE, "librgx.so")
 
 RGX_OK, RGX_E_INVALID, RGX_E_CUDA, RGX_E_NOT_BUILT, RGX_E_TOO_LARGE = 0, -1, -2, -3, -4
 CURVE_MORTON, CURVE_HILBERT = 0, 1
-FLAG_COUNT_WORK, FLAG_BRUTE_FORCE, FLAG_EXACT_SH_GRAD, FLAG_ACCUMULATE, FLAG_PER_RAY_SEARCH = 1, 2, 4, 8, 16
+FLAG_COUNT_WORK, FLAG_BRUTE_FORCE, FLAG_EXACT_SH_GRAD, FLAG_ACCUMULATE, FLAG_PER_RAY_SEARCH, FLAG_SAVE_HITS = 1, 2, 4, 8, 16, 32
 
 _fp = C.c_void_p  # device pointers travel as integers
 

@@ -46,6 +46,9 @@ struct rgx_ctx {
     int *tile_first = nullptr, *tile_last = nullptr, *tile_cnt = nullptr, *tile_pcnt = nullptr, *tile_pbegin = nullptr;
     int* ent_id = nullptr;
     float2 *ent_range = nullptr, *ent_blk = nullptr;
+    float4* tile_dir = nullptr;
+    int* pair_j = nullptr;
+    float* pair_far = nullptr;
     unsigned char* bin_cub = nullptr;
     int* bin_total_dev = nullptr;
     int* bin_total_host = nullptr;      // pinned
@@ -58,6 +61,17 @@ struct rgx_ctx {
     rgx_camera lists_cam{};
     int lists_row_begin = 0, lists_row_end = 0;
     TileLists lists{};
+    // tape of forward hits for the backward (RGX_FLAG_SAVE_HITS)
+    int* tape = nullptr;
+    long long tape_cap = 0;
+    unsigned long long* tape_used = nullptr;
+    unsigned long long* tape_used_host = nullptr;   // pinned; refreshed asynchronously after every recording forward
+    long long* ray_head = nullptr;
+    long long ray_head_cap = 0;
+    bool tape_valid = false;
+    unsigned long long tape_build_id = 0;
+    rgx_camera tape_cam{};
+    int tape_row_begin = 0, tape_row_end = 0;
     // optional kernel timing
     bool profiling = false;
     struct Timed { cudaEvent_t a, b; int kind; };
@@ -243,10 +257,11 @@ void rgx_destroy(rgx_ctx* ctx) {
                     ctx->cub_temp, ctx->bounds, ctx->box, ctx->counters, ctx->bin_counts, ctx->bin_offsets, ctx->bin_rect,
                     ctx->bin_depth, ctx->bin_keys_in, ctx->bin_keys_out, ctx->bin_vals_in, ctx->bin_vals_out,
                     ctx->tile_first, ctx->tile_last, ctx->tile_cnt, ctx->tile_pcnt, ctx->tile_pbegin, ctx->ent_id,
-                    ctx->ent_range, ctx->ent_blk, ctx->bin_cub, ctx->bin_total_dev};
+                    ctx->ent_range, ctx->ent_blk, ctx->bin_cub, ctx->bin_total_dev, ctx->tape, ctx->tape_used, ctx->ray_head, ctx->tile_dir, ctx->pair_j, ctx->pair_far};
     for (void* p : ptrs)
         if (p) cudaFree(p);
     if (ctx->bin_total_host) cudaFreeHost(ctx->bin_total_host);
+    if (ctx->tape_used_host) cudaFreeHost(ctx->tape_used_host);
     for (auto* v : {&ctx->timed, &ctx->spare})
         for (auto& t : *v) { cudaEventDestroy(t.a); cudaEventDestroy(t.b); }
     delete ctx;
@@ -345,6 +360,7 @@ static int ensure_lists(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m,
     if (ntiles + 1 > ctx->bin_tiles_cap) {
         size_t c = (size_t)ntiles + 1 + 64;
         RGB_(tile_first, c); RGB_(tile_last, c); RGB_(tile_cnt, c); RGB_(tile_pcnt, c); RGB_(tile_pbegin, c);
+        RGB_(tile_dir, c);
         ctx->bin_tiles_cap = (int)c;
     }
     auto need_cub = [&](size_t pairs) { return binning_cub_temp_bytes(pairs > 0 ? pairs : 1, ctx->bin_n_pad, ntiles); };
@@ -356,7 +372,8 @@ static int ensure_lists(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m,
     BinLaunch b{};
     b.n = ctx->n; b.n_pad = ctx->n_pad;
     b.bx = ctx->bx; b.by = ctx->by; b.bz = ctx->bz;
-    b.g0 = ctx->g0; b.quat = ctx->quat; b.sdens = ctx->sdens; b.hk = ctx->hk;
+    b.g0 = ctx->g0; b.g1 = ctx->g1; b.g2 = ctx->g2; b.quat = ctx->quat; b.sdens = ctx->sdens; b.hk = ctx->hk;
+    b.tile_dir = ctx->tile_dir;
     b.cam = *cam;
     if (!camera_dual(*cam, b.dual)) return fail(ctx, RGX_E_INVALID, "camera axes are not linearly independent");
     b.row_begin = m->row_begin; b.row_end = m->row_end; b.tile = kBinTile;
@@ -375,6 +392,7 @@ static int ensure_lists(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m,
     if ((size_t)total > ctx->bin_pair_cap) {
         size_t c = (size_t)total + (size_t)total / 4 + 1024;
         RGB_(bin_keys_in, c); RGB_(bin_keys_out, c); RGB_(bin_vals_in, c); RGB_(bin_vals_out, c);
+        RGB_(pair_j, c); RGB_(pair_far, c);
         ctx->bin_pair_cap = c;
     }
     const size_t ent_need = (((size_t)total + 32u * (size_t)ntiles + 31) / 32) * 32 + 32;
@@ -394,6 +412,7 @@ static int ensure_lists(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m,
     b.tile_first = ctx->tile_first; b.tile_last = ctx->tile_last; b.tile_cnt = ctx->tile_cnt; b.tile_pcnt = ctx->tile_pcnt;
     b.tile_pbegin = ctx->tile_pbegin;
     b.ent_id = ctx->ent_id; b.ent_range = ctx->ent_range; b.blk = ctx->ent_blk;
+    b.pair_j = ctx->pair_j; b.pair_far = ctx->pair_far;
     b.cub_temp = ctx->bin_cub; b.cub_bytes = ctx->bin_cub_cap;
     if ((e = launch_bin_fill(b, total, s)) != cudaSuccess) return cuda_fail(ctx, e, "tile-list fill");
     ctx->lists.ent_id = ctx->ent_id; ctx->lists.ent_range = ctx->ent_range; ctx->lists.blk = ctx->ent_blk;
@@ -438,11 +457,46 @@ int rgx_forward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, con
     }
     L.rgb = rgb; L.alpha = alpha; L.depth = depth;
     cudaError_t e;
+    const bool record = (march->flags & RGX_FLAG_SAVE_HITS) && L.lists.ent_id != nullptr && ctx->n > 0;
+    if (march->flags & RGX_FLAG_SAVE_HITS) ctx->tape_valid = false;
+    if (record) {
+        const long long rays = (long long)cam->width * cam->height;
+        const long long rows_rays = (long long)cam->width * (march->row_end - march->row_begin);
+        if (!ctx->tape_used) {
+            if ((e = regrow(ctx, ctx->tape_used, 1)) != cudaSuccess) return cuda_fail(ctx, e, "tape");
+            if ((e = cudaMallocHost((void**)&ctx->tape_used_host, sizeof(unsigned long long))) != cudaSuccess)
+                return cuda_fail(ctx, e, "tape");
+            *ctx->tape_used_host = 0;
+        }
+        if (rays > ctx->ray_head_cap) {
+            if ((e = regrow(ctx, ctx->ray_head, (size_t)rays)) != cudaSuccess) return cuda_fail(ctx, e, "tape");
+            ctx->ray_head_cap = rays;
+        }
+        // room: 256 ints per ray to begin with; more when the previous recording came close to the end
+        long long want = rows_rays * 256 + 1024;
+        const long long seen = (long long)*ctx->tape_used_host;
+        if (seen > (ctx->tape_cap / 4) * 3) want = want > seen * 2 ? want : seen * 2;
+        if (want > ctx->tape_cap) {
+            if ((e = regrow(ctx, ctx->tape, (size_t)want)) != cudaSuccess) return cuda_fail(ctx, e, "tape");
+            ctx->tape_cap = want;
+        }
+        if ((e = cudaMemsetAsync(ctx->tape_used, 0, sizeof(unsigned long long), s)) != cudaSuccess)
+            return cuda_fail(ctx, e, "tape");
+        L.tape = ctx->tape; L.tape_used = ctx->tape_used; L.tape_cap = ctx->tape_cap; L.ray_head = ctx->ray_head;
+    }
     {
         ScopedTimer timer(ctx, s, 0);
         e = launch_march_forward(L, s);
     }
-    return e == cudaSuccess ? RGX_OK : cuda_fail(ctx, e, "forward march");
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "forward march");
+    if (record) {
+        cudaMemcpyAsync(ctx->tape_used_host, ctx->tape_used, sizeof(unsigned long long), cudaMemcpyDeviceToHost, s);
+        ctx->tape_valid = true;
+        ctx->tape_build_id = ctx->build_id;
+        ctx->tape_cam = *cam;
+        ctx->tape_row_begin = march->row_begin; ctx->tape_row_end = march->row_end;
+    }
+    return RGX_OK;
 }
 
 int rgx_backward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, const rgx_march* march,
@@ -465,6 +519,11 @@ int rgx_backward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, co
     if (!(march->flags & (RGX_FLAG_BRUTE_FORCE | RGX_FLAG_PER_RAY_SEARCH))) {
         if ((rc = ensure_lists(ctx, cam, march, s))) return rc;
         L.lists = ctx->lists;
+    }
+    if (L.lists.ent_id && ctx->tape_valid && ctx->tape_build_id == ctx->build_id &&
+        ctx->tape_row_begin == march->row_begin && ctx->tape_row_end == march->row_end &&
+        std::memcmp(&ctx->tape_cam, cam, sizeof(rgx_camera)) == 0) {
+        L.tape = ctx->tape; L.tape_used = ctx->tape_used; L.tape_cap = ctx->tape_cap; L.ray_head = ctx->ray_head;
     }
     L.rgb_in = rgb; L.dl_drgb = dL_drgb; L.grad_rows = ctx->grad_rows;
     {

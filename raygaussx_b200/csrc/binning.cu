@@ -88,6 +88,95 @@ __device__ __forceinline__ void straddle_tiles(const float* xc, const float* zc,
     }
 }
 
+__device__ __forceinline__ float3 pixel_dir(const rgx_camera& c, float px, float py) {
+    float a = 2.0f * ((px + 0.5f) / (float)c.width - c.pp[0]) * c.tan_half_fov[0];
+    float bq = 2.0f * ((py + 0.5f) / (float)c.height - c.pp[1]) * c.tan_half_fov[1];
+    float3 d = make_float3(a * c.u[0] + bq * c.v[0] + c.w[0], a * c.u[1] + bq * c.v[1] + c.w[1],
+                           a * c.u[2] + bq * c.v[2] + c.w[2]);
+    float inv = 1.0f / sqrtf(dot3(d, d));
+    return d * inv;
+}
+
+// Per tile: direction of the ray through the tile centre and the largest chord |d - d_c| to a
+// ray of the tile (the rays of a tile lie inside the pyramid of its four corner rays).
+__global__ void bin_tile_dirs_kernel(BinLaunch b, int ntiles) {
+    int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= ntiles) return;
+    int tx = t % b.tiles_x, ty = t / b.tiles_x + b.ty_first;
+    float x0 = (float)(tx * b.tile), x1 = (float)min(tx * b.tile + b.tile - 1, b.cam.width - 1);
+    float y0 = (float)(ty * b.tile), y1 = (float)min(ty * b.tile + b.tile - 1, b.cam.height - 1);
+    float3 dc = pixel_dir(b.cam, 0.5f * (x0 + x1), 0.5f * (y0 + y1));
+    float chord = 0.f;
+    for (int c = 0; c < 4; ++c) {
+        float3 d = pixel_dir(b.cam, (c & 1) ? x1 : x0, (c & 2) ? y1 : y0) - dc;
+        chord = fmaxf(chord, sqrtf(dot3(d, d)));
+    }
+    b.tile_dir[t] = make_float4(dc.x, dc.y, dc.z, chord * 1.001f + 1e-7f);
+}
+
+// Per-Gaussian data needed to bound its meeting with a tile.
+struct PairGeom {
+    float2 bx, by, bz;
+    float4 g0, g1, g2;
+    float far_box;      // largest distance from the eye to the box
+    float rho_scale;    // operator norm of the whitening map: 1 / (k s_min), with slack for non-unit quaternions
+};
+
+// Range of ray parameters at which some ray of the tile can be inside the Gaussian's box and
+// inside its truncation ellipsoid; false if no ray of the tile can.  Every ray of the tile is, at
+// parameter t, within t * chord of the central ray's point, so the central ray is tested against
+// the box and the ellipsoid grown by that much.
+__device__ __forceinline__ bool pair_range(const float* eye, float4 td, const PairGeom& g, float& tn, float& tf) {
+    const float infl = g.far_box * td.w * 1.0001f + 1e-6f;
+    tn = 0.f; tf = INFINITY;
+    const float o[3] = {eye[0], eye[1], eye[2]}, d[3] = {td.x, td.y, td.z};
+    const float lo[3] = {g.bx.x - infl, g.by.x - infl, g.bz.x - infl}, hi[3] = {g.bx.y + infl, g.by.y + infl, g.bz.y + infl};
+#pragma unroll
+    for (int a = 0; a < 3; ++a) {
+        if (fabsf(d[a]) < 1e-12f) {
+            if (o[a] < lo[a] || o[a] > hi[a]) return false;
+        } else {
+            float t0 = (lo[a] - o[a]) / d[a], t1 = (hi[a] - o[a]) / d[a];
+            tn = fmaxf(tn, fminf(t0, t1));
+            tf = fminf(tf, fmaxf(t0, t1));
+        }
+    }
+    if (tn > tf * (1.0f + 1e-5f) + 1e-6f) return false;
+    // ellipsoid |M (x - p)| <= 1 grown to radius rho in the whitened frame
+    const float rho = 1.0f + infl * g.rho_scale;
+    float3 O = make_float3(o[0] - g.g0.x, o[1] - g.g0.y, o[2] - g.g0.z);
+    float3 Oe = make_float3(g.g0.w * O.x + g.g1.x * O.y + g.g1.y * O.z, g.g1.z * O.x + g.g1.w * O.y + g.g2.x * O.z,
+                            g.g2.y * O.x + g.g2.z * O.y + g.g2.w * O.z);
+    float3 de = make_float3(g.g0.w * d[0] + g.g1.x * d[1] + g.g1.y * d[2], g.g1.z * d[0] + g.g1.w * d[1] + g.g2.x * d[2],
+                            g.g2.y * d[0] + g.g2.z * d[1] + g.g2.w * d[2]);
+    const float qa = dot3(de, de), qb = -dot3(Oe, de), qc = dot3(Oe, Oe) - rho * rho;
+    const float disc = qb * qb - qa * qc;
+    const float mag = qb * qb + fabsf(qa * qc);
+    if (disc < -1e-5f * mag) return false;
+    if (qa > 1e-30f) {
+        const float sq = sqrtf(fmaxf(disc, 0.f) + 1e-5f * mag);
+        const float r1 = (qb - sq) / qa, r2 = (qb + sq) / qa;
+        tn = fmaxf(tn, r1);
+        tf = fminf(tf, r2);
+    }
+    tn = fmaxf(tn * (1.0f - 1e-5f) - 1e-6f, 0.f);
+    tf = tf * (1.0f + 1e-5f) + 1e-6f;
+    return tn <= tf;
+}
+
+__device__ __forceinline__ PairGeom load_pair_geom(const BinLaunch& b, int j) {
+    PairGeom g;
+    g.bx = b.bx[j]; g.by = b.by[j]; g.bz = b.bz[j];
+    g.g0 = b.g0[j]; g.g1 = b.g1[j]; g.g2 = b.g2[j];
+    g.far_box = b.depth[j].y;
+    float4 sd = b.sdens[j], q = b.quat[j];
+    float k = sqrtf(2.0f * 0.6931471805599453f * b.hk[j]);
+    float smin = fminf(sd.x, fminf(sd.y, sd.z));
+    float qn = q.x * q.x + q.y * q.y + q.z * q.z + q.w * q.w;
+    g.rho_scale = 1.02f * fmaxf(1.0f, qn) / (k * smin);
+    return g;
+}
+
 // One thread per sorted slot: tile rectangle (box rectangle cut by the rectangle of
 // the oriented box of the truncation ellipsoid), distance range, number of tiles.
 __global__ void __launch_bounds__(256) bin_count_kernel(BinLaunch b) {
@@ -156,9 +245,20 @@ __global__ void __launch_bounds__(256) bin_count_kernel(BinLaunch b) {
             }
         }
     }
-    b.counts[j] = count;
     b.rect[j] = rect;
     b.depth[j] = depth;
+    if (count > 0) {      // keep only the tiles some ray of which can actually meet the Gaussian
+        const PairGeom g = load_pair_geom(b, j);
+        unsigned tx0 = rect.x & 0xffffu, tx1 = rect.x >> 16, ty0 = rect.y & 0xffffu, ty1 = rect.y >> 16;
+        int kept = 0;
+        for (unsigned ty = ty0; ty <= ty1; ++ty)
+            for (unsigned tx = tx0; tx <= tx1; ++tx) {
+                float tn, tf;
+                kept += pair_range(b.cam.eye, b.tile_dir[ty * (unsigned)b.tiles_x + tx], g, tn, tf) ? 1 : 0;
+            }
+        count = kept;
+    }
+    b.counts[j] = count;
 }
 
 __global__ void bin_total_kernel(BinLaunch b) {
@@ -171,16 +271,20 @@ __global__ void bin_total_kernel(BinLaunch b) {
 __global__ void __launch_bounds__(256) bin_emit_kernel(BinLaunch b) {
     int j = blockIdx.x * blockDim.x + threadIdx.x;
     if (j >= b.n_pad) return;
-    int count = b.counts[j];
-    if (count == 0) return;
+    if (b.counts[j] == 0) return;
     uint2 rect = b.rect[j];
     unsigned tx0 = rect.x & 0xffffu, tx1 = rect.x >> 16, ty0 = rect.y & 0xffffu, ty1 = rect.y >> 16;
-    uint64_t dbits = (uint64_t)__float_as_uint(b.depth[j].x);
+    const PairGeom g = load_pair_geom(b, j);
     size_t k = (size_t)b.offsets[j];
     for (unsigned ty = ty0; ty <= ty1; ++ty)
         for (unsigned tx = tx0; tx <= tx1; ++tx) {
-            b.keys_in[k] = ((uint64_t)(ty * (unsigned)b.tiles_x + tx) << 32) | dbits;
-            b.vals_in[k] = (uint32_t)j;
+            const unsigned t = ty * (unsigned)b.tiles_x + tx;
+            float tn, tf;
+            if (!pair_range(b.cam.eye, b.tile_dir[t], g, tn, tf)) continue;
+            b.keys_in[k] = ((uint64_t)t << 32) | (uint64_t)__float_as_uint(tn);
+            b.vals_in[k] = (uint32_t)k;          // emission index; the sort carries it to the pair's data
+            b.pair_j[k] = j;
+            b.pair_far[k] = tf;
             ++k;
         }
 }
@@ -213,10 +317,10 @@ __global__ void __launch_bounds__(256) bin_scatter_kernel(BinLaunch b, int total
     if (k >= total) return;
     uint64_t key = b.keys_out[k];
     int t = (int)(key >> 32);
-    int j = (int)b.vals_out[k];
+    const uint32_t src = b.vals_out[k];
     size_t dest = (size_t)b.tile_pbegin[t] + (size_t)(k - b.tile_first[t]);
-    b.ent_id[dest] = j;
-    b.ent_range[dest] = make_float2(__uint_as_float((unsigned)(key & 0xffffffffu)), b.depth[j].y);
+    b.ent_id[dest] = b.pair_j[src];
+    b.ent_range[dest] = make_float2(__uint_as_float((unsigned)(key & 0xffffffffu)), b.pair_far[src]);
 }
 
 // One warp per block of 32 entries: nearest near distance and farthest far distance.
@@ -249,6 +353,8 @@ size_t binning_cub_temp_bytes(size_t pair_cap, int n_pad, int ntiles) {
 // Phase 1: rectangles, counts, offsets, total (left in b.total_dev; the caller copies it to the host).
 cudaError_t launch_bin_count(const BinLaunch& b, cudaStream_t s) {
     const int tb = 256;
+    const int ntiles = b.tiles_x * b.tiles_y;
+    bin_tile_dirs_kernel<<<(ntiles + tb - 1) / tb, tb, 0, s>>>(b, ntiles);
     bin_count_kernel<<<(b.n_pad + tb - 1) / tb, tb, 0, s>>>(b);
     size_t temp = b.cub_bytes;
     cudaError_t e = cub::DeviceScan::ExclusiveSum(b.cub_temp, temp, b.counts, b.offsets, b.n_pad, s);

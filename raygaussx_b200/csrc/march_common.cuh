@@ -17,10 +17,12 @@ constexpr unsigned kFull = 0xffffffffu;
 constexpr int kTile = 8;   // CTA = 8x8 pixels; warp w marches column w of the tile
 constexpr int kMaxSlabs = 1 << 22;   // hard bound on slab iterations per ray
 
-struct WarpShared {
+struct WarpStage {      // staged hit records of one warp
     float4 recA[kStage];
     float4 recB[kStage];
     float4 recC[kStage];
+};
+struct WarpShared : WarpStage {   // plus the search stack of the per-ray variant
     uint32_t stack[kStack];
     float stack_t[kStack];
 };
@@ -88,10 +90,8 @@ __device__ __forceinline__ bool box_hit(const Ray& r, float2 bx, float2 by, floa
     return tnear <= tfar;
 }
 
-// Interval of the ray inside the truncation ellipsoid
-// (cuda_train/forward/gaussians_aabb.cu:43-91 with M = S^-1 R^T / k folded into g0..g2).
-__device__ __forceinline__ bool ellipsoid_interval(const Ray& r, float4 g0, float4 g1, float4 g2, float3& Oe,
-                                                   float3& de, float& r1, float& r2) {
+// Ray origin and direction in the Gaussian's whitened frame (M = S^-1 R^T / k in g0..g2).
+__device__ __forceinline__ void whiten_ray(const Ray& r, float4 g0, float4 g1, float4 g2, float3& Oe, float3& de) {
     float3 O = make_float3(r.o.x - g0.x, r.o.y - g0.y, r.o.z - g0.z);
     Oe.x = fmaf(g0.w, O.x, fmaf(g1.x, O.y, __fmul_rn(g1.y, O.z)));
     Oe.y = fmaf(g1.z, O.x, fmaf(g1.w, O.y, __fmul_rn(g2.x, O.z)));
@@ -99,6 +99,13 @@ __device__ __forceinline__ bool ellipsoid_interval(const Ray& r, float4 g0, floa
     de.x = fmaf(g0.w, r.d.x, fmaf(g1.x, r.d.y, __fmul_rn(g1.y, r.d.z)));
     de.y = fmaf(g1.z, r.d.x, fmaf(g1.w, r.d.y, __fmul_rn(g2.x, r.d.z)));
     de.z = fmaf(g2.y, r.d.x, fmaf(g2.z, r.d.y, __fmul_rn(g2.w, r.d.z)));
+}
+
+// Interval of the ray inside the truncation ellipsoid
+// (cuda_train/forward/gaussians_aabb.cu:43-91 with M = S^-1 R^T / k folded into g0..g2).
+__device__ __forceinline__ bool ellipsoid_interval(const Ray& r, float4 g0, float4 g1, float4 g2, float3& Oe,
+                                                   float3& de, float& r1, float& r2) {
+    whiten_ray(r, g0, g1, g2, Oe, de);
     float a = dot3(de, de);
     float b = -dot3(Oe, de);
     float c = fmaf(Oe.x, Oe.x, fmaf(Oe.y, Oe.y, fmaf(Oe.z, Oe.z, -1.0f)));
@@ -374,7 +381,7 @@ __device__ __forceinline__ void clip_scene(const SceneBox& b, const Ray& r, floa
 // Evaluate `count` staged Gaussians at this lane's sample: sums of sigma*g and of
 // (payload)*g, payload being rgb*sigma in the forward (cuda_train/forward/gaussians_aabb.cu:166-178).
 template <bool COUNT>
-__device__ __forceinline__ void eval_forward(const WarpShared& ws, int count, float tau, float& s, float& cr,
+__device__ __forceinline__ void eval_forward(const WarpStage& ws, int count, float tau, float& s, float& cr,
                                              float& cg, float& cb, Tally& tl) {
 #pragma unroll 2
     for (int j = 0; j < count; ++j) {
@@ -434,7 +441,7 @@ __device__ __forceinline__ float reduce8(const float (&v)[8], int lane) {
 // the four per-Gaussian sums, the warp adds them up eight Gaussians at a time, and
 // lane j keeps the totals of staged Gaussian j.
 //   recA = (y_c.xyz, hk)  recB = (de.xyz, tbuffer - t_c)  recC = (chat_i, -, -, -)
-__device__ __forceinline__ void eval_backward(const WarpShared& ws, int count, float tau, float beta, float gamma,
+__device__ __forceinline__ void eval_backward(const WarpStage& ws, int count, float tau, float beta, float gamma,
                                               int lane, float& o_sb, float& o_n0, float& o_n1, float& o_n2) {
     for (int j0 = 0; j0 < count; j0 += 8) {
         float vb[8], v0[8], v1[8], v2[8];
@@ -474,7 +481,7 @@ __device__ __forceinline__ void eval_backward(const WarpShared& ws, int count, f
 // the forward and (dl . rgb*sigma, 0, 0) in the backward.  Returns the hit count.
 template <bool COUNT, bool BWD, class Enum>
 __device__ __forceinline__ int slab_sums(const MarchLaunch& L, const rgx_march& m, float tbuffer, float tau,
-                                         int ray_id, int slab_index, float3 dl, WarpShared& ws, int lane, Tally& tl,
+                                         int ray_id, int slab_index, float3 dl, WarpStage& ws, int lane, Tally& tl,
                                          Enum&& enumerate, float& s, float& c0, float& c1, float& c2,
                                          bool& overflow, int* hit_list = nullptr, int hit_cap = 0) {
     int nstage = 0, nhit = 0;
@@ -645,7 +652,7 @@ __device__ __forceinline__ GaussGrad expand_gradient(const MarchLaunch& L, const
 template <class Enum, class Emit>
 __device__ __forceinline__ void slab_gradients(const MarchLaunch& L, const rgx_march& m, const Ray& r,
                                                const SlabPlan& p, float tbuffer, float tau, float3 dl, float beta,
-                                               float gamma, WarpShared& ws, int* prim_of, int lane,
+                                               float gamma, WarpStage& ws, int* prim_of, int lane,
                                                Enum&& enumerate, Emit&& emit) {
     int nstage = 0, nhit = 0;
     auto drain = [&]() {

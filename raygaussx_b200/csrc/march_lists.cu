@@ -33,7 +33,7 @@ struct ListShared {
     int next_ray;
     int pend[kWarps][2 * kFan];
     int prim_of[kWarps][kFan];
-    WarpShared ws[kWarps];
+    WarpStage ws[kWarps];
 };
 
 struct TileView {      // one tile's list
@@ -164,11 +164,13 @@ __device__ __forceinline__ bool ray_pixel(const MarchLaunch& L, int tile_x, int 
 }
 
 // ---------------------------------------------------------------- forward
-template <bool COUNT>
+template <bool COUNT, bool SAVE>
 __global__ void __launch_bounds__(kThreads) march_forward_lists_kernel(const __grid_constant__ MarchLaunch L) {
     __shared__ ListShared sh;
+    __shared__ int hit_lists[SAVE ? kWarps : 1][SAVE ? kHitList : 1];
+    constexpr bool save = SAVE;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    WarpShared& ws = sh.ws[warp];
+    WarpStage& ws = sh.ws[warp];
     int* pend = sh.pend[warp];
     const int tile = blockIdx.x;
     const int tile_x = tile % L.lists.tiles_x, tile_y = tile / L.lists.tiles_x;
@@ -196,6 +198,8 @@ __global__ void __launch_bounds__(kThreads) march_forward_lists_kernel(const __g
         clip_scene(box, r, tenter, texit);
         RayColor st = {1.0f, 0.f, 0.f, 0.f, 0.f};
         int cursor = 0;
+        long long tape_head = -1, tape_prev = -1;    // first and latest chunk of this ray on the tape
+        bool tape_ok = true;
         if (COUNT) tl.v[C_RAYS] += 1;
         float first = closest_in_tile<COUNT>(L, r, tenter, texit, tv, cursor, pend, lane, tl);
         if (first < INFINITY && first < texit) {                                  // :249-260
@@ -210,11 +214,35 @@ __global__ void __launch_bounds__(kThreads) march_forward_lists_kernel(const __g
                 const float tau = __fmul_rn((float)lane + 0.5f, p.dt);
                 float s, cr, cg, cb;
                 bool overflow;
+                int* hits = hit_lists[SAVE ? warp : 0];
                 int nhit = slab_sums<COUNT, false>(L, L.m, tbuffer, tau, ray_id, slab_index, make_float3(0.f, 0.f, 0.f),
                                                    ws, lane, tl, [&](auto&& leaf) {
                     search_tile<COUNT>(L, r, p.tmin, p.tmax, tv, cursor, pend, lane, tl, leaf);
-                }, s, cr, cg, cb, overflow);
+                }, s, cr, cg, cb, overflow, save ? hits : nullptr, kHitList);
                 if (COUNT) { tl.v[C_HITS] += nhit; tl.v[C_OVF] += overflow ? 1 : 0; }
+                if (save && nhit > 0 && tape_ok) {
+                    // one chunk per slab with hits: [tbuffer, count, next lo, next hi, slots...]
+                    long long off = -1;
+                    if (nhit <= kHitList) {
+                        unsigned long long o = 0;
+                        if (lane == 0) o = atomicAdd(L.tape_used, (unsigned long long)(4 + nhit));
+                        o = __shfl_sync(kFull, o, 0);
+                        if ((long long)(o + 4 + nhit) <= L.tape_cap) off = (long long)o;
+                    }
+                    if (off < 0) tape_ok = false;          // no room (or too many hits): the backward will search this ray
+                    else {
+                        __syncwarp();
+                        if (lane == 0) {
+                            L.tape[off] = __float_as_int(tbuffer); L.tape[off + 1] = nhit;
+                            L.tape[off + 2] = -1; L.tape[off + 3] = -1;
+                            if (tape_prev >= 0) { L.tape[tape_prev + 2] = (int)(off & 0xffffffffll); L.tape[tape_prev + 3] = (int)(off >> 32); }
+                        }
+                        for (int i = lane; i < nhit; i += 32) L.tape[off + 4 + i] = hits[i];
+                        if (tape_head < 0) tape_head = off;
+                        tape_prev = off;
+                        __syncwarp();
+                    }
+                }
                 if (nhit == 0) {                                                  // :297-319
                     tbuffer = __fadd_rn(tbuffer, p.slab);
                     float nxt = closest_in_tile<COUNT>(L, r, tbuffer, texit, tv, cursor, pend, lane, tl);
@@ -233,6 +261,7 @@ __global__ void __launch_bounds__(kThreads) march_forward_lists_kernel(const __g
             L.rgb[3 * (size_t)ray_id + 2] = fmaf(st.T, bg, st.Cb);
             if (L.alpha) L.alpha[ray_id] = 1.0f - st.T;
             if (L.depth) L.depth[ray_id] = st.depth;
+            if (save) L.ray_head[ray_id] = tape_ok ? tape_head : -2;
         }
     }
     if (COUNT) flush_tally(L, tl, lane);
@@ -243,7 +272,7 @@ __global__ void __launch_bounds__(kThreads) march_backward_lists_kernel(const __
     __shared__ ListShared sh;
     __shared__ int hit_lists[kWarps][kHitList];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    WarpShared& ws = sh.ws[warp];
+    WarpStage& ws = sh.ws[warp];
     int* pend = sh.pend[warp];
     const int tile = blockIdx.x;
     const int tile_x = tile % L.lists.tiles_x, tile_y = tile / L.lists.tiles_x;
@@ -269,14 +298,52 @@ __global__ void __launch_bounds__(kThreads) march_backward_lists_kernel(const __
         float tenter, texit;
         clip_scene(box, r, tenter, texit);
         int cursor = 0;
-        float first = closest_in_tile<false>(L, r, tenter, texit, tv, cursor, pend, lane, tl);
-        if (!(first < INFINITY && first < texit)) continue;                       // backward .cu:249-254
-        tenter = first;
         const float3 dl = make_float3(L.dl_drgb[3 * (size_t)ray_id], L.dl_drgb[3 * (size_t)ray_id + 1],
                                       L.dl_drgb[3 * (size_t)ray_id + 2]);
         float D = fmaf(dl.x, L.rgb_in[3 * (size_t)ray_id],
                        fmaf(dl.y, L.rgb_in[3 * (size_t)ray_id + 1], __fmul_rn(dl.z, L.rgb_in[3 * (size_t)ray_id + 2])));
         float T = 1.0f;
+        const long long head = L.tape ? L.ray_head[ray_id] : -2;
+        if (head != -2) {
+            // The forward left this ray's slabs on the tape: same hits in the same order, so the sums, the
+            // transmittance and with it the step sizes come out bit for bit as in the forward -- no search.
+            long long off = head;
+            int* hits = hit_lists[warp];
+            while (off >= 0) {
+                const float tbuffer = __int_as_float(L.tape[off]);
+                const int nhit = L.tape[off + 1];
+                const long long next = ((long long)L.tape[off + 3] << 32) | (unsigned int)L.tape[off + 2];
+                for (int i = lane; i < nhit; i += 32) hits[i] = L.tape[off + 4 + i];
+                __syncwarp();
+                SlabPlan p = plan_slab(L.m, tbuffer, T, tbuffer, texit);
+                const float tau = __fmul_rn((float)lane + 0.5f, p.dt);
+                auto replay = [&](auto&& leaf) {
+                    for (int base = 0; base < nhit; base += kFan) {
+                        const bool valid = base + lane < nhit;
+                        const int j = valid ? hits[base + lane] : 0;
+                        LeafTest t;
+                        t.hit = valid;
+                        t.t_hit = 0.f;
+                        if (valid) whiten_ray(r, __ldg(&L.g.g0[j]), __ldg(&L.g.g1[j]), __ldg(&L.g.g2[j]), t.Oe, t.de);
+                        if (!leaf(t, j)) return;
+                    }
+                };
+                float s, dc, u0, u1;
+                bool overflow;
+                slab_sums<false, true>(L, L.m, tbuffer, tau, ray_id, 0, dl, ws, lane, tl, replay, s, dc, u0, u1, overflow);
+                SlabBackTerms bt = slab_back_terms(s, dc, p.dt, T, D, eps, lane);
+                slab_gradients(L, L.m, r, p, tbuffer, tau, dl, bt.beta, bt.gamma, ws, sh.prim_of[warp], lane, replay,
+                               [&](int j, const GaussGrad& g) { emit_global(L, dl, j, g); });
+                D = __fadd_rn(D, -bt.d_total);
+                T = slab_exit_T(bt.tr, eps);
+                off = next;
+                __syncwarp();
+            }
+            continue;
+        }
+        float first = closest_in_tile<false>(L, r, tenter, texit, tv, cursor, pend, lane, tl);
+        if (!(first < INFINITY && first < texit)) continue;                       // backward .cu:249-254
+        tenter = first;
         float tbuffer = tenter;
         int slab_index = 0;
         while (tbuffer < texit && T > eps && slab_index < kMaxSlabs) {
@@ -334,8 +401,11 @@ cudaError_t launch_march_forward(const MarchLaunch& m, cudaStream_t s) {
     if (!use_lists(m)) return launch_march_forward_per_ray(m, s);
     const int grid = m.lists.tiles_x * m.lists.tiles_y;
     if (grid <= 0) return cudaSuccess;
-    if (m.m.flags & RGX_FLAG_COUNT_WORK) march_forward_lists_kernel<true><<<grid, kThreads, 0, s>>>(m);
-    else march_forward_lists_kernel<false><<<grid, kThreads, 0, s>>>(m);
+    const bool count = (m.m.flags & RGX_FLAG_COUNT_WORK) != 0, save = m.tape != nullptr;
+    if (count && save) march_forward_lists_kernel<true, true><<<grid, kThreads, 0, s>>>(m);
+    else if (count) march_forward_lists_kernel<true, false><<<grid, kThreads, 0, s>>>(m);
+    else if (save) march_forward_lists_kernel<false, true><<<grid, kThreads, 0, s>>>(m);
+    else march_forward_lists_kernel<false, false><<<grid, kThreads, 0, s>>>(m);
     return cudaGetLastError();
 }
 

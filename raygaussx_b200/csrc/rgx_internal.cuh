@@ -71,7 +71,7 @@ struct TileLists {
 struct BinLaunch {
     int n, n_pad;
     const float2 *bx, *by, *bz;            // level-0 boxes
-    const float4 *g0, *quat, *sdens;
+    const float4 *g0, *g1, *g2, *quat, *sdens;
     const float* hk;
     rgx_camera cam;
     float dual[3][3];                      // dual basis of (u, v, w): rows u*, v*, w*
@@ -83,6 +83,8 @@ struct BinLaunch {
     uint32_t *vals_in, *vals_out;
     int *tile_first, *tile_last, *tile_cnt, *tile_pcnt, *tile_pbegin;   // [tiles + 1]
     int* ent_id; float2* ent_range; float2* blk;
+    float4* tile_dir;                      // [tiles] central ray direction, chord to the farthest corner ray
+    int* pair_j; float* pair_far;          // [pair capacity] in emission order
     void* cub_temp; size_t cub_bytes;
     int* total_dev;
 };
@@ -101,6 +103,13 @@ struct MarchLaunch {
     float* depth;
     const float* rgb_in;
     const float* dl_drgb;
+    // "tape": what the forward met, kept for the backward (RGX_FLAG_SAVE_HITS).  Per slab with hits a chunk
+    // [tbuffer bits, hit count, next chunk offset lo, hi, sorted slots...]; ray_head[ray] = first chunk,
+    // -1 = no slab with hits, -2 = not recorded (the backward searches again).
+    int* tape;
+    unsigned long long* tape_used;
+    long long tape_cap;
+    long long* ray_head;
     float4* grad_rows;    // [n_pad,4] float4: (dpos.xyz, dscale.x) (dscale.yz, dquat.xy) (dquat.zw, dsigma, drgb.x) (drgb.yz, 0, 0)
 };
 

@@ -118,7 +118,7 @@ def accumulation_step(renderer, tensors: Sequence[torch.Tensor], cameras, target
         rows = (blk.row_begin, blk.row_end)
         r_total = cam.width * cam.height
         lo, hi = blk.row_begin * cam.width, blk.row_end * cam.width
-        rgb, _, _ = renderer.forward(*tensors, cam, march_of(cam, rows, 0))
+        rgb, _, _ = renderer.forward(*tensors, cam, march_of(cam, rows, _lib.FLAG_SAVE_HITS))
         seg = rgb[lo:hi]
         dl = torch.empty_like(rgb)      # only rows [row_begin, row_end) are read by the backward
         dl[lo:hi] = l1_loss_gradient(seg, targets[blk.view][lo:hi], r_total, n_views)

@@ -281,7 +281,8 @@ class RenderOptixFunction(torch.autograd.Function):
         if not getattr(settings, "reuse_acceleration_structure", False) or r._n_built != tensors[0].shape[0]:
             r.build(*tensors[:4], sigma_threshold=SIGMA_THRESHOLD,
                     morton_bits=getattr(settings, "morton_bits", 10))
-        march = _settings_march(settings, cam)
+        # keep what the rays met, so that the backward of this view does not have to search again
+        march = _settings_march(settings, cam, flags=_lib.FLAG_SAVE_HITS)
         rgb, _, _ = r.forward(*tensors, cam, march)
         ctx.settings = settings
         ctx.save_for_backward(*tensors, rgb)

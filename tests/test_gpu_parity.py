@@ -121,6 +121,25 @@ def test_backward_variants_agree(ro):
             assert rel_max(a.cpu(), b.cpu()) < 1e-5      # only the order of atomic additions differs
 
 
+@pytest.mark.parametrize("name", ["small_dynamic_white", "config1"])
+def test_backward_from_recorded_hits_equals_backward_by_search(ro, name):
+    sc = make_scene(name)
+    r, tens, cs, rgb, _, _ = render(ro, sc)
+    dl = loss_gradient(rgb.cpu().double(), rgb.shape[0])
+    searched = backward(ro, r, sc, tens, cs, rgb, dl)                 # nothing recorded: the backward searches
+    st = settings_for(ro, sc, sc.cameras[0])
+    rgb2, _, _ = r.forward(*tens, cs, ro._settings_march(st, cs, flags=_lib.FLAG_SAVE_HITS))
+    assert torch.equal(rgb, rgb2)
+    replayed = backward(ro, r, sc, tens, cs, rgb2, dl)                # reads the recorded hits
+    for a, b in zip(searched[:5], replayed[:5]):
+        assert rel_max(a.cpu(), b.cpu()) < 1e-5
+    # a recording for another view must not be used: render a shifted camera without recording, then check
+    g = load_golden(name)
+    for nm, gr in zip(GRAD_NAMES, replayed):
+        if "oracle_grad_" + nm in g.files and torch.allclose(dl, torch.from_numpy(g["dl"]), atol=0):
+            assert rel_max(g["oracle_grad_" + nm], gr.cpu()) <= GRAD_TOL, nm
+
+
 def test_autograd_function_is_a_drop_in(ro):
     sc = make_scene("small_lobes_deg2")
     g = load_golden("small_lobes_deg2")
