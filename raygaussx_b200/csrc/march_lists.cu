@@ -268,6 +268,9 @@ __global__ void __launch_bounds__(kThreads) march_forward_lists_kernel(const __g
 }
 
 // ---------------------------------------------------------------- backward
+// TAPE = true: rays whose forward was recorded, replayed from the tape, no search code at all.
+// TAPE = false: rays without a recording (all of them when nothing was recorded), by searching again.
+template <bool TAPE>
 __global__ void __launch_bounds__(kThreads) march_backward_lists_kernel(const __grid_constant__ MarchLaunch L) {
     __shared__ ListShared sh;
     __shared__ int hit_lists[kWarps][kHitList];
@@ -304,7 +307,8 @@ __global__ void __launch_bounds__(kThreads) march_backward_lists_kernel(const __
                        fmaf(dl.y, L.rgb_in[3 * (size_t)ray_id + 1], __fmul_rn(dl.z, L.rgb_in[3 * (size_t)ray_id + 2])));
         float T = 1.0f;
         const long long head = L.tape ? L.ray_head[ray_id] : -2;
-        if (head != -2) {
+        if (TAPE != (head != -2)) continue;
+        if (TAPE) {
             // The forward left this ray's slabs on the tape: same hits in the same order, so the sums, the
             // transmittance and with it the step sizes come out bit for bit as in the forward -- no search.
             long long off = head;
@@ -341,6 +345,7 @@ __global__ void __launch_bounds__(kThreads) march_backward_lists_kernel(const __
             }
             continue;
         }
+        if constexpr (!TAPE) {
         float first = closest_in_tile<false>(L, r, tenter, texit, tv, cursor, pend, lane, tl);
         if (!(first < INFINITY && first < texit)) continue;                       // backward .cu:249-254
         tenter = first;
@@ -385,6 +390,7 @@ __global__ void __launch_bounds__(kThreads) march_backward_lists_kernel(const __
             T = slab_exit_T(bt.tr, eps);
             tbuffer = __fadd_rn(tbuffer, p.slab);
         }
+        }   // !TAPE
     }
 }
 
@@ -413,7 +419,8 @@ cudaError_t launch_march_backward(const MarchLaunch& m, cudaStream_t s) {
     if (!use_lists(m)) return launch_march_backward_per_ray(m, s);
     const int grid = m.lists.tiles_x * m.lists.tiles_y;
     if (grid <= 0) return cudaSuccess;
-    march_backward_lists_kernel<<<grid, kThreads, 0, s>>>(m);
+    if (m.tape) march_backward_lists_kernel<true><<<grid, kThreads, 0, s>>>(m);     // recorded rays
+    march_backward_lists_kernel<false><<<grid, kThreads, 0, s>>>(m);               // the others (a quick no-op per recorded ray)
     return cudaGetLastError();
 }
 
