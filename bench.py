@@ -313,23 +313,26 @@ def main():
     rows_per_launch = sum(b.row_end - b.row_begin for b in shard_rows(args.views, args.height, 0, world)) / max(
         1, len(shard_rows(args.views, args.height, 0, world)))
     rays_per_launch = rows_per_launch * args.width
-    alg_bytes = 536.0 * args.gaussians + 28.0 * rays_per_launch          # backward: per Gaussian, per ray
-    achieved = alg_bytes / (bwd_ms * 1e-3) / 1e9
-    # work counters of one view (outside the timed region) for the FP32 / MUFU figures
+    # work counters of one view (outside the timed region): hits P, (sample, Gaussian) pairs E, slabs with hits Sh
     renderer.reset_counters()
     renderer.forward(*scene_dev_tensors, cams[0], march_of(cams[0], None, _lib.FLAG_COUNT_WORK))
     cn = renderer.read_counters()
     P, E, Sh = cn["hits"], cn["pairs_inside"], cn["slabs_hit"]
     frac_view = rays_per_launch / R
-    f_bwd = (290.0 * P + 22.0 * E + 640.0 * Sh) * frac_view
-    mufu_bwd = (2.0 * E + 96.0 * Sh) * frac_view
+    # backward: per Gaussian its records and gradient row, per ray colour and loss gradient, and the forward's
+    # recording (per slab with hits a 528-byte head with the per-sample sums, 4 bytes per hit)
+    tape_bytes = (528.0 * Sh + 4.0 * P) * frac_view
+    alg_bytes = 536.0 * args.gaussians + 28.0 * rays_per_launch + tape_bytes
+    achieved = alg_bytes / (bwd_ms * 1e-3) / 1e9
+    f_bwd = (290.0 * P + 11.0 * E + 320.0 * Sh) * frac_view
+    mufu_bwd = (1.0 * E + 48.0 * Sh) * frac_view
     fp32_peak = 2.0 * 128 * n_sm * sm_max_mhz * 1e6
     mufu_peak = 16.0 * n_sm * sm_max_mhz * 1e6
-    roofline = {"kernel": "march_backward_tiled_kernel", "bound": "hbm", "achieved": achieved, "peak": hbm_peak,
+    roofline = {"kernel": "march_backward_lists_kernel<true> (replay of the recorded forward)", "bound": "hbm", "achieved": achieved, "peak": hbm_peak,
                 "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_src, "traffic": None,
                 "ms_per_launch": bwd_ms, "launches_timed": ktimes["backward_launches"],
                 "forward_ms_per_launch": fwd_ms,
-                "algorithmic_bytes_per_launch": alg_bytes,
+                "algorithmic_bytes_per_launch": alg_bytes, "of_which_recording": tape_bytes,
                 "fp32_frac": f_bwd / (bwd_ms * 1e-3) / fp32_peak, "mufu_frac": mufu_bwd / (bwd_ms * 1e-3) / mufu_peak,
                 "note": "the march kernels are issue/latency bound, not HBM bound: fp32_frac and mufu_frac are useful "
                         "flops and ex2 per second over the derived peaks (2*128*SMs*f, 16*SMs*f)",
@@ -353,7 +356,9 @@ def main():
             cpu_baseline = {"value": None, "unit": "Mrays/s", "cores": os.cpu_count() or 1, "kind": "reference",
                             "sample": f"failed: {exc}"}
 
-    launches_per_step = 6 + 5 * len(shard_rows(args.views, args.height, 0, world))
+    # hand-written kernels: 6 of the build, then per row block colours, 7 of the tile lists, forward,
+    # 2 of the backward, finalise (the library's CUB sort and scan kernels are not counted)
+    launches_per_step = 6 + 12 * len(shard_rows(args.views, args.height, 0, world))
     out = {
         "metric": METRIC, "value": value, "unit": "Mrays/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",

@@ -22,6 +22,7 @@ struct rgx_ctx {
     float2 *bx = nullptr, *by = nullptr, *bz = nullptr;
     float4 *g0 = nullptr, *g1 = nullptr, *g2 = nullptr, *quat = nullptr, *sdens = nullptr, *rgba = nullptr;
     float4* grad_rows = nullptr;
+    int grad_copies = 1;     // sets of gradient rows the backward spreads its atomic additions over
     float* hk = nullptr;
     unsigned int* refit_counters = nullptr;
     unsigned char* cub_temp = nullptr;
@@ -36,22 +37,21 @@ struct rgx_ctx {
     Hierarchy hier{};
     unsigned long long build_id = 0;   // bumped by every rgx_build
     // per-view tile lists (binning.cu)
-    int bin_n_pad = 0, bin_tiles_cap = 0;
+    int bin_tiles_cap = 0;
     size_t bin_pair_cap = 0, bin_ent_cap = 0, bin_cub_cap = 0;
-    int *bin_counts = nullptr, *bin_offsets = nullptr;
-    uint2* bin_rect = nullptr;
-    float2* bin_depth = nullptr;
     uint64_t *bin_keys_in = nullptr, *bin_keys_out = nullptr;
     uint32_t *bin_vals_in = nullptr, *bin_vals_out = nullptr;
     int *tile_first = nullptr, *tile_last = nullptr, *tile_cnt = nullptr, *tile_pcnt = nullptr, *tile_pbegin = nullptr;
+    int *tile_iota = nullptr, *tile_cnt_sorted = nullptr, *tile_order = nullptr;
     int* ent_id = nullptr;
     float2 *ent_range = nullptr, *ent_blk = nullptr;
     float4* tile_dir = nullptr;
-    int* pair_j = nullptr;
-    float* pair_far = nullptr;
     unsigned char* bin_cub = nullptr;
-    int* bin_total_dev = nullptr;
-    int* bin_total_host = nullptr;      // pinned
+    int* big_slot = nullptr;
+    uint2* big_rect = nullptr;
+    int big_cap = 0, sm_count = 0;
+    unsigned long long* bin_total_dev = nullptr;
+    unsigned long long* bin_total_host = nullptr;      // pinned
     // what the current lists were made for
     int last_pairs = 0;
     float binning_ms = 0.f; int binning_runs = 0;
@@ -146,7 +146,10 @@ int ensure_workspace(rgx_ctx* ctx, int n_pad, int boxes) {
         RG(keys_in); RG(keys_out); RG(vals_in); RG(vals_out);
         RG(g0); RG(g1); RG(g2); RG(quat); RG(sdens); RG(rgba); RG(hk);
 #undef RG
-        if ((e = regrow(ctx, ctx->grad_rows, 4 * c)) != cudaSuccess) return cuda_fail(ctx, e, "workspace grad_rows");
+        int copies = 8;                                  // 64 bytes per Gaussian and copy, at most 2 GiB in all
+        while (copies > 1 && (size_t)copies * c * 64 > ((size_t)2 << 30)) copies >>= 1;
+        if ((e = regrow(ctx, ctx->grad_rows, 4 * c * (size_t)copies)) != cudaSuccess) return cuda_fail(ctx, e, "workspace grad_rows");
+        ctx->grad_copies = copies;
         ctx->cap_n_pad = (int)c;
         size_t cub = build_cub_temp_bytes((int)c);
         if ((e = regrow(ctx, ctx->cub_temp, cub)) != cudaSuccess)
@@ -254,10 +257,9 @@ void rgx_destroy(rgx_ctx* ctx) {
     cudaSetDevice(ctx->device);
     void* ptrs[] = {ctx->keys_in, ctx->keys_out, ctx->vals_in, ctx->vals_out, ctx->bx, ctx->by, ctx->bz, ctx->g0, ctx->g1,
                     ctx->g2, ctx->quat, ctx->sdens, ctx->rgba, ctx->grad_rows, ctx->hk, ctx->refit_counters,
-                    ctx->cub_temp, ctx->bounds, ctx->box, ctx->counters, ctx->bin_counts, ctx->bin_offsets, ctx->bin_rect,
-                    ctx->bin_depth, ctx->bin_keys_in, ctx->bin_keys_out, ctx->bin_vals_in, ctx->bin_vals_out,
+                    ctx->cub_temp, ctx->bounds, ctx->box, ctx->counters, ctx->bin_keys_in, ctx->bin_keys_out, ctx->bin_vals_in, ctx->bin_vals_out,
                     ctx->tile_first, ctx->tile_last, ctx->tile_cnt, ctx->tile_pcnt, ctx->tile_pbegin, ctx->ent_id,
-                    ctx->ent_range, ctx->ent_blk, ctx->bin_cub, ctx->bin_total_dev, ctx->tape, ctx->tape_used, ctx->ray_head, ctx->tile_dir, ctx->pair_j, ctx->pair_far};
+                    ctx->ent_range, ctx->ent_blk, ctx->bin_cub, ctx->bin_total_dev, ctx->tape, ctx->tape_used, ctx->ray_head, ctx->tile_dir, ctx->tile_iota, ctx->tile_cnt_sorted, ctx->tile_order, ctx->big_slot, ctx->big_rect};
     for (void* p : ptrs)
         if (p) cudaFree(p);
     if (ctx->bin_total_host) cudaFreeHost(ctx->bin_total_host);
@@ -349,26 +351,33 @@ static int ensure_lists(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m,
 #define RGB_(p, cnt) if ((e = regrow(ctx, ctx->p, (cnt))) != cudaSuccess) return cuda_fail(ctx, e, "tile-list workspace " #p)
     if (!ctx->bin_total_dev) {
         RGB_(bin_total_dev, 4);
-        if ((e = cudaMallocHost((void**)&ctx->bin_total_host, 4 * sizeof(int))) != cudaSuccess)
+        if ((e = cudaMallocHost((void**)&ctx->bin_total_host, 4 * sizeof(unsigned long long))) != cudaSuccess)
             return cuda_fail(ctx, e, "pinned scalar");
+        if (cudaDeviceGetAttribute(&ctx->sm_count, cudaDevAttrMultiProcessorCount, ctx->device) != cudaSuccess || ctx->sm_count <= 0)
+            ctx->sm_count = 148;
     }
-    if (ctx->n_pad > ctx->bin_n_pad) {
-        size_t c = (size_t)ctx->cap_n_pad > (size_t)ctx->n_pad ? ctx->cap_n_pad : ctx->n_pad;
-        RGB_(bin_counts, c); RGB_(bin_offsets, c); RGB_(bin_rect, c); RGB_(bin_depth, c);
-        ctx->bin_n_pad = (int)c;
+    if (ctx->n_pad > ctx->big_cap) {
+        RGB_(big_slot, (size_t)ctx->n_pad); RGB_(big_rect, (size_t)ctx->n_pad);
+        ctx->big_cap = ctx->n_pad;
     }
     if (ntiles + 1 > ctx->bin_tiles_cap) {
         size_t c = (size_t)ntiles + 1 + 64;
         RGB_(tile_first, c); RGB_(tile_last, c); RGB_(tile_cnt, c); RGB_(tile_pcnt, c); RGB_(tile_pbegin, c);
-        RGB_(tile_dir, c);
+        RGB_(tile_dir, c); RGB_(tile_iota, c); RGB_(tile_cnt_sorted, c); RGB_(tile_order, c);
         ctx->bin_tiles_cap = (int)c;
     }
-    auto need_cub = [&](size_t pairs) { return binning_cub_temp_bytes(pairs > 0 ? pairs : 1, ctx->bin_n_pad, ntiles); };
-    if (need_cub(ctx->bin_pair_cap) > ctx->bin_cub_cap) {
-        size_t c = need_cub(ctx->bin_pair_cap);
-        RGB_(bin_cub, c);
-        ctx->bin_cub_cap = c;
-    }
+    auto grow_pairs = [&](size_t pairs) -> cudaError_t {
+        size_t c = pairs + pairs / 4 + 1024;
+        cudaError_t err;
+        if ((err = regrow(ctx, ctx->bin_keys_in, c)) != cudaSuccess || (err = regrow(ctx, ctx->bin_keys_out, c)) != cudaSuccess ||
+            (err = regrow(ctx, ctx->bin_vals_in, c)) != cudaSuccess || (err = regrow(ctx, ctx->bin_vals_out, c)) != cudaSuccess)
+            return err;
+        ctx->bin_pair_cap = c;
+        return cudaSuccess;
+    };
+    // first view of a context: room for eight tiles per Gaussian; a view that needs more runs the emission twice
+    if (ctx->bin_pair_cap == 0 && (e = grow_pairs((size_t)ctx->n_pad * 8)) != cudaSuccess)
+        return cuda_fail(ctx, e, "tile-list workspace pairs");
     BinLaunch b{};
     b.n = ctx->n; b.n_pad = ctx->n_pad;
     b.bx = ctx->bx; b.by = ctx->by; b.bz = ctx->bz;
@@ -378,23 +387,23 @@ static int ensure_lists(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m,
     if (!camera_dual(*cam, b.dual)) return fail(ctx, RGX_E_INVALID, "camera axes are not linearly independent");
     b.row_begin = m->row_begin; b.row_end = m->row_end; b.tile = kBinTile;
     b.tiles_x = tiles_x; b.tiles_y = tiles_y; b.ty_first = ty_first;
-    b.counts = ctx->bin_counts; b.offsets = ctx->bin_offsets; b.rect = ctx->bin_rect; b.depth = ctx->bin_depth;
-    b.cub_temp = ctx->bin_cub; b.cub_bytes = ctx->bin_cub_cap;
     b.total_dev = ctx->bin_total_dev;
+    b.big_slot = ctx->big_slot; b.big_rect = ctx->big_rect; b.big_grid = ctx->sm_count * 4;
     ScopedTimer timer(ctx, s, 2);
-    if ((e = launch_bin_count(b, s)) != cudaSuccess) return cuda_fail(ctx, e, "tile-list count");
-    // the one host round trip of a view: the sort needs the number of pairs
-    if ((e = cudaMemcpyAsync(ctx->bin_total_host, ctx->bin_total_dev, sizeof(int), cudaMemcpyDeviceToHost, s)) != cudaSuccess ||
-        (e = cudaStreamSynchronize(s)) != cudaSuccess)
-        return cuda_fail(ctx, e, "tile-list count read-back");
-    const int total = ctx->bin_total_host[0];
-    if (total < 0 || total > (1 << 30)) return fail(ctx, RGX_E_TOO_LARGE, "more than 2^30 (tile, Gaussian) pairs in this view");
-    if ((size_t)total > ctx->bin_pair_cap) {
-        size_t c = (size_t)total + (size_t)total / 4 + 1024;
-        RGB_(bin_keys_in, c); RGB_(bin_keys_out, c); RGB_(bin_vals_in, c); RGB_(bin_vals_out, c);
-        RGB_(pair_j, c); RGB_(pair_far, c);
-        ctx->bin_pair_cap = c;
+    unsigned long long total64 = 0;
+    for (int attempt = 0; attempt < 2; ++attempt) {
+        b.keys_in = ctx->bin_keys_in; b.vals_in = ctx->bin_vals_in; b.pair_cap = ctx->bin_pair_cap;
+        if ((e = launch_bin_emit(b, s)) != cudaSuccess) return cuda_fail(ctx, e, "tile-list pairs");
+        // the one host round trip of a view: the sort needs the number of pairs
+        if ((e = cudaMemcpyAsync(ctx->bin_total_host, ctx->bin_total_dev, sizeof(unsigned long long), cudaMemcpyDeviceToHost, s)) != cudaSuccess ||
+            (e = cudaStreamSynchronize(s)) != cudaSuccess)
+            return cuda_fail(ctx, e, "tile-list pair count read-back");
+        total64 = ctx->bin_total_host[0];
+        if (total64 > (1ull << 30)) return fail(ctx, RGX_E_TOO_LARGE, "more than 2^30 (tile, Gaussian) pairs in this view");
+        if (total64 <= ctx->bin_pair_cap) break;
+        if ((e = grow_pairs((size_t)total64)) != cudaSuccess) return cuda_fail(ctx, e, "tile-list workspace pairs");
     }
+    const int total = (int)total64;
     const size_t ent_need = (((size_t)total + 32u * (size_t)ntiles + 31) / 32) * 32 + 32;
     if (ent_need > ctx->bin_ent_cap) {
         size_t c = ent_need + ent_need / 4;
@@ -402,21 +411,22 @@ static int ensure_lists(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m,
         RGB_(ent_id, c); RGB_(ent_range, c); RGB_(ent_blk, c / 32 + 1);
         ctx->bin_ent_cap = c;
     }
-    if (need_cub(ctx->bin_pair_cap) > ctx->bin_cub_cap) {
-        size_t c = need_cub(ctx->bin_pair_cap);
-        RGB_(bin_cub, c);
-        ctx->bin_cub_cap = c;
+    const size_t cub_need = binning_cub_temp_bytes(ctx->bin_pair_cap, ntiles);
+    if (cub_need > ctx->bin_cub_cap) {
+        RGB_(bin_cub, cub_need);
+        ctx->bin_cub_cap = cub_need;
     }
 #undef RGB_
     b.keys_in = ctx->bin_keys_in; b.keys_out = ctx->bin_keys_out; b.vals_in = ctx->bin_vals_in; b.vals_out = ctx->bin_vals_out;
+    b.pair_cap = ctx->bin_pair_cap;
     b.tile_first = ctx->tile_first; b.tile_last = ctx->tile_last; b.tile_cnt = ctx->tile_cnt; b.tile_pcnt = ctx->tile_pcnt;
     b.tile_pbegin = ctx->tile_pbegin;
+    b.tile_iota = ctx->tile_iota; b.tile_cnt_sorted = ctx->tile_cnt_sorted; b.tile_order = ctx->tile_order;
     b.ent_id = ctx->ent_id; b.ent_range = ctx->ent_range; b.blk = ctx->ent_blk;
-    b.pair_j = ctx->pair_j; b.pair_far = ctx->pair_far;
     b.cub_temp = ctx->bin_cub; b.cub_bytes = ctx->bin_cub_cap;
     if ((e = launch_bin_fill(b, total, s)) != cudaSuccess) return cuda_fail(ctx, e, "tile-list fill");
     ctx->lists.ent_id = ctx->ent_id; ctx->lists.ent_range = ctx->ent_range; ctx->lists.blk = ctx->ent_blk;
-    ctx->lists.tile_pbegin = ctx->tile_pbegin; ctx->lists.tile_cnt = ctx->tile_cnt;
+    ctx->lists.tile_pbegin = ctx->tile_pbegin; ctx->lists.tile_cnt = ctx->tile_cnt; ctx->lists.tile_order = ctx->tile_order;
     ctx->lists.tiles_x = tiles_x; ctx->lists.tiles_y = tiles_y; ctx->lists.ty_first = ty_first;
     ctx->lists_cam = *cam;
     ctx->lists_row_begin = m->row_begin; ctx->lists_row_end = m->row_end;
@@ -472,24 +482,41 @@ int rgx_forward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, con
             if ((e = regrow(ctx, ctx->ray_head, (size_t)rays)) != cudaSuccess) return cuda_fail(ctx, e, "tape");
             ctx->ray_head_cap = rays;
         }
-        // room: 256 ints per ray to begin with; more when the previous recording came close to the end
-        long long want = rows_rays * 256 + 1024;
+        // room: 1024 ints per ray to begin with; what the previous recording asked for and half as much again when
+        // that came close to the end (the counter keeps counting past the end), within half of the free memory
+        long long want = rows_rays * 1024 + 4096;
         const long long seen = (long long)*ctx->tape_used_host;
-        if (seen > (ctx->tape_cap / 4) * 3) want = want > seen * 2 ? want : seen * 2;
+        if (seen > (ctx->tape_cap / 8) * 7) want = want > seen + seen / 2 ? want : seen + seen / 2;
         if (want > ctx->tape_cap) {
-            if ((e = regrow(ctx, ctx->tape, (size_t)want)) != cudaSuccess) return cuda_fail(ctx, e, "tape");
-            ctx->tape_cap = want;
+            size_t free_b = 0, total_b = 0;
+            if (cudaMemGetInfo(&free_b, &total_b) == cudaSuccess) {
+                const long long room = (long long)((free_b + (size_t)ctx->tape_cap * sizeof(int)) / 2 / sizeof(int));
+                if (want > room) want = room;
+            }
+        }
+        if (want > ctx->tape_cap) {
+            if ((e = regrow(ctx, ctx->tape, (size_t)want)) != cudaSuccess) {
+                // no memory for a larger tape: render without one, the backward searches again
+                (void)cudaGetLastError();
+                ctx->tape = nullptr;
+                ctx->tape_cap = 0;
+            } else {
+                ctx->tape_cap = want;
+            }
         }
         if ((e = cudaMemsetAsync(ctx->tape_used, 0, sizeof(unsigned long long), s)) != cudaSuccess)
             return cuda_fail(ctx, e, "tape");
-        L.tape = ctx->tape; L.tape_used = ctx->tape_used; L.tape_cap = ctx->tape_cap; L.ray_head = ctx->ray_head;
+        if (ctx->tape) {
+            L.tape = ctx->tape; L.tape_used = ctx->tape_used; L.tape_cap = ctx->tape_cap; L.ray_head = ctx->ray_head;
+        }
     }
+    const bool recorded = L.tape != nullptr;
     {
         ScopedTimer timer(ctx, s, 0);
         e = launch_march_forward(L, s);
     }
     if (e != cudaSuccess) return cuda_fail(ctx, e, "forward march");
-    if (record) {
+    if (recorded) {
         cudaMemcpyAsync(ctx->tape_used_host, ctx->tape_used, sizeof(unsigned long long), cudaMemcpyDeviceToHost, s);
         ctx->tape_valid = true;
         ctx->tape_build_id = ctx->build_id;
@@ -514,7 +541,7 @@ int rgx_backward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, co
     cudaSetDevice(ctx->device);
     cudaStream_t s = (cudaStream_t)stream;
     if ((rc = run_colors(ctx, scene, cam->eye, s))) return rc;
-    cudaError_t e = cudaMemsetAsync(ctx->grad_rows, 0, sizeof(float4) * 4 * (size_t)ctx->n_pad, s);
+    cudaError_t e = cudaMemsetAsync(ctx->grad_rows, 0, sizeof(float4) * 4 * (size_t)ctx->n_pad * (size_t)ctx->grad_copies, s);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "backward memset");
     if (!(march->flags & (RGX_FLAG_BRUTE_FORCE | RGX_FLAG_PER_RAY_SEARCH))) {
         if ((rc = ensure_lists(ctx, cam, march, s))) return rc;
@@ -525,7 +552,7 @@ int rgx_backward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, co
         std::memcmp(&ctx->tape_cam, cam, sizeof(rgx_camera)) == 0) {
         L.tape = ctx->tape; L.tape_used = ctx->tape_used; L.tape_cap = ctx->tape_cap; L.ray_head = ctx->ray_head;
     }
-    L.rgb_in = rgb; L.dl_drgb = dL_drgb; L.grad_rows = ctx->grad_rows;
+    L.rgb_in = rgb; L.dl_drgb = dL_drgb; L.grad_rows = ctx->grad_rows; L.grad_copies = ctx->grad_copies;
     {
         ScopedTimer timer(ctx, s, 1);
         e = launch_march_backward(L, s);
@@ -536,7 +563,8 @@ int rgx_backward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, co
     f.gr = *grads;
     std::memcpy(f.eye, cam->eye, sizeof(f.eye));
     f.perm = ctx->vals_out;
-    f.grad_rows = ctx->grad_rows;
+    f.grad_rows = ctx->grad_rows; f.grad_copies = ctx->grad_copies; f.n_pad = ctx->n_pad;
+    f.quat = ctx->quat; f.sdens = ctx->sdens; f.hk = ctx->hk;
     f.flags = march->flags;
     e = launch_finalize(f, s);
     return e == cudaSuccess ? RGX_OK : cuda_fail(ctx, e, "gradient finalise");

@@ -15,6 +15,7 @@
 #include "device_math.cuh"
 #include <cub/device/device_radix_sort.cuh>
 #include <cub/device/device_scan.cuh>
+#include <cub/block/block_scan.cuh>
 
 namespace rgx {
 
@@ -68,24 +69,50 @@ __device__ __forceinline__ int project_corners(const Projector& p, const float* 
 }
 
 // A convex body that straddles the eye plane has no bounded projection.  Its tile
-// columns are found one by one instead: column [a_lo, a_hi] (in x/z) can only be
-// touched if some corner lies on the inner side of each of its two bounding planes
-// x - a z = 0 through the eye.  Conservative, exact per plane.  Same for rows.
+// columns are found from the planes through the eye instead: column [a_lo, a_hi] (in
+// x/z) can only be touched if some corner lies on the inner side of each of its two
+// bounding planes x - a z = 0, that is unless x_i - a_lo z_i < 0 for every corner or
+// x_i - a_hi z_i > 0 for every corner.  Each of the two holds for a in an open interval
+// whose ends are ratios x_i / z_i, so the eight corners are looked at once and a column
+// costs two comparisons.  Conservative (a tolerance on every corner), exact per plane.
+// Same for rows.  Returns the first and last pixel of the touched columns.
 __device__ __forceinline__ void straddle_tiles(const float* xc, const float* zc, float scale, float offset, int n_tiles,
                                                int tile, int n_pix, float& lo_pix, float& hi_pix) {
-    lo_pix = INFINITY; hi_pix = -INFINITY;
-    for (int c = 0; c < n_tiles; ++c) {
-        const float p0 = (float)(c * tile), p1 = (float)min(c * tile + tile - 1, n_pix - 1);
-        const float a_lo = (p0 - 0.02f - offset) / scale, a_hi = (p1 + 0.02f - offset) / scale;
-        float g = -INFINITY, h = INFINITY, mag = 0.f;
+    const float inv_scale = 1.0f / scale;
+    const float a_first = (-0.02f - offset) * inv_scale, a_last = ((float)(n_pix - 1) + 0.02f - offset) * inv_scale;
+    const float amax = 2.0f * fmaxf(fabsf(a_first), fabsf(a_last));
+    float gl = -INFINITY, gh = INFINITY, hl = -INFINITY, hh = INFINITY;   // all below: a in (gl, gh); all above: a in (hl, hh)
+    bool okg = true, okh = true;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            g = fmaxf(g, xc[i] - a_lo * zc[i]);
-            h = fminf(h, xc[i] - a_hi * zc[i]);
-            mag = fmaxf(mag, fabsf(xc[i]) + (fabsf(a_lo) + fabsf(a_hi)) * fabsf(zc[i]));
+    for (int i = 0; i < 8; ++i) {
+        const float tol = 1e-5f * (fabsf(xc[i]) + amax * fabsf(zc[i]));
+        const float up = xc[i] + tol, dn = xc[i] - tol;
+        if (zc[i] > 1e-20f) {
+            gl = fmaxf(gl, up / zc[i]);
+            hh = fminf(hh, dn / zc[i]);
+        } else if (zc[i] < -1e-20f) {
+            gh = fminf(gh, up / zc[i]);
+            hl = fmaxf(hl, dn / zc[i]);
+        } else {
+            okg = okg && up < 0.f;
+            okh = okh && dn > 0.f;
         }
-        if (g >= -1e-5f * mag && h <= 1e-5f * mag) { lo_pix = fminf(lo_pix, p0); hi_pix = fmaxf(hi_pix, p1); }
     }
+    auto touched = [&](int c, float& p0, float& p1) {
+        p0 = (float)(c * tile);
+        p1 = (float)min(c * tile + tile - 1, n_pix - 1);
+        const float a_lo = (p0 - 0.02f - offset) * inv_scale, a_hi = (p1 + 0.02f - offset) * inv_scale;
+        const bool all_below = okg && a_lo > gl && a_lo < gh;
+        const bool all_above = okh && a_hi > hl && a_hi < hh;
+        return !(all_below || all_above);
+    };
+    lo_pix = INFINITY; hi_pix = -INFINITY;
+    int c0 = 0;
+    float p0, p1;
+    for (; c0 < n_tiles; ++c0)
+        if (touched(c0, p0, p1)) { lo_pix = p0; hi_pix = p1; break; }
+    for (int c = n_tiles - 1; c > c0; --c)
+        if (touched(c, p0, p1)) { hi_pix = p1; break; }
 }
 
 __device__ __forceinline__ float3 pixel_dir(const rgx_camera& c, float px, float py) {
@@ -136,7 +163,8 @@ __device__ __forceinline__ bool pair_range(const float* eye, float4 td, const Pa
         if (fabsf(d[a]) < 1e-12f) {
             if (o[a] < lo[a] || o[a] > hi[a]) return false;
         } else {
-            float t0 = (lo[a] - o[a]) / d[a], t1 = (hi[a] - o[a]) / d[a];
+            const float inv = __fdividef(1.0f, d[a]);      // the margins below cover its rounding
+            float t0 = (lo[a] - o[a]) * inv, t1 = (hi[a] - o[a]) * inv;
             tn = fmaxf(tn, fminf(t0, t1));
             tf = fminf(tf, fmaxf(t0, t1));
         }
@@ -155,7 +183,8 @@ __device__ __forceinline__ bool pair_range(const float* eye, float4 td, const Pa
     if (disc < -1e-5f * mag) return false;
     if (qa > 1e-30f) {
         const float sq = sqrtf(fmaxf(disc, 0.f) + 1e-5f * mag);
-        const float r1 = (qb - sq) / qa, r2 = (qb + sq) / qa;
+        const float inv_qa = __fdividef(1.0f, qa);
+        const float r1 = (qb - sq) * inv_qa, r2 = (qb + sq) * inv_qa;
         tn = fmaxf(tn, r1);
         tf = fminf(tf, r2);
     }
@@ -164,137 +193,264 @@ __device__ __forceinline__ bool pair_range(const float* eye, float4 td, const Pa
     return tn <= tf;
 }
 
-__device__ __forceinline__ PairGeom load_pair_geom(const BinLaunch& b, int j) {
+// How a (tile, Gaussian) pair is packed into its 64-bit sort key, most significant first:
+// tile | near distance (sign dropped, low mantissa bits dropped) | sorted slot of the Gaussian.
+// Every key is distinct, so the sorted order does not depend on the order of emission.
+struct KeyLayout {
+    int tile_bits, near_bits, id_bits;
+};
+
+__host__ __device__ inline KeyLayout key_layout(int ntiles, int n_pad) {
+    KeyLayout k;
+    k.tile_bits = 1;
+    while ((1 << k.tile_bits) < ntiles) ++k.tile_bits;
+    k.id_bits = 1;
+    while ((1ll << k.id_bits) < (long long)n_pad) ++k.id_bits;
+    int avail = 64 - k.tile_bits - k.id_bits;
+    k.near_bits = avail < 24 ? avail : 24;
+    // a whole number of 8-bit sort passes if that costs no more than a few mantissa bits
+    while (((k.tile_bits + k.near_bits + k.id_bits) & 7) != 0 && k.near_bits > 20) --k.near_bits;
+    return k;
+}
+
+// The near distance as the list stores it: rounded down to what the key keeps, so that the
+// order of the keys is exactly the order of the stored distances.
+__device__ __forceinline__ unsigned near_quantised(float tn, int near_bits) { return (__float_as_uint(tn) << 1) >> (32 - near_bits); }
+__device__ __forceinline__ float near_stored(unsigned q, int near_bits) { return __uint_as_float((q << (32 - near_bits)) >> 1); }
+
+// What pair_range needs to know of a Gaussian, from its box, whitening map, scales, quaternion and hk.
+__device__ __forceinline__ PairGeom make_pair_geom(const float* eye, float2 bx, float2 by, float2 bz, float4 g0, float4 g1,
+                                                   float4 g2, float4 sd, float4 q, float kk) {
     PairGeom g;
-    g.bx = b.bx[j]; g.by = b.by[j]; g.bz = b.bz[j];
-    g.g0 = b.g0[j]; g.g1 = b.g1[j]; g.g2 = b.g2[j];
-    g.far_box = b.depth[j].y;
-    float4 sd = b.sdens[j], q = b.quat[j];
-    float k = sqrtf(2.0f * 0.6931471805599453f * b.hk[j]);
+    g.bx = bx; g.by = by; g.bz = bz;
+    g.g0 = g0; g.g1 = g1; g.g2 = g2;
+    float fx = fmaxf(fabsf(bx.x - eye[0]), fabsf(bx.y - eye[0])), fy = fmaxf(fabsf(by.x - eye[1]), fabsf(by.y - eye[1])),
+          fz = fmaxf(fabsf(bz.x - eye[2]), fabsf(bz.y - eye[2]));
+    g.far_box = sqrtf(fx * fx + fy * fy + fz * fz) * (1.0f + 1e-5f) + 1e-6f;
     float smin = fminf(sd.x, fminf(sd.y, sd.z));
     float qn = q.x * q.x + q.y * q.y + q.z * q.z + q.w * q.w;
-    g.rho_scale = 1.02f * fmaxf(1.0f, qn) / (k * smin);
+    g.rho_scale = 1.02f * fmaxf(1.0f, qn) / (kk * smin);
     return g;
 }
 
-// One thread per sorted slot: tile rectangle (box rectangle cut by the rectangle of
-// the oriented box of the truncation ellipsoid), distance range, number of tiles.
-__global__ void __launch_bounds__(256) bin_count_kernel(BinLaunch b) {
-    int j = blockIdx.x * blockDim.x + threadIdx.x;
-    if (j >= b.n_pad) return;
+__device__ __forceinline__ unsigned long long pair_key(const KeyLayout& kl, unsigned tile, float tn, unsigned slot) {
+    return ((unsigned long long)tile << (kl.near_bits + kl.id_bits)) |
+           ((unsigned long long)near_quantised(tn, kl.near_bits) << kl.id_bits) | (unsigned long long)slot;
+}
+
+constexpr int kEmitThreads = 256;
+constexpr int kBigRect = 48;       // Gaussians that cover more tiles than this are left to bin_emit_big_kernel
+constexpr int kEmitBuf = 1280;     // pairs gathered in shared memory between two appends to the global arrays
+
+struct EmitShared {
+    PairGeom geom[kEmitThreads];
+    uint2 rect[kEmitThreads];
+    int prefix[kEmitThreads + 1];
+    unsigned long long keys[kEmitBuf];
+    float fars[kEmitBuf];
+    int nbuf;
+    unsigned long long base;
+};
+
+// Appends the gathered pairs to the global arrays: one atomic per call and block.  Pairs
+// past the capacity are counted but not written; the host then grows the arrays and
+// runs the emission again.
+__device__ __forceinline__ void emit_flush(const BinLaunch& b, EmitShared& sh, int tid) {
+    const int n = sh.nbuf;
+    if (tid == 0 && n > 0) sh.base = atomicAdd(b.total_dev, (unsigned long long)n);
+    __syncthreads();
+    const unsigned long long base = sh.base;
+    for (int i = tid; i < n; i += kEmitThreads) {
+        const unsigned long long k = base + (unsigned long long)i;
+        if (k < b.pair_cap) { b.keys_in[k] = sh.keys[i]; b.vals_in[k] = __float_as_uint(sh.fars[i]); }
+    }
+    __syncthreads();
+    if (tid == 0) sh.nbuf = 0;
+    __syncthreads();
+}
+
+// One block per 256 sorted slots.  First every thread finds its Gaussian's rectangle of
+// tiles (box rectangle cut by the rectangle of the oriented box of the truncation
+// ellipsoid).  Then the block walks all (Gaussian, tile) candidates of its 256 Gaussians
+// together, one candidate per thread and round, whatever Gaussian it belongs to -- a
+// Gaussian that covers the screen costs its block a few rounds, not one thread thousands
+// of iterations -- and keeps the pairs in which some ray of the tile can meet the Gaussian.
+__global__ void __launch_bounds__(kEmitThreads) bin_emit_kernel(BinLaunch b) {
+    __shared__ EmitShared sh;
+    using Scan = cub::BlockScan<int, kEmitThreads>;
+    __shared__ typename Scan::TempStorage scan_tmp;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int j = blockIdx.x * kEmitThreads + tid;
     int count = 0;
-    uint2 rect = make_uint2(0u, 0u);
-    float2 depth = make_float2(INFINITY, -INFINITY);
-    float2 bx = b.bx[j], by = b.by[j], bz = b.bz[j];
-    if (j < b.n && bx.x <= bx.y) {
-        const Projector p = make_projector(b);
-        const int W = b.cam.width, H = b.cam.height;
-        const int tiles_x_all = (W + b.tile - 1) / b.tile, tiles_y_all = (H + b.tile - 1) / b.tile;
-        float xc[8], yc[8], zc[8];
+    if (j < b.n) {
+        const float2 bx = b.bx[j], by = b.by[j], bz = b.bz[j];
+        if (bx.x <= bx.y) {
+            const Projector p = make_projector(b);
+            const int W = b.cam.width, H = b.cam.height;
+            const int tiles_x_all = (W + b.tile - 1) / b.tile, tiles_y_all = (H + b.tile - 1) / b.tile;
+            float xc[8], yc[8], zc[8];
 #pragma unroll
-        for (int c = 0; c < 8; ++c)
-            to_camera(p, (c & 1) ? bx.y : bx.x, (c & 2) ? by.y : by.x, (c & 4) ? bz.y : bz.x, xc[c], yc[c], zc[c]);
-        float lox, hix, loy, hiy;
-        int kind = project_corners(p, xc, yc, zc, lox, hix, loy, hiy);
-        if (kind == 2) {
-            straddle_tiles(xc, zc, p.sx, p.ox, tiles_x_all, b.tile, W, lox, hix);
-            straddle_tiles(yc, zc, p.sy, p.oy, tiles_y_all, b.tile, H, loy, hiy);
-        }
-        if (kind != 0) {
-            // oriented box of the ellipsoid {x : |S^-1 R^T (x - p)| <= k}: centre +- k s_a col_a
-            float4 sd = b.sdens[j], q = b.quat[j], g0 = b.g0[j];
-            float k = sqrtf(2.0f * 0.6931471805599453f * b.hk[j]) * 1.0001f;
-            float3 U, V, Wc;
-            quat_to_columns(q, U, V, Wc);
-            float3 e0 = U * (k * sd.x), e1 = V * (k * sd.y), e2 = Wc * (k * sd.z);
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                float sa = (c & 1) ? 1.f : -1.f, sb = (c & 2) ? 1.f : -1.f, sc = (c & 4) ? 1.f : -1.f;
-                to_camera(p, g0.x + sa * e0.x + sb * e1.x + sc * e2.x, g0.y + sa * e0.y + sb * e1.y + sc * e2.y,
-                          g0.z + sa * e0.z + sb * e1.z + sc * e2.z, xc[c], yc[c], zc[c]);
+            for (int c = 0; c < 8; ++c)
+                to_camera(p, (c & 1) ? bx.y : bx.x, (c & 2) ? by.y : by.x, (c & 4) ? bz.y : bz.x, xc[c], yc[c], zc[c]);
+            float lox, hix, loy, hiy;
+            int kind = project_corners(p, xc, yc, zc, lox, hix, loy, hiy);
+            if (kind == 2) {
+                straddle_tiles(xc, zc, p.sx, p.ox, tiles_x_all, b.tile, W, lox, hix);
+                straddle_tiles(yc, zc, p.sy, p.oy, tiles_y_all, b.tile, H, loy, hiy);
             }
-            float olx, ohx, oly, ohy;
-            int okind = project_corners(p, xc, yc, zc, olx, ohx, oly, ohy);
-            if (okind == 0) kind = 0;
-            else {
-                if (okind == 2) {
-                    straddle_tiles(xc, zc, p.sx, p.ox, tiles_x_all, b.tile, W, olx, ohx);
-                    straddle_tiles(yc, zc, p.sy, p.oy, tiles_y_all, b.tile, H, oly, ohy);
+            const float4 sd = b.sdens[j], q = b.quat[j], g0 = b.g0[j];
+            const float kk = sqrtf(2.0f * 0.6931471805599453f * b.hk[j]);
+            if (kind != 0) {
+                // oriented box of the ellipsoid {x : |S^-1 R^T (x - p)| <= k}: centre +- k s_a col_a
+                const float k = kk * 1.0001f;
+                float3 U, V, Wc;
+                quat_to_columns(q, U, V, Wc);
+                float3 e0 = U * (k * sd.x), e1 = V * (k * sd.y), e2 = Wc * (k * sd.z);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    float sa = (c & 1) ? 1.f : -1.f, sb = (c & 2) ? 1.f : -1.f, sc = (c & 4) ? 1.f : -1.f;
+                    to_camera(p, g0.x + sa * e0.x + sb * e1.x + sc * e2.x, g0.y + sa * e0.y + sb * e1.y + sc * e2.y,
+                              g0.z + sa * e0.z + sb * e1.z + sc * e2.z, xc[c], yc[c], zc[c]);
                 }
-                lox = fmaxf(lox, olx); hix = fminf(hix, ohx); loy = fmaxf(loy, oly); hiy = fminf(hiy, ohy);
+                float olx, ohx, oly, ohy;
+                int okind = project_corners(p, xc, yc, zc, olx, ohx, oly, ohy);
+                if (okind == 0) kind = 0;
+                else {
+                    if (okind == 2) {
+                        straddle_tiles(xc, zc, p.sx, p.ox, tiles_x_all, b.tile, W, olx, ohx);
+                        straddle_tiles(yc, zc, p.sy, p.oy, tiles_y_all, b.tile, H, oly, ohy);
+                    }
+                    lox = fmaxf(lox, olx); hix = fminf(hix, ohx); loy = fmaxf(loy, oly); hiy = fminf(hiy, ohy);
+                }
             }
-        }
-        if (kind != 0) {
-            // rays sit at integer pixel coordinates; keep a small safety margin for rounding
-            const float m = 0.02f;
-            float fx0 = ceilf(lox - m - 1e-5f * fabsf(lox)), fx1 = floorf(hix + m + 1e-5f * fabsf(hix));
-            float fy0 = ceilf(loy - m - 1e-5f * fabsf(loy)), fy1 = floorf(hiy + m + 1e-5f * fabsf(hiy));
-            fx0 = fmaxf(fx0, 0.f); fx1 = fminf(fx1, (float)W - 1.f);
-            fy0 = fmaxf(fy0, (float)b.row_begin); fy1 = fminf(fy1, (float)b.row_end - 1.f);
-            if (fx0 <= fx1 && fy0 <= fy1) {
-                unsigned tx0 = (unsigned)fx0 / b.tile, tx1 = (unsigned)fx1 / b.tile;
-                unsigned ty0 = (unsigned)fy0 / b.tile - b.ty_first, ty1 = (unsigned)fy1 / b.tile - b.ty_first;
-                rect = make_uint2(tx0 | (tx1 << 16), ty0 | (ty1 << 16));
-                count = (int)((tx1 - tx0 + 1) * (ty1 - ty0 + 1));
-                float nx = fmaxf(fmaxf(bx.x - p.eye[0], p.eye[0] - bx.y), 0.f), ny = fmaxf(fmaxf(by.x - p.eye[1], p.eye[1] - by.y), 0.f),
-                      nz = fmaxf(fmaxf(bz.x - p.eye[2], p.eye[2] - bz.y), 0.f);
-                float fx = fmaxf(fabsf(bx.x - p.eye[0]), fabsf(bx.y - p.eye[0])), fy = fmaxf(fabsf(by.x - p.eye[1]), fabsf(by.y - p.eye[1])),
-                      fz = fmaxf(fabsf(bz.x - p.eye[2]), fabsf(bz.y - p.eye[2]));
-                depth.x = fmaxf(sqrtf(nx * nx + ny * ny + nz * nz) * (1.0f - 1e-5f) - 1e-6f, 0.f);
-                depth.y = sqrtf(fx * fx + fy * fy + fz * fz) * (1.0f + 1e-5f) + 1e-6f;
+            if (kind != 0) {
+                // rays sit at integer pixel coordinates; keep a small safety margin for rounding
+                const float m = 0.02f;
+                float fx0 = ceilf(lox - m - 1e-5f * fabsf(lox)), fx1 = floorf(hix + m + 1e-5f * fabsf(hix));
+                float fy0 = ceilf(loy - m - 1e-5f * fabsf(loy)), fy1 = floorf(hiy + m + 1e-5f * fabsf(hiy));
+                fx0 = fmaxf(fx0, 0.f); fx1 = fminf(fx1, (float)W - 1.f);
+                fy0 = fmaxf(fy0, (float)b.row_begin); fy1 = fminf(fy1, (float)b.row_end - 1.f);
+                if (fx0 <= fx1 && fy0 <= fy1) {
+                    unsigned tx0 = (unsigned)fx0 / b.tile, tx1 = (unsigned)fx1 / b.tile;
+                    unsigned ty0 = (unsigned)fy0 / b.tile - b.ty_first, ty1 = (unsigned)fy1 / b.tile - b.ty_first;
+                    sh.rect[tid] = make_uint2(tx0 | (tx1 << 16), ty0 | (ty1 << 16));
+                    count = (int)((tx1 - tx0 + 1) * (ty1 - ty0 + 1));
+                    if (count > kBigRect) {
+                        const unsigned long long at = atomicAdd(b.total_dev + 1, 1ull);
+                        b.big_slot[at] = j;
+                        b.big_rect[at] = sh.rect[tid];
+                        count = 0;
+                    }
+                    const PairGeom g = make_pair_geom(p.eye, bx, by, bz, g0, b.g1[j], b.g2[j], sd, q, kk);
+                    sh.geom[tid] = g;
+                }
             }
         }
     }
-    b.rect[j] = rect;
-    b.depth[j] = depth;
-    if (count > 0) {      // keep only the tiles some ray of which can actually meet the Gaussian
-        const PairGeom g = load_pair_geom(b, j);
-        unsigned tx0 = rect.x & 0xffffu, tx1 = rect.x >> 16, ty0 = rect.y & 0xffffu, ty1 = rect.y >> 16;
-        int kept = 0;
-        for (unsigned ty = ty0; ty <= ty1; ++ty)
-            for (unsigned tx = tx0; tx <= tx1; ++tx) {
-                float tn, tf;
-                kept += pair_range(b.cam.eye, b.tile_dir[ty * (unsigned)b.tiles_x + tx], g, tn, tf) ? 1 : 0;
+    int excl, total;
+    Scan(scan_tmp).ExclusiveSum(count, excl, total);
+    sh.prefix[tid] = excl;
+    if (tid == 0) { sh.prefix[kEmitThreads] = total; sh.nbuf = 0; }
+    __syncthreads();
+
+    const KeyLayout kl = key_layout(b.tiles_x * ((b.cam.height + b.tile - 1) / b.tile), b.n_pad);
+    for (int it0 = 0; it0 < total; it0 += kEmitThreads) {
+        if (sh.nbuf > kEmitBuf - kEmitThreads) emit_flush(b, sh, tid);      // same decision in every thread
+        const int item = it0 + tid;
+        bool keep = false;
+        unsigned long long key = 0;
+        float tf = 0.f;
+        if (item < total) {
+            int lo = 0, hi = kEmitThreads - 1;
+            while (lo < hi) {                       // last slot whose first candidate is not after `item`
+                const int mid = (lo + hi + 1) >> 1;
+                if (sh.prefix[mid] <= item) lo = mid; else hi = mid - 1;
             }
-        count = kept;
-    }
-    b.counts[j] = count;
-}
-
-__global__ void bin_total_kernel(BinLaunch b) {
-    if (threadIdx.x == 0 && blockIdx.x == 0) {
-        long long t = b.n_pad > 0 ? (long long)b.offsets[b.n_pad - 1] + b.counts[b.n_pad - 1] : 0;
-        b.total_dev[0] = (int)t;
-    }
-}
-
-__global__ void __launch_bounds__(256) bin_emit_kernel(BinLaunch b) {
-    int j = blockIdx.x * blockDim.x + threadIdx.x;
-    if (j >= b.n_pad) return;
-    if (b.counts[j] == 0) return;
-    uint2 rect = b.rect[j];
-    unsigned tx0 = rect.x & 0xffffu, tx1 = rect.x >> 16, ty0 = rect.y & 0xffffu, ty1 = rect.y >> 16;
-    const PairGeom g = load_pair_geom(b, j);
-    size_t k = (size_t)b.offsets[j];
-    for (unsigned ty = ty0; ty <= ty1; ++ty)
-        for (unsigned tx = tx0; tx <= tx1; ++tx) {
-            const unsigned t = ty * (unsigned)b.tiles_x + tx;
-            float tn, tf;
-            if (!pair_range(b.cam.eye, b.tile_dir[t], g, tn, tf)) continue;
-            b.keys_in[k] = ((uint64_t)t << 32) | (uint64_t)__float_as_uint(tn);
-            b.vals_in[k] = (uint32_t)k;          // emission index; the sort carries it to the pair's data
-            b.pair_j[k] = j;
-            b.pair_far[k] = tf;
-            ++k;
+            const uint2 rect = sh.rect[lo];
+            const unsigned tx0 = rect.x & 0xffffu, tx1 = rect.x >> 16, ty0 = rect.y & 0xffffu;
+            const unsigned w = tx1 - tx0 + 1, local = (unsigned)(item - sh.prefix[lo]);
+            const unsigned t = (ty0 + local / w) * (unsigned)b.tiles_x + tx0 + local % w;
+            float tn;
+            keep = pair_range(b.cam.eye, b.tile_dir[t], sh.geom[lo], tn, tf);
+            if (keep) key = pair_key(kl, t, tn, (unsigned)(blockIdx.x * kEmitThreads + lo));
         }
+        const unsigned m = __ballot_sync(kFullMask, keep);
+        if (m) {
+            int at = 0;
+            if (lane == __ffs(m) - 1) at = atomicAdd(&sh.nbuf, __popc(m));
+            at = __shfl_sync(kFullMask, at, __ffs(m) - 1) + __popc(m & ((1u << lane) - 1u));
+            if (keep) { sh.keys[at] = key; sh.fars[at] = tf; }
+        }
+        __syncthreads();
+    }
+    emit_flush(b, sh, tid);
 }
 
-__global__ void __launch_bounds__(256) bin_ranges_kernel(BinLaunch b, int total) {
+// The Gaussians that cover many tiles: warps take them one at a time from the list the
+// kernel above left, 32 tiles per step, and gather the kept pairs in a buffer of their
+// own in shared memory.
+constexpr int kBigWarps = 8;
+constexpr int kBigBuf = 256;
+
+__global__ void __launch_bounds__(kBigWarps * 32) bin_emit_big_kernel(BinLaunch b) {
+    __shared__ unsigned long long s_keys[kBigWarps][kBigBuf];
+    __shared__ float s_fars[kBigWarps][kBigBuf];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    unsigned long long* keys = s_keys[warp];
+    float* fars = s_fars[warp];
+    const unsigned long long nbig = b.total_dev[1];
+    const KeyLayout kl = key_layout(b.tiles_x * ((b.cam.height + b.tile - 1) / b.tile), b.n_pad);
+    int nbuf = 0;
+    auto flush = [&]() {
+        unsigned long long base = 0;
+        if (lane == 0 && nbuf > 0) base = atomicAdd(b.total_dev, (unsigned long long)nbuf);
+        base = __shfl_sync(kFullMask, base, 0);
+        __syncwarp();
+        for (int i = lane; i < nbuf; i += 32) {
+            const unsigned long long k = base + (unsigned long long)i;
+            if (k < b.pair_cap) { b.keys_in[k] = keys[i]; b.vals_in[k] = __float_as_uint(fars[i]); }
+        }
+        nbuf = 0;
+        __syncwarp();
+    };
+    while (true) {
+        unsigned long long idx = 0;
+        if (lane == 0) idx = atomicAdd(b.total_dev + 2, 1ull);
+        idx = __shfl_sync(kFullMask, idx, 0);
+        if (idx >= nbig) break;
+        const int j = b.big_slot[idx];
+        const uint2 rect = b.big_rect[idx];
+        const float4 sd = b.sdens[j];
+        const float kk = sqrtf(2.0f * 0.6931471805599453f * b.hk[j]);
+        const PairGeom g = make_pair_geom(b.cam.eye, b.bx[j], b.by[j], b.bz[j], b.g0[j], b.g1[j], b.g2[j], sd, b.quat[j], kk);
+        const unsigned tx0 = rect.x & 0xffffu, tx1 = rect.x >> 16, ty0 = rect.y & 0xffffu, ty1 = rect.y >> 16;
+        const unsigned w = tx1 - tx0 + 1, count = w * (ty1 - ty0 + 1);
+        for (unsigned it0 = 0; it0 < count; it0 += 32) {
+            const unsigned item = it0 + lane;
+            bool keep = false;
+            unsigned long long key = 0;
+            float tf = 0.f;
+            if (item < count) {
+                const unsigned t = (ty0 + item / w) * (unsigned)b.tiles_x + tx0 + item % w;
+                float tn;
+                keep = pair_range(b.cam.eye, b.tile_dir[t], g, tn, tf);
+                if (keep) key = pair_key(kl, t, tn, (unsigned)j);
+            }
+            const unsigned m = __ballot_sync(kFullMask, keep);
+            if (nbuf + __popc(m) > kBigBuf) flush();
+            if (keep) { const int at = nbuf + __popc(m & ((1u << lane) - 1u)); keys[at] = key; fars[at] = tf; }
+            nbuf += __popc(m);
+        }
+    }
+    flush();
+}
+
+__global__ void __launch_bounds__(256) bin_ranges_kernel(BinLaunch b, int total, int tile_shift) {
     int k = blockIdx.x * blockDim.x + threadIdx.x;
     if (k >= total) return;
-    int t = (int)(b.keys_out[k] >> 32);
-    if (k == 0 || (int)(b.keys_out[k - 1] >> 32) != t) b.tile_first[t] = k;
-    if (k == total - 1 || (int)(b.keys_out[k + 1] >> 32) != t) b.tile_last[t] = k + 1;
+    int t = (int)(b.keys_out[k] >> tile_shift);
+    if (k == 0 || (int)(b.keys_out[k - 1] >> tile_shift) != t) b.tile_first[t] = k;
+    if (k == total - 1 || (int)(b.keys_out[k + 1] >> tile_shift) != t) b.tile_last[t] = k + 1;
 }
 
 __global__ void bin_tile_counts_kernel(BinLaunch b, int ntiles) {
@@ -303,6 +459,7 @@ __global__ void bin_tile_counts_kernel(BinLaunch b, int ntiles) {
     int cnt = b.tile_last[t] - b.tile_first[t];
     b.tile_cnt[t] = cnt;
     b.tile_pcnt[t] = ((cnt + 31) / 32) * 32;
+    b.tile_iota[t] = t;
 }
 
 __global__ void __launch_bounds__(256) bin_fill_kernel(BinLaunch b, size_t n_entries) {
@@ -312,15 +469,15 @@ __global__ void __launch_bounds__(256) bin_fill_kernel(BinLaunch b, size_t n_ent
     b.ent_range[k] = make_float2(INFINITY, -INFINITY);
 }
 
-__global__ void __launch_bounds__(256) bin_scatter_kernel(BinLaunch b, int total) {
+__global__ void __launch_bounds__(256) bin_scatter_kernel(BinLaunch b, int total, KeyLayout kl) {
     int k = blockIdx.x * blockDim.x + threadIdx.x;
     if (k >= total) return;
-    uint64_t key = b.keys_out[k];
-    int t = (int)(key >> 32);
-    const uint32_t src = b.vals_out[k];
-    size_t dest = (size_t)b.tile_pbegin[t] + (size_t)(k - b.tile_first[t]);
-    b.ent_id[dest] = b.pair_j[src];
-    b.ent_range[dest] = make_float2(__uint_as_float((unsigned)(key & 0xffffffffu)), b.pair_far[src]);
+    const uint64_t key = b.keys_out[k];
+    const int t = (int)(key >> (kl.near_bits + kl.id_bits));
+    const size_t dest = (size_t)b.tile_pbegin[t] + (size_t)(k - b.tile_first[t]);
+    b.ent_id[dest] = (int)(key & ((1ull << kl.id_bits) - 1ull));
+    const unsigned q = (unsigned)((key >> kl.id_bits) & ((1ull << kl.near_bits) - 1ull));
+    b.ent_range[dest] = make_float2(near_stored(q, kl.near_bits), __uint_as_float(b.vals_out[k]));
 }
 
 // One warp per block of 32 entries: nearest near distance and farthest far distance.
@@ -340,53 +497,59 @@ __global__ void __launch_bounds__(256) bin_blocks_kernel(BinLaunch b, size_t n_b
 
 }  // namespace
 
-size_t binning_cub_temp_bytes(size_t pair_cap, int n_pad, int ntiles) {
-    size_t a = 0, c = 0, d = 0;
+size_t binning_cub_temp_bytes(size_t pair_cap, int ntiles) {
+    size_t a = 0, d = 0;
     cub::DeviceRadixSort::SortPairs(nullptr, a, (const uint64_t*)nullptr, (uint64_t*)nullptr, (const uint32_t*)nullptr,
                                     (uint32_t*)nullptr, (int64_t)pair_cap, 0, 64, (cudaStream_t)0);
-    cub::DeviceScan::ExclusiveSum(nullptr, c, (const int*)nullptr, (int*)nullptr, n_pad, (cudaStream_t)0);
     cub::DeviceScan::ExclusiveSum(nullptr, d, (const int*)nullptr, (int*)nullptr, ntiles + 1, (cudaStream_t)0);
-    size_t m = a > c ? a : c;
-    return m > d ? m : d;
+    size_t o = 0;
+    cub::DeviceRadixSort::SortPairsDescending(nullptr, o, (const int*)nullptr, (int*)nullptr, (const int*)nullptr,
+                                              (int*)nullptr, ntiles, 0, 32, (cudaStream_t)0);
+    if (o > a) a = o;
+    return a > d ? a : d;
 }
 
-// Phase 1: rectangles, counts, offsets, total (left in b.total_dev; the caller copies it to the host).
-cudaError_t launch_bin_count(const BinLaunch& b, cudaStream_t s) {
+// Phase 1: all (tile, Gaussian) pairs, unsorted, and their number in b.total_dev (which keeps
+// counting past b.pair_cap; the caller reads it back and repeats the phase with more room if needed).
+cudaError_t launch_bin_emit(const BinLaunch& b, cudaStream_t s) {
     const int tb = 256;
     const int ntiles = b.tiles_x * b.tiles_y;
+    cudaError_t e;
+    // total_dev: [0] pairs, [1] length of the list of large Gaussians, [2] next of them to take
+    if ((e = cudaMemsetAsync(b.total_dev, 0, 4 * sizeof(unsigned long long), s)) != cudaSuccess) return e;
     bin_tile_dirs_kernel<<<(ntiles + tb - 1) / tb, tb, 0, s>>>(b, ntiles);
-    bin_count_kernel<<<(b.n_pad + tb - 1) / tb, tb, 0, s>>>(b);
-    size_t temp = b.cub_bytes;
-    cudaError_t e = cub::DeviceScan::ExclusiveSum(b.cub_temp, temp, b.counts, b.offsets, b.n_pad, s);
-    if (e != cudaSuccess) return e;
-    bin_total_kernel<<<1, 32, 0, s>>>(b);
+    bin_emit_kernel<<<(b.n_pad + kEmitThreads - 1) / kEmitThreads, kEmitThreads, 0, s>>>(b);
+    bin_emit_big_kernel<<<b.big_grid, kBigWarps * 32, 0, s>>>(b);
     return cudaGetLastError();
 }
 
-// Phase 2: emit, sort, per-tile ranges, padded layout, block summaries.
+// Phase 2: sort, per-tile ranges, padded layout, block summaries.
 cudaError_t launch_bin_fill(const BinLaunch& b, int total, cudaStream_t s) {
     const int tb = 256;
     const int ntiles = b.tiles_x * b.tiles_y;
+    // the layout is that of the whole image whatever the row range, so that a row range sees the same order
+    const KeyLayout kl = key_layout(b.tiles_x * ((b.cam.height + b.tile - 1) / b.tile), b.n_pad);
     cudaError_t e;
     if ((e = cudaMemsetAsync(b.tile_first, 0, sizeof(int) * (ntiles + 1), s)) != cudaSuccess) return e;
     if ((e = cudaMemsetAsync(b.tile_last, 0, sizeof(int) * (ntiles + 1), s)) != cudaSuccess) return e;
     if ((e = cudaMemsetAsync(b.tile_pcnt, 0, sizeof(int) * (ntiles + 1), s)) != cudaSuccess) return e;
     size_t temp = b.cub_bytes;
     if (total > 0) {
-        bin_emit_kernel<<<(b.n_pad + tb - 1) / tb, tb, 0, s>>>(b);
-        int tile_bits = 1;
-        while ((1 << tile_bits) < ntiles) ++tile_bits;
         e = cub::DeviceRadixSort::SortPairs(b.cub_temp, temp, b.keys_in, b.keys_out, b.vals_in, b.vals_out, (int64_t)total, 0,
-                                            32 + tile_bits, s);
+                                            kl.tile_bits + kl.near_bits + kl.id_bits, s);
         if (e != cudaSuccess) return e;
-        bin_ranges_kernel<<<(total + tb - 1) / tb, tb, 0, s>>>(b, total);
+        bin_ranges_kernel<<<(total + tb - 1) / tb, tb, 0, s>>>(b, total, kl.near_bits + kl.id_bits);
     }
     bin_tile_counts_kernel<<<(ntiles + tb - 1) / tb, tb, 0, s>>>(b, ntiles);
     temp = b.cub_bytes;
     if ((e = cub::DeviceScan::ExclusiveSum(b.cub_temp, temp, b.tile_pcnt, b.tile_pbegin, ntiles + 1, s)) != cudaSuccess) return e;
+    // CTAs take the tiles with the longest lists first: the march ends with short tiles, not with one long one
+    temp = b.cub_bytes;
+    if ((e = cub::DeviceRadixSort::SortPairsDescending(b.cub_temp, temp, b.tile_cnt, b.tile_cnt_sorted, b.tile_iota, b.tile_order,
+                                                       ntiles, 0, 32, s)) != cudaSuccess) return e;
     const size_t n_entries = (((size_t)total + 32u * (size_t)ntiles + 31) / 32) * 32;   // upper bound of the padded layout
     bin_fill_kernel<<<(unsigned)((n_entries + tb - 1) / tb), tb, 0, s>>>(b, n_entries);
-    if (total > 0) bin_scatter_kernel<<<(total + tb - 1) / tb, tb, 0, s>>>(b, total);
+    if (total > 0) bin_scatter_kernel<<<(total + tb - 1) / tb, tb, 0, s>>>(b, total, kl);
     const size_t n_blocks = (n_entries + 31) / 32;
     bin_blocks_kernel<<<(unsigned)((n_blocks + 7) / 8), 256, 0, s>>>(b, n_blocks);
     return cudaGetLastError();

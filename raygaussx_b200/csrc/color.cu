@@ -131,18 +131,65 @@ __global__ void __launch_bounds__(128) finalize_kernel(FinalizeLaunch f) {
     const int K = f.sc.sh_coeffs, G = f.sc.num_lobes;
     const bool acc = (f.flags & RGX_FLAG_ACCUMULATE) != 0;
     const bool exact = (f.flags & RGX_FLAG_EXACT_SH_GRAD) != 0;
-    const float4 r0 = f.grad_rows[4 * (size_t)j], r1 = f.grad_rows[4 * (size_t)j + 1],
-                 r2 = f.grad_rows[4 * (size_t)j + 2], r3 = f.grad_rows[4 * (size_t)j + 3];
-    float dpos[3] = {r0.x, r0.y, r0.z};
-    const float dscale[3] = {r0.w, r1.x, r1.y};
-    const float dquat[4] = {r1.z, r1.w, r2.x, r2.y};
-    const float ddens = r2.z;
-    const float drgb[3] = {r2.w, r3.x, r3.y};
+    float4 r0 = f.grad_rows[4 * (size_t)j], r1 = f.grad_rows[4 * (size_t)j + 1],
+           r2 = f.grad_rows[4 * (size_t)j + 2], r3 = f.grad_rows[4 * (size_t)j + 3];
+    for (int c = 1; c < f.grad_copies; ++c) {          // the march spreads its additions over several sets of rows
+        const float4* row = f.grad_rows + 4 * ((size_t)c * (size_t)f.n_pad + (size_t)j);
+        const float4 a0 = row[0], a1 = row[1], a2 = row[2], a3 = row[3];
+        r0.x += a0.x; r0.y += a0.y; r0.z += a0.z; r0.w += a0.w;
+        r1.x += a1.x; r1.y += a1.y; r1.z += a1.z; r1.w += a1.w;
+        r2.x += a2.x; r2.y += a2.y; r2.z += a2.z; r2.w += a2.w;
+        r3.x += a3.x;
+    }
+    // The march left the moments of the loss gradient in the Gaussian's whitened frame y = M (x - p),
+    // M = S^-1 R^T / k (rows as in emit_global).  With N = S^-1 R^T = k M:
+    //   dL/dp     = N^T k mu                      = k sum_a col_a mu_a / s_a
+    //   dL/ds_a   = k^2 Y_aa / s_a
+    //   dL/dcol_a = -(k^2 / s_a) sum_b Y_ab s_b row_b(R^-1),  then through the quaternion formula
+    // (x - p = R^-T S k y; R^-1 has the columns of R as rows only for a unit quaternion, which nothing enforces)
+    // (cuda_train/backward/gaussians_aabb.cu:401-481 summed over the samples of all rays).
+    const float mu[3] = {r0.x, r0.y, r0.z};
+    const float Ym[3][3] = {{r0.w, r1.z, r1.w}, {r1.z, r1.x, r2.x}, {r1.w, r2.x, r1.y}};
+    const float ddens = r2.y;
+    const float drgb[3] = {r2.z, r2.w, r3.x};
+    const float4 sd = f.sdens[j], qq = f.quat[j];
+    const float k2 = 2.0f * 0.6931471805599453f * f.hk[j];
+    const float kk = sqrtf(fmaxf(k2, 0.f));
+    const float sc[3] = {sd.x, sd.y, sd.z};
+    float3 cols[3];
+    quat_to_columns(qq, cols[0], cols[1], cols[2]);
+    float3 inv_rows[3] = {cross3(cols[1], cols[2]), cross3(cols[2], cols[0]), cross3(cols[0], cols[1])};
+    const float det = dot3(cols[0], inv_rows[0]);
+    const float inv_det = det != 0.f ? 1.0f / det : 1.0f;
+    float dpos[3] = {0.f, 0.f, 0.f};
+    float dscale[3];
+    float3 dcol[3];
+#pragma unroll
+    for (int a = 0; a < 3; ++a) {
+        const float inv = 1.0f / sc[a];
+        const float cf = kk * mu[a] * inv;
+        dpos[0] += cols[a].x * cf; dpos[1] += cols[a].y * cf; dpos[2] += cols[a].z * cf;
+        dscale[a] = k2 * Ym[a][a] * inv;
+        float3 acc3 = make_float3(0.f, 0.f, 0.f);
+#pragma unroll
+        for (int b = 0; b < 3; ++b) acc3 = acc3 + inv_rows[b] * (Ym[a][b] * sc[b]);
+        dcol[a] = acc3 * (-k2 * inv * inv_det);
+    }
+    const float4 dq = quat_grad_from_columns(qq, dcol[0], dcol[1], dcol[2]);
+    const float dquat[4] = {dq.x, dq.y, dq.z, dq.w};
+    const bool touched = r0.x != 0.f || r0.y != 0.f || r0.z != 0.f || r0.w != 0.f || r1.x != 0.f || r1.y != 0.f ||
+                         r1.z != 0.f || r1.w != 0.f || r2.x != 0.f;
+    if (!touched) {          // a Gaussian no ray met: exact zeros even where hk, s or q are degenerate
+        dpos[0] = dpos[1] = dpos[2] = 0.f;
+        dscale[0] = dscale[1] = dscale[2] = 0.f;
+    }
+    const float dquat_out[4] = {touched ? dquat[0] : 0.f, touched ? dquat[1] : 0.f, touched ? dquat[2] : 0.f,
+                                touched ? dquat[3] : 0.f};
 
 #pragma unroll
     for (int a = 0; a < 3; ++a) put(f.gr.scales + 3 * (size_t)i + a, dscale[a], acc);
 #pragma unroll
-    for (int a = 0; a < 4; ++a) put(f.gr.quaternions + 4 * (size_t)i + a, dquat[a], acc);
+    for (int a = 0; a < 4; ++a) put(f.gr.quaternions + 4 * (size_t)i + a, dquat_out[a], acc);
     put(f.gr.densities + i, ddens, acc);
 
     const bool zero = drgb[0] == 0.f && drgb[1] == 0.f && drgb[2] == 0.f;   // utils/sh_utils.cu:226-228

@@ -600,50 +600,39 @@ __device__ __forceinline__ SlabBackTerms slab_back_terms(float s, float dc, floa
     return o;
 }
 
-// Gradient of one (ray, slab, Gaussian) triple from its four moment sums; the
-// sample-wise sums of cuda_train/backward/gaussians_aabb.cu:401-441 collapse to
-// these because the whitened offset is affine in the sample position.
+// Gradient of one (ray, slab, Gaussian) triple from its four moment sums.  The
+// sample-wise sums of cuda_train/backward/gaussians_aabb.cu:401-441 collapse because
+// the whitened offset y = y_c + t' de is affine in the sample position: with the
+// weights w_s (sigma times the sample's share of the loss gradient) everything the
+// chain rule needs is the first moment mu = sum_s w_s y_s and the second moment
+// Y = sum_s w_s y_s y_s^T, both in the Gaussian's whitened frame.  The march adds
+// those up per Gaussian; the step to position, scale and quaternion gradients is
+// taken once per Gaussian afterwards (finalize_kernel), not once per hit.
 struct GaussGrad {
-    float3 dpos;
-    float dscale[3];
-    float4 dquat;
+    float3 mu;
+    float y00, y11, y22, y01, y02, y12;
     float dsigma;
     float drgb_scale;   // dL/drgb = dl * drgb_scale
 };
-__device__ __forceinline__ GaussGrad expand_gradient(const MarchLaunch& L, const Ray& r, int j, float4 A, float4 B,
-                                                     float tbuffer, float sb, float n0, float n1, float n2) {
-    const float4 sd = __ldg(&L.g.sdens[j]);
-    const float4 qq = __ldg(&L.g.quat[j]);
-    const float4 g0 = __ldg(&L.g.g0[j]);
-    const float sigma = sd.w;
-    const float kk = __fsqrt_rn(__fmul_rn(2.0f * 0.6931471805599453f, A.w));   // k = sqrt(2 ln(sigma/sigma_t))
-    const float m0 = sigma * n0, m1 = sigma * n1, m2 = sigma * n2;
-    const float tc = __fadd_rn(tbuffer, -B.w);                                 // reference point t_c
-    const float3 xc = make_float3(fmaf(tc, r.d.x, r.o.x - g0.x), fmaf(tc, r.d.y, r.o.y - g0.y),
-                                  fmaf(tc, r.d.z, r.o.z - g0.z));
-    const float inv_sc[3] = {1.0f / sd.x, 1.0f / sd.y, 1.0f / sd.z};
-    const float ycv[3] = {A.x, A.y, A.z}, dev[3] = {B.x, B.y, B.z};
-    float3 U, V, Wc;
-    quat_to_columns(qq, U, V, Wc);
-    const float3 cols[3] = {U, V, Wc};
+// A = (y_c.xyz, -), B = (de.xyz, -): the whitened ray point at the reference parameter and the whitened direction
+__device__ __forceinline__ GaussGrad expand_gradient(float sigma, float4 A, float4 B, float sb, float n0, float n1,
+                                                     float n2) {
+    const float m0 = __fmul_rn(sigma, n0), m1 = __fmul_rn(sigma, n1), m2 = __fmul_rn(sigma, n2);
+    const float3 yc = make_float3(A.x, A.y, A.z), de = make_float3(B.x, B.y, B.z);
+    const float3 U = make_float3(fmaf(m0, yc.x, __fmul_rn(m1, de.x)), fmaf(m0, yc.y, __fmul_rn(m1, de.y)),
+                                 fmaf(m0, yc.z, __fmul_rn(m1, de.z)));
+    const float3 V = make_float3(fmaf(m1, yc.x, __fmul_rn(m2, de.x)), fmaf(m1, yc.y, __fmul_rn(m2, de.y)),
+                                 fmaf(m1, yc.z, __fmul_rn(m2, de.z)));
     GaussGrad g;
-    g.dpos = make_float3(0.f, 0.f, 0.f);
-    float3 dcol[3];
-    const float k2 = kk * kk;
-#pragma unroll
-    for (int a = 0; a < 3; ++a) {
-        // sum_s omega y_a^2 / s_a,  y = k (y_c + t' de)
-        g.dscale[a] = k2 * (m0 * ycv[a] * ycv[a] + 2.0f * m1 * ycv[a] * dev[a] + m2 * dev[a] * dev[a]) * inv_sc[a];
-        const float coef = kk * (m0 * ycv[a] + m1 * dev[a]) * inv_sc[a];
-        g.dpos = g.dpos + cols[a] * coef;
-        // -(1/s_a) sum_s omega y_a (x_c + t' d)
-        const float cx = kk * (m0 * ycv[a]) + kk * (m1 * dev[a]);
-        const float cd = kk * (m1 * ycv[a]) + kk * (m2 * dev[a]);
-        dcol[a] = (xc * cx + r.d * cd) * (-inv_sc[a]);
-    }
-    g.dquat = quat_grad_from_columns(qq, dcol[0], dcol[1], dcol[2]);
+    g.mu = U;
+    g.y00 = fmaf(yc.x, U.x, __fmul_rn(de.x, V.x));
+    g.y11 = fmaf(yc.y, U.y, __fmul_rn(de.y, V.y));
+    g.y22 = fmaf(yc.z, U.z, __fmul_rn(de.z, V.z));
+    g.y01 = fmaf(yc.x, U.y, __fmul_rn(de.x, V.y));
+    g.y02 = fmaf(yc.x, U.z, __fmul_rn(de.x, V.z));
+    g.y12 = fmaf(yc.y, U.z, __fmul_rn(de.y, V.z));
     g.dsigma = n0;
-    g.drgb_scale = sigma * sb;
+    g.drgb_scale = __fmul_rn(sigma, sb);
     return g;
 }
 
@@ -660,7 +649,7 @@ __device__ __forceinline__ void slab_gradients(const MarchLaunch& L, const rgx_m
         eval_backward(ws, nstage, tau, beta, gamma, lane, sb, n0, n1, n2);
         if (lane < nstage) {
             const int j = prim_of[lane];
-            emit(j, expand_gradient(L, r, j, ws.recA[lane], ws.recB[lane], tbuffer, sb, n0, n1, n2));
+            emit(j, expand_gradient(__ldg(&L.g.sdens[j]).w, ws.recA[lane], ws.recB[lane], sb, n0, n1, n2));
         }
         nstage = 0;
         __syncwarp();
@@ -699,12 +688,16 @@ __device__ __forceinline__ void slab_gradients(const MarchLaunch& L, const rgx_m
     if (nstage > 0) drain();
 }
 
+// Row layout of grad_rows, [copies, n_pad, 4] float4 per sorted slot:
+//   (mu.xyz, Y00) (Y11, Y22, Y01, Y02) (Y12, dsigma, drgb.xy) (drgb.z, -, -, -)
+// A Gaussian that fills the view is met by every ray, and additions to one address queue up in
+// the L2; CTAs therefore spread over `copies` sets of rows, which finalize_kernel adds up.
 __device__ __forceinline__ void emit_global(const MarchLaunch& L, float3 dl, int j, const GaussGrad& g) {
-    float4* row = L.grad_rows + 4 * (size_t)j;
-    red_add_v4(row, g.dpos.x, g.dpos.y, g.dpos.z, g.dscale[0]);
-    red_add_v4(row + 1, g.dscale[1], g.dscale[2], g.dquat.x, g.dquat.y);
-    red_add_v4(row + 2, g.dquat.z, g.dquat.w, g.dsigma, dl.x * g.drgb_scale);
-    red_add_v4(row + 3, dl.y * g.drgb_scale, dl.z * g.drgb_scale, 0.f, 0.f);
+    float4* row = L.grad_rows + 4 * ((size_t)(blockIdx.x & (unsigned)(L.grad_copies - 1)) * (size_t)L.g.n_pad + (size_t)j);
+    red_add_v4(row, g.mu.x, g.mu.y, g.mu.z, g.y00);
+    red_add_v4(row + 1, g.y11, g.y22, g.y01, g.y02);
+    red_add_v4(row + 2, g.y12, g.dsigma, __fmul_rn(dl.x, g.drgb_scale), __fmul_rn(dl.y, g.drgb_scale));
+    atomicAdd(reinterpret_cast<float*>(row + 3), __fmul_rn(dl.z, g.drgb_scale));
 }
 
 }  // namespace

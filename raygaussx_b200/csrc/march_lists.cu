@@ -29,6 +29,13 @@ constexpr int kThreads = kWarps * 32;
 
 constexpr int kHitList = 256;      // hits of a slab remembered between the two passes of the backward
 
+// Recording of a forward slab for the backward ("tape"), in ints, 16-byte aligned:
+//   [0] tbuffer bits  [1] hit count  [2,3] offset of the ray's next chunk (-1: last)
+//   [4, 132) per sample (lane) the sums (sigma, r sigma, g sigma, b sigma) weighted by the Gaussians' responses
+//   [132, 132 + hits) sorted slots of the hits in the order they were met
+constexpr int kTapeHead = 4 + 4 * kSlab;
+constexpr int kTapeBlock = 4096;   // ints a warp reserves at a time; slabs are recorded if kTapeHead + hit cap fits
+
 struct ListShared {
     int next_ray;
     int pend[kWarps][2 * kFan];
@@ -165,14 +172,13 @@ __device__ __forceinline__ bool ray_pixel(const MarchLaunch& L, int tile_x, int 
 
 // ---------------------------------------------------------------- forward
 template <bool COUNT, bool SAVE>
-__global__ void __launch_bounds__(kThreads) march_forward_lists_kernel(const __grid_constant__ MarchLaunch L) {
+__global__ void __launch_bounds__(kThreads, COUNT ? 1 : 3) march_forward_lists_kernel(const __grid_constant__ MarchLaunch L) {
     __shared__ ListShared sh;
-    __shared__ int hit_lists[SAVE ? kWarps : 1][SAVE ? kHitList : 1];
     constexpr bool save = SAVE;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     WarpStage& ws = sh.ws[warp];
     int* pend = sh.pend[warp];
-    const int tile = blockIdx.x;
+    const int tile = L.lists.tile_order ? __ldg(&L.lists.tile_order[blockIdx.x]) : blockIdx.x;   // longest lists first
     const int tile_x = tile % L.lists.tiles_x, tile_y = tile / L.lists.tiles_x;
     const float eps = L.m.transmittance_eps;
     const float bg = L.m.white_background ? 1.0f : 0.0f;
@@ -183,6 +189,8 @@ __global__ void __launch_bounds__(kThreads) march_forward_lists_kernel(const __g
     for (int i = 0; i < C_NUM; ++i) tl.v[i] = 0;
     if (tid == 0) sh.next_ray = 0;
     __syncthreads();
+    long long blk_off = 0;      // the warp's current block of the tape and what is left of it
+    int blk_left = 0;
 
     while (true) {
         int ray = 0;
@@ -201,7 +209,11 @@ __global__ void __launch_bounds__(kThreads) march_forward_lists_kernel(const __g
         long long tape_head = -1, tape_prev = -1;    // first and latest chunk of this ray on the tape
         bool tape_ok = true;
         if (COUNT) tl.v[C_RAYS] += 1;
+        // cycle counters of the counting variant: whole ray, closest-hit queries, slab queries (the
+        // evaluation of the staged hits is timed inside slab_sums), compositing
+        const long long c_ray = COUNT ? clock64() : 0;
         float first = closest_in_tile<COUNT>(L, r, tenter, texit, tv, cursor, pend, lane, tl);
+        if (COUNT) tl.v[C_CYC_SEEK] += clock64() - c_ray;
         if (first < INFINITY && first < texit) {                                  // :249-260
             tenter = first;
             float tbuffer = tenter;
@@ -214,44 +226,51 @@ __global__ void __launch_bounds__(kThreads) march_forward_lists_kernel(const __g
                 const float tau = __fmul_rn((float)lane + 0.5f, p.dt);
                 float s, cr, cg, cb;
                 bool overflow;
-                int* hits = hit_lists[SAVE ? warp : 0];
+                // room on the tape for the largest chunk this slab can make; the hits are written there as they
+                // are met and the unused rest is handed back
+                int* chunk = nullptr;
+                if (save && tape_ok) {
+                    const int worst = (kTapeHead + L.m.max_prim_slice + 3) & ~3;
+                    if (worst > blk_left && worst <= kTapeBlock) {
+                        unsigned long long o = 0;
+                        if (lane == 0) o = atomicAdd(L.tape_used, (unsigned long long)kTapeBlock);
+                        o = __shfl_sync(kFull, o, 0);
+                        if ((long long)(o + kTapeBlock) <= L.tape_cap) { blk_off = (long long)o; blk_left = kTapeBlock; }
+                    }
+                    if (worst <= blk_left) chunk = L.tape + blk_off;
+                    else tape_ok = false;                  // no room: the backward will search this ray
+                }
+                const long long c_q = COUNT ? clock64() : 0;
                 int nhit = slab_sums<COUNT, false>(L, L.m, tbuffer, tau, ray_id, slab_index, make_float3(0.f, 0.f, 0.f),
                                                    ws, lane, tl, [&](auto&& leaf) {
                     search_tile<COUNT>(L, r, p.tmin, p.tmax, tv, cursor, pend, lane, tl, leaf);
-                }, s, cr, cg, cb, overflow, save ? hits : nullptr, kHitList);
-                if (COUNT) { tl.v[C_HITS] += nhit; tl.v[C_OVF] += overflow ? 1 : 0; }
-                if (save && nhit > 0 && tape_ok) {
-                    // one chunk per slab with hits: [tbuffer, count, next lo, next hi, slots...]
-                    long long off = -1;
-                    if (nhit <= kHitList) {
-                        unsigned long long o = 0;
-                        if (lane == 0) o = atomicAdd(L.tape_used, (unsigned long long)(4 + nhit));
-                        o = __shfl_sync(kFull, o, 0);
-                        if ((long long)(o + 4 + nhit) <= L.tape_cap) off = (long long)o;
+                }, s, cr, cg, cb, overflow, chunk ? chunk + kTapeHead : nullptr, chunk ? L.m.max_prim_slice : 0);
+                if (COUNT) { tl.v[C_HITS] += nhit; tl.v[C_OVF] += overflow ? 1 : 0; tl.v[C_CYC_SEARCH] += clock64() - c_q; }
+                if (chunk && nhit > 0) {
+                    const int need = (kTapeHead + nhit + 3) & ~3;
+                    if (lane == 0) {
+                        *reinterpret_cast<int4*>(chunk) = make_int4(__float_as_int(tbuffer), nhit, -1, -1);
+                        if (tape_prev >= 0)
+                            *reinterpret_cast<int2*>(L.tape + tape_prev + 2) = make_int2((int)(blk_off & 0xffffffffll), (int)(blk_off >> 32));
                     }
-                    if (off < 0) tape_ok = false;          // no room (or too many hits): the backward will search this ray
-                    else {
-                        __syncwarp();
-                        if (lane == 0) {
-                            L.tape[off] = __float_as_int(tbuffer); L.tape[off + 1] = nhit;
-                            L.tape[off + 2] = -1; L.tape[off + 3] = -1;
-                            if (tape_prev >= 0) { L.tape[tape_prev + 2] = (int)(off & 0xffffffffll); L.tape[tape_prev + 3] = (int)(off >> 32); }
-                        }
-                        for (int i = lane; i < nhit; i += 32) L.tape[off + 4 + i] = hits[i];
-                        if (tape_head < 0) tape_head = off;
-                        tape_prev = off;
-                        __syncwarp();
-                    }
+                    reinterpret_cast<float4*>(chunk + 4)[lane] = make_float4(s, cr, cg, cb);
+                    if (tape_head < 0) tape_head = blk_off;
+                    tape_prev = blk_off;
+                    blk_off += need; blk_left -= need;
                 }
                 if (nhit == 0) {                                                  // :297-319
                     tbuffer = __fadd_rn(tbuffer, p.slab);
+                    const long long c_s = COUNT ? clock64() : 0;
                     float nxt = closest_in_tile<COUNT>(L, r, tbuffer, texit, tv, cursor, pend, lane, tl);
+                    if (COUNT) tl.v[C_CYC_SEEK] += clock64() - c_s;
                     if (!(nxt < INFINITY)) break;
                     tbuffer = nxt;
                     continue;
                 }
                 if (COUNT) tl.v[C_SLABS_HIT] += 1;
+                const long long c_c = COUNT ? clock64() : 0;
                 composite_forward(p, tbuffer, tau, eps, lane, s, cr, cg, cb, L.depth != nullptr, st);
+                if (COUNT) tl.v[C_CYC_COMP] += clock64() - c_c;
                 tbuffer = __fadd_rn(tbuffer, p.slab);                             // :324
             }
         }
@@ -263,21 +282,194 @@ __global__ void __launch_bounds__(kThreads) march_forward_lists_kernel(const __g
             if (L.depth) L.depth[ray_id] = st.depth;
             if (save) L.ray_head[ray_id] = tape_ok ? tape_head : -2;
         }
+        if (COUNT) tl.v[C_CYC_TOTAL] += clock64() - c_ray;
     }
     if (COUNT) flush_tally(L, tl, lane);
 }
 
-// ---------------------------------------------------------------- backward
-// TAPE = true: rays whose forward was recorded, replayed from the tape, no search code at all.
-// TAPE = false: rays without a recording (all of them when nothing was recorded), by searching again.
-template <bool TAPE>
+// ---------------------------------------------------------------- backward, by replaying the forward's recording
+//
+// For rays whose forward was recorded.  Per slab the recording holds the hits and the
+// per-sample sums, so what is left is the second pass of the reference's backward
+// (cuda_train/backward/gaussians_aabb.cu:354-470): the gradient of every (slab,
+// Gaussian) pair.  Here lanes are Gaussians, not samples: a lane takes one hit of the
+// slab, walks only the samples that lie inside that Gaussian's truncation ellipsoid
+// (a handful of the 32 on average) and keeps the four moment sums in registers -- no
+// staging in shared memory and no reduction across lanes.
+constexpr int kRun = 4;     // samples per work item of the replay
+
+struct ReplayStage {        // per warp: one group of up to 32 hits
+    float4 a[kFan];         // whitened ray point at the reference parameter, hk
+    float4 b[kFan];         // whitened direction, tbuffer - reference parameter
+    float4 c[kFan];         // chat_i, sigma, first and last sample (as int bits)
+    int slot[kFan];
+    int upto[kFan];         // inclusive prefix of the number of runs
+};
+
+struct ReplayShared {
+    int next_ray;
+    float beta[kWarps][kSlab];
+    float gamma[kWarps][kSlab];
+    ReplayStage stage[kWarps];
+};
+
+__global__ void __launch_bounds__(kThreads) march_backward_replay_kernel(const __grid_constant__ MarchLaunch L) {
+    __shared__ ReplayShared sh;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tile = L.lists.tile_order ? __ldg(&L.lists.tile_order[blockIdx.x]) : blockIdx.x;
+    const int tile_x = tile % L.lists.tiles_x, tile_y = tile / L.lists.tiles_x;
+    const float eps = L.m.transmittance_eps;
+    const SceneBox box = *L.box;
+    float* sbeta = sh.beta[warp];
+    float* sgamma = sh.gamma[warp];
+    ReplayStage& sp = sh.stage[warp];
+    if (tid == 0) sh.next_ray = 0;
+    __syncthreads();
+
+    while (true) {
+        int ray = 0;
+        if (lane == 0) ray = atomicAdd(&sh.next_ray, 1);
+        ray = __shfl_sync(kFull, ray, 0);
+        if (ray >= kRaysPerTile) break;
+        int px, py;
+        if (!ray_pixel(L, tile_x, tile_y, ray, px, py)) continue;
+        const int ray_id = py * L.cam.width + px;
+        long long off = L.ray_head[ray_id];
+        if (off < 0) continue;                     // -1: the ray met nothing; -2: not recorded, left to the search kernel
+        Ray r;
+        make_ray(L.cam, px, py, r);
+        float tenter, texit;
+        clip_scene(box, r, tenter, texit);
+        const float3 dl = make_float3(L.dl_drgb[3 * (size_t)ray_id], L.dl_drgb[3 * (size_t)ray_id + 1],
+                                      L.dl_drgb[3 * (size_t)ray_id + 2]);
+        float D = fmaf(dl.x, L.rgb_in[3 * (size_t)ray_id],
+                       fmaf(dl.y, L.rgb_in[3 * (size_t)ray_id + 1], __fmul_rn(dl.z, L.rgb_in[3 * (size_t)ray_id + 2])));
+        float T = 1.0f;
+        while (off >= 0) {
+            const int4 hd = *reinterpret_cast<const int4*>(L.tape + off);
+            const float tbuffer = __int_as_float(hd.x);
+            const int nhit = hd.y;
+            const float4 sums = reinterpret_cast<const float4*>(L.tape + off + 4)[lane];
+            const int* hits = L.tape + off + kTapeHead;
+            off = ((long long)hd.w << 32) | (unsigned int)hd.z;
+            // same step size as the forward: T is rebuilt from the recorded sums bit for bit
+            const SlabPlan p = plan_slab(L.m, tbuffer, T, tbuffer, texit);
+            const float dc = fmaf(dl.x, sums.y, fmaf(dl.y, sums.z, __fmul_rn(dl.z, sums.w)));
+            const SlabBackTerms bt = slab_back_terms(sums.x, dc, p.dt, T, D, eps, lane);
+            D = __fadd_rn(D, -bt.d_total);
+            T = slab_exit_T(bt.tr, eps);
+            __syncwarp();                          // the previous slab's readers are done
+            sbeta[lane] = bt.beta;
+            sgamma[lane] = bt.gamma;
+            __syncwarp();
+            const float inv_dt = __fdividef(1.0f, p.dt);
+            const float tend = __fadd_rn(tbuffer, p.slab);
+            for (int base = 0; base < nhit; base += kFan) {
+                // step 1, one hit per lane: where the ray is inside the Gaussian, cut into runs of kRun samples
+                int nitem = 0;
+                if (base + lane < nhit) {
+                    const int j = hits[base + lane];
+                    float3 Oe, de;
+                    whiten_ray(r, __ldg(&L.g.g0[j]), __ldg(&L.g.g1[j]), __ldg(&L.g.g2[j]), Oe, de);
+                    const float hk = __ldg(&L.g.hk[j]);
+                    const float4 c = __ldg(&L.g.rgba[j]);
+                    const float ci = __fdividef(fmaf(dl.x, c.x, fmaf(dl.y, c.y, __fmul_rn(dl.z, c.z))), c.w);
+                    // closest approach and half width of the stretch inside the ellipsoid |Oe + t de| < 1
+                    const float inv_a = __fdividef(1.0f, dot3(de, de));
+                    const float tca = __fmul_rn(-dot3(Oe, de), inv_a);
+                    const float3 P = make_float3(fmaf(tca, de.x, Oe.x), fmaf(tca, de.y, Oe.y), fmaf(tca, de.z, Oe.z));
+                    const float hw = __fsqrt_rn(__fmul_rn(fmaxf(1.0f - dot3(P, P), 0.f), inv_a));
+                    // samples (s + 1/2) dt inside it, one more on each side against rounding; the test q < 1 decides
+                    const float x_lo = fmaf(__fadd_rn(__fadd_rn(tca, -hw), -tbuffer), inv_dt, -0.5f);
+                    const float x_hi = fmaf(__fadd_rn(__fadd_rn(tca, hw), -tbuffer), inv_dt, -0.5f);
+                    const int s_lo = (int)fminf(fmaxf(ceilf(x_lo) - 1.0f, 0.f), (float)kSlab);
+                    const int s_hi = (int)fmaxf(fminf(floorf(x_hi) + 1.0f, (float)(kSlab - 1)), -1.f);
+                    // moments about the closest approach clamped to the slab, so that they stay small
+                    const float tcr = fminf(fmaxf(tca, tbuffer), tend);
+                    sp.a[lane] = make_float4(fmaf(tcr, de.x, Oe.x), fmaf(tcr, de.y, Oe.y), fmaf(tcr, de.z, Oe.z), hk);
+                    sp.b[lane] = make_float4(de.x, de.y, de.z, __fadd_rn(tbuffer, -tcr));
+                    sp.c[lane] = make_float4(ci, c.w, __int_as_float(s_lo), __int_as_float(s_hi));
+                    sp.slot[lane] = j;
+                    nitem = s_hi >= s_lo ? (s_hi - s_lo + kRun) / kRun : 0;
+                }
+                int incl = nitem;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int t = __shfl_up_sync(kFull, incl, o);
+                    if (lane >= o) incl += t;
+                }
+                const int total = __shfl_sync(kFull, incl, 31);
+                sp.upto[lane] = incl;
+                __syncwarp();
+                // step 2, one run per lane, whichever hit it belongs to: the four moment sums of the run,
+                // which share the reference point with the other runs of the hit and so simply add up
+                for (int i0 = 0; i0 < total; i0 += kFan) {
+                    const int i = i0 + lane;
+                    const bool active = i < total;
+                    int h = 0;
+                    float sb = 0.f, n0 = 0.f, n1 = 0.f, n2 = 0.f;
+                    float4 A = make_float4(0.f, 0.f, 0.f, 0.f), B = A, C = A;
+                    if (active) {
+#pragma unroll
+                        for (int step = 16; step > 0; step >>= 1)
+                            if (sp.upto[h + step - 1] <= i) h += step;          // first hit whose runs end after i
+                        A = sp.a[h]; B = sp.b[h]; C = sp.c[h];
+                        const int s_hi = __float_as_int(C.w);
+                        const int nrun = (s_hi - __float_as_int(C.z) + kRun) / kRun;
+                        const int s0 = __float_as_int(C.z) + kRun * (i - (sp.upto[h] - nrun));
+#pragma unroll
+                        for (int k = 0; k < kRun; ++k) {
+                            const int s = s0 + k;
+                            if (s <= s_hi) {
+                                const float tc = __fadd_rn(__fmul_rn((float)s + 0.5f, p.dt), B.w);
+                                const float yx = fmaf(tc, B.x, A.x), yy = fmaf(tc, B.y, A.y), yz = fmaf(tc, B.z, A.z);
+                                const float q = fmaf(yx, yx, fmaf(yy, yy, __fmul_rn(yz, yz)));
+                                if (q < 1.0f) {
+                                    const float ex = ex2_approx(__fmul_rn(-A.w, q));
+                                    const float be = sbeta[s];
+                                    const float ga = __fmul_rn(ex, fmaf(C.x, be, sgamma[s]));   // g * (alpha + beta*(chat_i - chat_s))
+                                    const float g1 = __fmul_rn(ga, tc);
+                                    sb = fmaf(ex, be, sb);
+                                    n0 = __fadd_rn(n0, ga);
+                                    n1 = __fadd_rn(n1, g1);
+                                    n2 = fmaf(g1, tc, n2);
+                                }
+                            }
+                        }
+                    }
+                    // runs of one hit sit in neighbouring lanes (at most 32 / kRun of them): add them up so that
+                    // the Gaussian's row gets one update per hit, not one per run
+                    const int seg = active ? h : -1 - lane;
+#pragma unroll
+                    for (int d = 1; d < kSlab / kRun; d <<= 1) {
+                        const int seg_o = __shfl_down_sync(kFull, seg, d);
+                        const float o_sb = __shfl_down_sync(kFull, sb, d), o_n0 = __shfl_down_sync(kFull, n0, d),
+                                    o_n1 = __shfl_down_sync(kFull, n1, d), o_n2 = __shfl_down_sync(kFull, n2, d);
+                        if (lane + d < 32 && seg_o == seg) {
+                            sb = __fadd_rn(sb, o_sb); n0 = __fadd_rn(n0, o_n0); n1 = __fadd_rn(n1, o_n1); n2 = __fadd_rn(n2, o_n2);
+                        }
+                    }
+                    const int seg_prev = __shfl_up_sync(kFull, seg, 1);
+                    const bool first = lane == 0 || seg_prev != seg;
+                    if (active && first && (sb != 0.f || n0 != 0.f || n1 != 0.f || n2 != 0.f))
+                        emit_global(L, dl, sp.slot[h], expand_gradient(C.y, A, B, sb, n0, n1, n2));
+                }
+                __syncwarp();                      // the next group reuses the staging arrays
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------- backward, by searching again
+// For rays without a recording: all of them when the forward did not record, else only those
+// it could not record (ray_head == -2).
 __global__ void __launch_bounds__(kThreads) march_backward_lists_kernel(const __grid_constant__ MarchLaunch L) {
     __shared__ ListShared sh;
     __shared__ int hit_lists[kWarps][kHitList];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     WarpStage& ws = sh.ws[warp];
     int* pend = sh.pend[warp];
-    const int tile = blockIdx.x;
+    const int tile = L.lists.tile_order ? __ldg(&L.lists.tile_order[blockIdx.x]) : blockIdx.x;
     const int tile_x = tile % L.lists.tiles_x, tile_y = tile / L.lists.tiles_x;
     const float eps = L.m.transmittance_eps;
     const SceneBox box = *L.box;
@@ -296,6 +488,7 @@ __global__ void __launch_bounds__(kThreads) march_backward_lists_kernel(const __
         int px, py;
         if (!ray_pixel(L, tile_x, tile_y, ray, px, py)) continue;
         const int ray_id = py * L.cam.width + px;
+        if (L.tape && L.ray_head[ray_id] != -2) continue;       // recorded: the replay kernel's
         Ray r;
         make_ray(L.cam, px, py, r);
         float tenter, texit;
@@ -306,46 +499,6 @@ __global__ void __launch_bounds__(kThreads) march_backward_lists_kernel(const __
         float D = fmaf(dl.x, L.rgb_in[3 * (size_t)ray_id],
                        fmaf(dl.y, L.rgb_in[3 * (size_t)ray_id + 1], __fmul_rn(dl.z, L.rgb_in[3 * (size_t)ray_id + 2])));
         float T = 1.0f;
-        const long long head = L.tape ? L.ray_head[ray_id] : -2;
-        if (TAPE != (head != -2)) continue;
-        if (TAPE) {
-            // The forward left this ray's slabs on the tape: same hits in the same order, so the sums, the
-            // transmittance and with it the step sizes come out bit for bit as in the forward -- no search.
-            long long off = head;
-            int* hits = hit_lists[warp];
-            while (off >= 0) {
-                const float tbuffer = __int_as_float(L.tape[off]);
-                const int nhit = L.tape[off + 1];
-                const long long next = ((long long)L.tape[off + 3] << 32) | (unsigned int)L.tape[off + 2];
-                for (int i = lane; i < nhit; i += 32) hits[i] = L.tape[off + 4 + i];
-                __syncwarp();
-                SlabPlan p = plan_slab(L.m, tbuffer, T, tbuffer, texit);
-                const float tau = __fmul_rn((float)lane + 0.5f, p.dt);
-                auto replay = [&](auto&& leaf) {
-                    for (int base = 0; base < nhit; base += kFan) {
-                        const bool valid = base + lane < nhit;
-                        const int j = valid ? hits[base + lane] : 0;
-                        LeafTest t;
-                        t.hit = valid;
-                        t.t_hit = 0.f;
-                        if (valid) whiten_ray(r, __ldg(&L.g.g0[j]), __ldg(&L.g.g1[j]), __ldg(&L.g.g2[j]), t.Oe, t.de);
-                        if (!leaf(t, j)) return;
-                    }
-                };
-                float s, dc, u0, u1;
-                bool overflow;
-                slab_sums<false, true>(L, L.m, tbuffer, tau, ray_id, 0, dl, ws, lane, tl, replay, s, dc, u0, u1, overflow);
-                SlabBackTerms bt = slab_back_terms(s, dc, p.dt, T, D, eps, lane);
-                slab_gradients(L, L.m, r, p, tbuffer, tau, dl, bt.beta, bt.gamma, ws, sh.prim_of[warp], lane, replay,
-                               [&](int j, const GaussGrad& g) { emit_global(L, dl, j, g); });
-                D = __fadd_rn(D, -bt.d_total);
-                T = slab_exit_T(bt.tr, eps);
-                off = next;
-                __syncwarp();
-            }
-            continue;
-        }
-        if constexpr (!TAPE) {
         float first = closest_in_tile<false>(L, r, tenter, texit, tv, cursor, pend, lane, tl);
         if (!(first < INFINITY && first < texit)) continue;                       // backward .cu:249-254
         tenter = first;
@@ -390,7 +543,6 @@ __global__ void __launch_bounds__(kThreads) march_backward_lists_kernel(const __
             T = slab_exit_T(bt.tr, eps);
             tbuffer = __fadd_rn(tbuffer, p.slab);
         }
-        }   // !TAPE
     }
 }
 
@@ -419,8 +571,8 @@ cudaError_t launch_march_backward(const MarchLaunch& m, cudaStream_t s) {
     if (!use_lists(m)) return launch_march_backward_per_ray(m, s);
     const int grid = m.lists.tiles_x * m.lists.tiles_y;
     if (grid <= 0) return cudaSuccess;
-    if (m.tape) march_backward_lists_kernel<true><<<grid, kThreads, 0, s>>>(m);     // recorded rays
-    march_backward_lists_kernel<false><<<grid, kThreads, 0, s>>>(m);               // the others (a quick no-op per recorded ray)
+    if (m.tape) march_backward_replay_kernel<<<grid, kThreads, 0, s>>>(m);          // recorded rays
+    march_backward_lists_kernel<<<grid, kThreads, 0, s>>>(m);                      // the others (a quick no-op per recorded ray)
     return cudaGetLastError();
 }
 

@@ -65,6 +65,7 @@ struct TileLists {
     const float2* blk;         // per 32 entries: (smallest near, largest far)
     const int* tile_pbegin;
     const int* tile_cnt;
+    const int* tile_order;     // tiles by falling list length: CTA b marches tile tile_order[b] (null: tile b)
     int tiles_x, tiles_y, ty_first;
 };
 
@@ -76,17 +77,17 @@ struct BinLaunch {
     rgx_camera cam;
     float dual[3][3];                      // dual basis of (u, v, w): rows u*, v*, w*
     int row_begin, row_end, tile, tiles_x, tiles_y, ty_first;
-    int *counts, *offsets;                 // [n_pad]
-    uint2* rect;                           // [n_pad] tile rectangle (x0 | x1 << 16, y0 | y1 << 16)
-    float2* depth;                         // [n_pad] (near, far)
-    uint64_t *keys_in, *keys_out;          // [pair capacity]
-    uint32_t *vals_in, *vals_out;
+    uint64_t *keys_in, *keys_out;          // [pair capacity] (tile, near distance, sorted slot)
+    uint32_t *vals_in, *vals_out;          // [pair capacity] far distance (float bits)
+    unsigned long long pair_cap;
     int *tile_first, *tile_last, *tile_cnt, *tile_pcnt, *tile_pbegin;   // [tiles + 1]
+    int *tile_iota, *tile_cnt_sorted, *tile_order;                      // [tiles]
     int* ent_id; float2* ent_range; float2* blk;
     float4* tile_dir;                      // [tiles] central ray direction, chord to the farthest corner ray
-    int* pair_j; float* pair_far;          // [pair capacity] in emission order
     void* cub_temp; size_t cub_bytes;
-    int* total_dev;
+    unsigned long long* total_dev;         // [4]; [0] = number of pairs met by the emission (may exceed pair_cap)
+    int* big_slot; uint2* big_rect;        // [n_pad] Gaussians that cover many tiles, and their tile rectangles
+    int big_grid;                          // CTAs that work the list off (a few per SM)
 };
 
 struct MarchLaunch {
@@ -110,7 +111,8 @@ struct MarchLaunch {
     unsigned long long* tape_used;
     long long tape_cap;
     long long* ray_head;
-    float4* grad_rows;    // [n_pad,4] float4: (dpos.xyz, dscale.x) (dscale.yz, dquat.xy) (dquat.zw, dsigma, drgb.x) (drgb.yz, 0, 0)
+    float4* grad_rows;    // [grad_copies, n_pad, 4] float4 of accumulated moments, layout in emit_global
+    int grad_copies;      // power of two
 };
 
 struct ColorLaunch {
@@ -127,7 +129,10 @@ struct FinalizeLaunch {
     rgx_grads gr;
     float eye[3];
     const uint32_t* perm;
-    const float4* grad_rows;
+    const float4* grad_rows;   // [grad_copies, n_pad, 4], see emit_global
+    int grad_copies, n_pad;
+    const float4 *quat, *sdens;   // sorted copies the march used
+    const float* hk;
     int flags;
 };
 
@@ -157,8 +162,8 @@ cudaError_t launch_build(const BuildLaunch& b, cudaStream_t s);
 size_t build_cub_temp_bytes(int n_pad);
 cudaError_t launch_colors(const ColorLaunch& c, cudaStream_t s);
 cudaError_t launch_finalize(const FinalizeLaunch& f, cudaStream_t s);
-size_t binning_cub_temp_bytes(size_t pair_cap, int n_pad, int ntiles);
-cudaError_t launch_bin_count(const BinLaunch& b, cudaStream_t s);
+size_t binning_cub_temp_bytes(size_t pair_cap, int ntiles);
+cudaError_t launch_bin_emit(const BinLaunch& b, cudaStream_t s);
 cudaError_t launch_bin_fill(const BinLaunch& b, int total, cudaStream_t s);
 cudaError_t launch_march_forward(const MarchLaunch& m, cudaStream_t s);
 cudaError_t launch_march_backward(const MarchLaunch& m, cudaStream_t s);
