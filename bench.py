@@ -16,7 +16,7 @@ fixed (strong scaling).
 Printed JSON line (rank 0): ``value`` = forward+backward Mrays/s of the whole job
 with all inputs resident in HBM; ``e2e`` = the same through the reference-facing
 autograd entry point with the target images copied from pinned host memory and the
-loss read back every step; ``roofline`` for the backward march kernel;
+loss read back every step; ``roofline`` for the forward march kernel (the dominant one);
 ``cpu_baseline`` = the reference's own device code compiled for the host CPU
 (oracle/_ref) on a bounded sample of the same workload.
 
@@ -297,7 +297,8 @@ def main():
             dist.destroy_process_group()
         return
 
-    # ---- roofline of the dominant kernel (backward march), from live CUDA-event timings
+    # ---- roofline of the dominant kernel (the recording forward march: 49 % of a step in the ncu launch list),
+    # from live CUDA-event timings
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -307,8 +308,7 @@ def main():
     peak_src = "measured" if "hbm_gbs" in peaks else "fallback"
     sm_max_mhz = float(peaks.get("sm_max_mhz", 1965.0))
     n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
-    bwd_launches = max(1, ktimes["backward_launches"])
-    bwd_ms = ktimes["backward_ms"] / bwd_launches
+    bwd_ms = ktimes["backward_ms"] / max(1, ktimes["backward_launches"])
     fwd_ms = ktimes["forward_ms"] / max(1, ktimes["forward_launches"])
     rows_per_launch = sum(b.row_end - b.row_begin for b in shard_rows(args.views, args.height, 0, world)) / max(
         1, len(shard_rows(args.views, args.height, 0, world)))
@@ -319,26 +319,38 @@ def main():
     cn = renderer.read_counters()
     P, E, Sh = cn["hits"], cn["pairs_inside"], cn["slabs_hit"]
     frac_view = rays_per_launch / R
-    # backward: per Gaussian its records and gradient row, per ray colour and loss gradient, and the forward's
-    # recording (per slab with hits a 528-byte head with the per-sample sums, 4 bytes per hit)
+    # the forward's recording for the backward: per slab with hits a 528-byte head with the per-sample sums,
+    # 4 bytes per hit; written by the forward, read by the backward
     tape_bytes = (528.0 * Sh + 4.0 * P) * frac_view
-    alg_bytes = 536.0 * args.gaussians + 28.0 * rays_per_launch + tape_bytes
-    achieved = alg_bytes / (bwd_ms * 1e-3) / 1e9
-    f_bwd = (290.0 * P + 11.0 * E + 320.0 * Sh) * frac_view
-    mufu_bwd = (1.0 * E + 48.0 * Sh) * frac_view
+    # forward: per Gaussian its records (300 B), per ray its outputs (16 B), the recording
+    alg_fwd = 300.0 * args.gaussians + 16.0 * rays_per_launch + tape_bytes
+    # backward: per Gaussian records and gradient row (536 B), per ray colour and loss gradient (28 B), the recording
+    alg_bwd = 536.0 * args.gaussians + 28.0 * rays_per_launch + tape_bytes
+    achieved = alg_fwd / (fwd_ms * 1e-3) / 1e9
+    # DRAM traffic of a launch: ncu capture of the 1M-Gaussian 628x414 case (1.024 GB for 1.006 GB recorded; the
+    # recording is what the traffic consists of), scaled to this launch by the bytes recorded
+    traffic = 1.018 * tape_bytes
+    f_fwd = (60.0 * P + 20.0 * E + 300.0 * Sh) * frac_view          # useful FP32 operations of the forward
+    mufu_fwd = (1.0 * E + 70.0 * Sh) * frac_view
     fp32_peak = 2.0 * 128 * n_sm * sm_max_mhz * 1e6
     mufu_peak = 16.0 * n_sm * sm_max_mhz * 1e6
-    roofline = {"kernel": "march_backward_lists_kernel<true> (replay of the recorded forward)", "bound": "hbm", "achieved": achieved, "peak": hbm_peak,
-                "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_src, "traffic": None,
-                "ms_per_launch": bwd_ms, "launches_timed": ktimes["backward_launches"],
-                "forward_ms_per_launch": fwd_ms,
-                "algorithmic_bytes_per_launch": alg_bytes, "of_which_recording": tape_bytes,
-                "fp32_frac": f_bwd / (bwd_ms * 1e-3) / fp32_peak, "mufu_frac": mufu_bwd / (bwd_ms * 1e-3) / mufu_peak,
-                "note": "the march kernels are issue/latency bound, not HBM bound: fp32_frac and mufu_frac are useful "
-                        "flops and ex2 per second over the derived peaks (2*128*SMs*f, 16*SMs*f)",
+    roofline = {"kernel": "march_forward_lists_kernel<false,true> (forward march, recording for the backward)",
+                "bound": "hbm", "achieved": achieved, "peak": hbm_peak,
+                "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_src, "traffic": traffic,
+                "ms_per_launch": fwd_ms, "launches_timed": ktimes["forward_launches"],
+                "algorithmic_bytes_per_launch": alg_fwd, "of_which_recording": tape_bytes,
+                "backward": {"kernel": "march_backward_replay_kernel + march_backward_lists_kernel",
+                             "ms_per_launch": bwd_ms, "launches_timed": ktimes["backward_launches"],
+                             "algorithmic_bytes_per_launch": alg_bwd,
+                             "achieved": alg_bwd / (bwd_ms * 1e-3) / 1e9,
+                             "frac": alg_bwd / (bwd_ms * 1e-3) / 1e9 / hbm_peak},
+                "fp32_frac": f_fwd / (fwd_ms * 1e-3) / fp32_peak, "mufu_frac": mufu_fwd / (fwd_ms * 1e-3) / mufu_peak,
+                "note": "the march kernels are bound by instruction issue (62-69 % of issue slots used, ncu), not by "
+                        "HBM: fp32_frac and mufu_frac are useful flops and ex2 per second over the derived peaks "
+                        "(2*128*SMs*f, 16*SMs*f)",
                 "counters_per_view": {k: cn[k] for k in ("rays", "slabs", "slabs_hit", "closest_queries", "hits",
-                                                         "pairs_inside", "overflow_slabs", "windows",
-                                                         "fallback_windows", "candidates")}}
+                                                         "pairs_inside", "overflow_slabs", "prim_tests",
+                                                         "candidates")}}
 
     # ---- CPU baseline on a bounded sample (rank 0, N = 1 only)
     cpu_baseline = None
@@ -365,7 +377,7 @@ def main():
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "gaussians": args.gaussians, "image": f"{args.width}x{args.height}",
                    "views_per_step": args.views, "sh_degree": 3, "sharding": f"rows/{world}",
-                   "l2": "inputs larger than L2 (Gaussian records 0.5 GB, gradients 0.7 GB)"},
+                   "l2": "inputs larger than L2 (Gaussian records 0.65 GB, gradient rows 1.5 GB, 3 GB recorded per view)"},
         "views_per_s": args.views / (ms_per_step * 1e-3),
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
         "roofline": roofline, "cpu_baseline": cpu_baseline,

@@ -86,11 +86,13 @@ enum {
     RGX_FLAG_BRUTE_FORCE = 2,    /* skip the hierarchy: test every Gaussian in every query (validation only) */
     RGX_FLAG_EXACT_SH_GRAD = 4,  /* backward: exact d(basis 9)/dy instead of the reference's term (utils/sh_utils.cu:367) */
     RGX_FLAG_ACCUMULATE = 8,     /* backward: add into the gradient tensors instead of overwriting them */
-    RGX_FLAG_SAVE_HITS = 32,     /* forward: keep, per ray and slab, the Gaussians that were hit (in the context's
-                                    workspace) so that a backward for the same view reads them back instead of
-                                    searching again; the backward falls back to searching where nothing was kept */
-    RGX_FLAG_PER_RAY_SEARCH = 16 /* search the hierarchy once per ray and slab instead of once per 8x8 tile and depth
-                                    window (same results; the general path, kept for validation) */
+    RGX_FLAG_SAVE_HITS = 32,     /* forward: keep, per ray and slab, the Gaussians that were hit and the per-sample
+                                    sums (in the context's workspace, about 3 KB per ray) so that a backward for
+                                    the same view replays them instead of searching and evaluating again; the
+                                    backward falls back to searching where nothing was kept */
+    RGX_FLAG_PER_RAY_SEARCH = 16 /* search the hierarchy once per ray and slab instead of sliding along the view's
+                                    per-tile lists (same hits; the general path, kept for validation and used by
+                                    rgx_forward_static) */
 };
 
 /* Gradient tensors, shaped like the inputs (what RenderOptixFunction.backward
@@ -120,18 +122,19 @@ typedef struct rgx_counters {
     uint64_t ellipsoid_tests;/* exact ray/ellipsoid tests */
     uint64_t stack_overflows;/* traversal-stack overflows (results invalid if non-zero) */
     uint64_t hits_hash;     /* order-independent hash of every (ray, slab, Gaussian) hit triple */
-    uint64_t windows;       /* tiled march: depth windows processed (summed over tiles) */
-    uint64_t window_retries;/* tiled march: candidate searches repeated with a shallower window */
-    uint64_t fallback_windows;/* tiled march: windows advanced by per-ray searches because the candidates did not fit */
-    uint64_t candidates;    /* tiled march: candidate-list entries summed over windows */
-    /* tiled forward march: warp-cycles spent per phase (clock64 differences summed over warps) */
-    uint64_t cycles_window;   /* opening windows: hierarchy sweep, scans, barriers inside it */
-    uint64_t cycles_seek;     /* closest-hit scans of the candidate list */
-    uint64_t cycles_search;   /* slab queries: candidate filtering, exact tests, staging */
+    uint64_t windows;       /* unused (kept so that the struct keeps its size) */
+    uint64_t window_retries;/* unused */
+    uint64_t fallback_windows;/* unused */
+    uint64_t candidates;    /* tile-list march: list entries looked at (32 per opened block of a tile's list) */
+    /* tile-list forward march, counting variant: warp-cycles spent per phase (clock64 differences summed over
+     * warps).  cycles_search contains cycles_wait, which contains cycles_window and most of cycles_eval. */
+    uint64_t cycles_window;   /* staging of hits for the evaluation */
+    uint64_t cycles_seek;     /* closest-hit queries over the tile's list */
+    uint64_t cycles_search;   /* slab queries: list scan, exact tests, staging, evaluation */
     uint64_t cycles_eval;     /* per-sample evaluation of staged Gaussians */
-    uint64_t cycles_composite;/* compositing and ray bookkeeping */
-    uint64_t cycles_wait;     /* waiting for the other warps of the tile at the end of a window */
-    uint64_t cycles_total;    /* whole kernel, per warp */
+    uint64_t cycles_composite;/* compositing of a slab */
+    uint64_t cycles_wait;     /* exact tests of 32 candidates and what follows from their hits */
+    uint64_t cycles_total;    /* whole ray */
     uint64_t reserved;
 } rgx_counters;
 

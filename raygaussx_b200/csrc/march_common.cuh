@@ -490,6 +490,7 @@ __device__ __forceinline__ int slab_sums(const MarchLaunch& L, const rgx_march& 
     enumerate([&](const LeafTest& t, int j) {
         unsigned mask = __ballot_sync(kFull, t.hit);
         if (mask == 0u) return true;
+        const long long c_s = COUNT ? clock64() : 0;
         int rank = __popc(mask & ((1u << lane) - 1u)), n = __popc(mask);
         bool take = t.hit;
         if (nhit + n > m.max_prim_slice) {            // cuda_train/forward/gaussians_aabb.cu:352-356
@@ -518,6 +519,7 @@ __device__ __forceinline__ int slab_sums(const MarchLaunch& L, const rgx_march& 
         nstage += n;
         nhit += n;
         __syncwarp();
+        if (COUNT) tl.v[C_CYC_WINDOW] += clock64() - c_s;       // staging of the hits
         if (nstage > kStage - kFan) {
             long long c_a = COUNT ? clock64() : 0;
             eval_forward<COUNT>(ws, nstage, tau, s, c0, c1, c2, tl);

@@ -108,12 +108,21 @@ __device__ __forceinline__ void search_tile(const MarchLaunch& L, const Ray& r, 
             npend += __popc(m);
             if (COUNT) tl.v[C_CANDS] += 32;
             __syncwarp();
-            if (npend >= kFan && !test_pending<COUNT>(L, r, tmin, tmax, pend, npend, lane, tl, leaf)) return;
+            if (npend >= kFan) {
+                const long long c_t = COUNT ? clock64() : 0;
+                const bool go = test_pending<COUNT>(L, r, tmin, tmax, pend, npend, lane, tl, leaf);
+                if (COUNT) tl.v[C_CYC_WAIT] += clock64() - c_t;       // exact tests and what the caller does with the hits
+                if (!go) return;
+            }
         }
         if (any_beyond) break;
     }
-    while (npend > 0)
-        if (!test_pending<COUNT>(L, r, tmin, tmax, pend, npend, lane, tl, leaf)) return;
+    while (npend > 0) {
+        const long long c_t = COUNT ? clock64() : 0;
+        const bool go = test_pending<COUNT>(L, r, tmin, tmax, pend, npend, lane, tl, leaf);
+        if (COUNT) tl.v[C_CYC_WAIT] += clock64() - c_t;
+        if (!go) return;
+    }
 }
 
 // Closest hit over [tmin,tmax] in a tile list, +inf on a miss.
