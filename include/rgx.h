@@ -167,6 +167,15 @@ RGX_API int rgx_build(rgx_ctx* ctx, const rgx_scene* scene, float sigma_threshol
 RGX_API int rgx_forward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, const rgx_march* march,
                 float* rgb, float* alpha, float* depth, rgx_stream stream);
 
+/* Replaces: the viewer's ray generation program with its frame and depth buffers
+ * (cuda_gui/gaussians_aabb.cu:205-342; colour quantisation cuda_gui/helpers.h:45-58:
+ * clamp to [0,1], times 256, truncated, at most 255, no gamma; alpha byte 255).
+ * Same march as rgx_forward; frame_rgba8 is [R,4] bytes in a plain device buffer
+ * (no window, swapchain or graphics interop), depth [R] may be NULL.  The viewer
+ * composites over black: pass white_background = 0 for its exact output. */
+RGX_API int rgx_forward_frame(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, const rgx_march* march,
+                              unsigned char* frame_rgba8, float* depth, rgx_stream stream);
+
 /* Replaces: launch_pipeline_backward + reduce_temp_grads + compute_cupy_sh_grad
  * (render_optix.py:166-185; device code cuda_train/backward/gaussians_aabb.cu,
  * utils/sh_utils.cu:218-412).  rgb is the forward's output for the same camera,

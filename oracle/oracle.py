@@ -532,6 +532,15 @@ def march(positions, scales, quaternions, densities, rgb_g, cam: CameraParams, m
 
 
 # --------------------------------------------------------------------------- operator
+def quantize_frame(rgb):
+    """8-bit colour of the reference's viewer (cuda_gui/helpers.h:45-58): clamp to [0, 1],
+    times 256 in float32, truncated, at most 255; alpha byte 255.  ``rgb`` [..., 3] -> uint8 [..., 4]."""
+    import numpy as np
+    x = np.clip(np.asarray(rgb, dtype=np.float32), np.float32(0.0), np.float32(1.0))
+    q = np.minimum((x * np.float32(256.0)).astype(np.uint32), 255).astype(np.uint8)
+    return np.concatenate([q, np.full(q.shape[:-1] + (1,), 255, dtype=np.uint8)], axis=-1)
+
+
 def render_forward(positions, scales, quaternions, densities, color_features, sg_features, sharpness, lobe_axis,
                    camera, mp, supersampling=(1, 1), ray_ids=None, chunk=64):
     """Forward of render_optix.py:92-141 in float64: returns the march output and

@@ -60,6 +60,8 @@ SYMBOLS = {
     "rgx_build": (C.c_int, [C.c_void_p, C.POINTER(Scene), C.c_float, C.c_int, C.c_int, C.c_void_p]),
     "rgx_forward": (C.c_int, [C.c_void_p, C.POINTER(Scene), C.POINTER(Camera), C.POINTER(March), _fp, _fp, _fp,
                               C.c_void_p]),
+    "rgx_forward_frame": (C.c_int, [C.c_void_p, C.POINTER(Scene), C.POINTER(Camera), C.POINTER(March), _fp, _fp,
+                                    C.c_void_p]),
     "rgx_backward": (C.c_int, [C.c_void_p, C.POINTER(Scene), C.POINTER(Camera), C.POINTER(March), _fp, _fp,
                                C.POINTER(Grads), C.c_void_p]),
     "rgx_gaussian_colors": (C.c_int, [C.c_void_p, C.POINTER(Scene), C.POINTER(C.c_float), _fp, C.c_void_p]),

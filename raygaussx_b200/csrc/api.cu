@@ -452,12 +452,12 @@ static int prepare_march(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera*
     return RGX_OK;
 }
 
-int rgx_forward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, const rgx_march* march, float* rgb,
-                float* alpha, float* depth, rgx_stream stream) {
+static int forward_impl(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, const rgx_march* march, float* rgb,
+                        float* alpha, float* depth, uchar4* frame, rgx_stream stream) {
     MarchLaunch L{};
     int rc = prepare_march(ctx, scene, cam, march, L);
     if (rc) return rc;
-    if (!rgb) return fail(ctx, RGX_E_INVALID, "rgb output is null");
+    if (!rgb && !frame) return fail(ctx, RGX_E_INVALID, "colour output is null");
     cudaSetDevice(ctx->device);
     cudaStream_t s = (cudaStream_t)stream;
     if ((rc = run_colors(ctx, scene, cam->eye, s))) return rc;
@@ -465,7 +465,7 @@ int rgx_forward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, con
         if ((rc = ensure_lists(ctx, cam, march, s))) return rc;
         L.lists = ctx->lists;
     }
-    L.rgb = rgb; L.alpha = alpha; L.depth = depth;
+    L.rgb = rgb; L.alpha = alpha; L.depth = depth; L.frame = frame;
     cudaError_t e;
     const bool record = (march->flags & RGX_FLAG_SAVE_HITS) && L.lists.ent_id != nullptr && ctx->n > 0;
     if (march->flags & RGX_FLAG_SAVE_HITS) ctx->tape_valid = false;
@@ -524,6 +524,19 @@ int rgx_forward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, con
         ctx->tape_row_begin = march->row_begin; ctx->tape_row_end = march->row_end;
     }
     return RGX_OK;
+}
+
+int rgx_forward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, const rgx_march* march, float* rgb,
+                float* alpha, float* depth, rgx_stream stream) {
+    if (ctx && !rgb) return fail(ctx, RGX_E_INVALID, "rgb output is null");
+    return forward_impl(ctx, scene, cam, march, rgb, alpha, depth, nullptr, stream);
+}
+
+int rgx_forward_frame(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, const rgx_march* march,
+                      unsigned char* frame_rgba8, float* depth, rgx_stream stream) {
+    if (ctx && !frame_rgba8) return fail(ctx, RGX_E_INVALID, "frame buffer is null");
+    if (ctx && (reinterpret_cast<uintptr_t>(frame_rgba8) & 3u)) return fail(ctx, RGX_E_INVALID, "frame buffer must be 4-byte aligned");
+    return forward_impl(ctx, scene, cam, march, nullptr, nullptr, depth, reinterpret_cast<uchar4*>(frame_rgba8), stream);
 }
 
 int rgx_backward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, const rgx_march* march,

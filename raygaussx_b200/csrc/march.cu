@@ -84,11 +84,7 @@ __global__ void __launch_bounds__(kWarps * 32) march_forward_kernel(const __grid
             }
         }
         if (lane == 0) {                                                           // :326-339
-            L.rgb[3 * (size_t)ray_id] = fmaf(st.T, bg, st.Cr);
-            L.rgb[3 * (size_t)ray_id + 1] = fmaf(st.T, bg, st.Cg);
-            L.rgb[3 * (size_t)ray_id + 2] = fmaf(st.T, bg, st.Cb);
-            if (L.alpha) L.alpha[ray_id] = 1.0f - st.T;
-            if (L.depth) L.depth[ray_id] = st.depth;
+            write_ray(L, ray_id, st, bg);
         }
     }
     if (COUNT) flush_tally(L, tl, lane);

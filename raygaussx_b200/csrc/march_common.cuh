@@ -580,6 +580,22 @@ __device__ __forceinline__ void composite_forward(const SlabPlan& p, float tbuff
     st.T = slab_exit_T(tr, eps);
 }
 
+// 8-bit colour of the reference's viewer (cuda_gui/helpers.h:45-58): clamp to [0,1], times 256,
+// truncate, at most 255; no gamma.
+__device__ __forceinline__ unsigned char quantize8(float x) {
+    x = fminf(fmaxf(x, 0.0f), 1.0f);
+    return (unsigned char)min((unsigned int)__fmul_rn(x, 256.0f), 255u);
+}
+
+// What a ray leaves behind (cuda_train/forward/gaussians_aabb.cu:326-339; cuda_gui/gaussians_aabb.cu:330-342).
+__device__ __forceinline__ void write_ray(const MarchLaunch& L, int ray_id, const RayColor& st, float bg) {
+    const float r = fmaf(st.T, bg, st.Cr), g = fmaf(st.T, bg, st.Cg), b = fmaf(st.T, bg, st.Cb);
+    if (L.rgb) { L.rgb[3 * (size_t)ray_id] = r; L.rgb[3 * (size_t)ray_id + 1] = g; L.rgb[3 * (size_t)ray_id + 2] = b; }
+    if (L.frame) L.frame[ray_id] = make_uchar4(quantize8(r), quantize8(g), quantize8(b), 255u);
+    if (L.alpha) L.alpha[ray_id] = 1.0f - st.T;
+    if (L.depth) L.depth[ray_id] = st.depth;
+}
+
 // Per-sample terms of the backward (cuda_train/backward/gaussians_aabb.cu:330-352).
 struct SlabBackTerms {
     float beta, gamma, d_total;

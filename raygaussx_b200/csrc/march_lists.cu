@@ -284,11 +284,7 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 3) march_forward_lists_k
             }
         }
         if (lane == 0) {                                                           // :326-339
-            L.rgb[3 * (size_t)ray_id] = fmaf(st.T, bg, st.Cr);
-            L.rgb[3 * (size_t)ray_id + 1] = fmaf(st.T, bg, st.Cg);
-            L.rgb[3 * (size_t)ray_id + 2] = fmaf(st.T, bg, st.Cb);
-            if (L.alpha) L.alpha[ray_id] = 1.0f - st.T;
-            if (L.depth) L.depth[ray_id] = st.depth;
+            write_ray(L, ray_id, st, bg);
             if (save) L.ray_head[ray_id] = tape_ok ? tape_head : -2;
         }
         if (COUNT) tl.v[C_CYC_TOTAL] += clock64() - c_ray;

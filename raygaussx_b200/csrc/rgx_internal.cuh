@@ -99,9 +99,10 @@ struct MarchLaunch {
     const SceneBox* box;
     DeviceCounters* counters;
     // forward outputs / backward inputs
-    float* rgb;
+    float* rgb;           // [R,3]; may be null when frame is given
     float* alpha;
     float* depth;
+    uchar4* frame;        // [R] 8-bit colour (cuda_gui/helpers.h:45-58), or null
     const float* rgb_in;
     const float* dl_drgb;
     // "tape": what the forward met, kept for the backward (RGX_FLAG_SAVE_HITS).  Per slab with hits a chunk

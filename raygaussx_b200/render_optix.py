@@ -190,6 +190,17 @@ class Renderer:
                                                     _ptr(rgb), _ptr(alpha), _ptr(depth), self._stream()))
         return rgb, alpha, depth
 
+    def forward_frame(self, positions, scales, quaternions, densities, color_features, sg_features, sharpness,
+                      lobe_axis, cam: _Camera, march: _March, want_depth=True):
+        """The viewer's outputs (cuda_gui/gaussians_aabb.cu:205-342) into plain device
+        buffers: ``(frame [H, W, 4] uint8, depth [H, W] float32 or None)``."""
+        frame = torch.empty(cam.height, cam.width, 4, device=self.device, dtype=torch.uint8)
+        depth = torch.empty(cam.height, cam.width, device=self.device, dtype=torch.float32) if want_depth else None
+        sc = self._scene(positions, scales, quaternions, densities, color_features, sg_features, sharpness, lobe_axis)
+        _lib.check(self._ctx, self._lib.rgx_forward_frame(self._ctx, C.byref(sc), C.byref(cam), C.byref(march),
+                                                          _ptr(frame), _ptr(depth), self._stream()))
+        return frame, depth
+
     def backward(self, positions, scales, quaternions, densities, color_features, sg_features, sharpness, lobe_axis,
                  cam: _Camera, march: _March, rgb, dl_drgb, grads: Tuple[torch.Tensor, ...]):
         """``grads`` = (positions, scales, quaternions, densities, color_features[, sg, sharpness, axis])

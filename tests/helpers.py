@@ -44,3 +44,43 @@ def rel_max(a, b):
     a = torch.as_tensor(a, dtype=torch.float64)
     b = torch.as_tensor(b, dtype=torch.float64)
     return ((a - b).abs().max() / a.abs().max().clamp_min(1e-300)).item()
+
+
+class FakePointCloud:
+    """The accessors of the reference's classes/point_cloud.py that the forward-only entry points read,
+    over a generated scene (scales are kept as logarithms, as the reference does)."""
+
+    def __init__(self, sc, device="cpu"):
+        t = [x.to(device) for x in sc.tensors()]
+        self.positions, scales, self.quaternions, self.densities = t[0], t[1], t[2], t[3]
+        self.scales = torch.log(scales)
+        self._color = t[4]
+        self.sph_gauss_features, self._sharp, self.lobe_axis = t[5], t[6], t[7]
+        self.num_sph_gauss = t[5].shape[2]
+
+    def get_scale(self):
+        return torch.exp(self.scales)
+
+    def get_normalized_quaternion(self):
+        return self.quaternions / torch.norm(self.quaternions, dim=1)[:, None]
+
+    def get_density(self):
+        return self.densities
+
+    def get_color_features(self):
+        return self._color
+
+    def get_bandwidth_sharpness(self):
+        return self._sharp
+
+    def get_normalized_lobe_axis(self):
+        return self.lobe_axis
+
+    def project_points(self, camera):
+        return torch.matmul(self.positions, camera.world_view_transform[:3, :3]) + camera.world_view_transform[3, :3]
+
+    def select_inside_mask(self, mask):
+        return (self.positions[mask].contiguous(), self._color[mask].contiguous(), self.densities[mask].contiguous(),
+                self.get_scale()[mask].contiguous(), self.get_normalized_quaternion()[mask].contiguous(),
+                self.sph_gauss_features[mask].contiguous(), self._sharp[mask].contiguous(),
+                self.lobe_axis[mask].contiguous())
