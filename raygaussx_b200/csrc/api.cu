@@ -69,6 +69,7 @@ struct rgx_ctx {
     long long* ray_head = nullptr;
     long long ray_head_cap = 0;
     bool tape_valid = false;
+    unsigned long long rgba_serial = 0, tape_rgba_serial = 0;   // which evaluation of the per-view colours is in rgba / was recorded with
     unsigned long long tape_build_id = 0;
     rgx_camera tape_cam{};
     int tape_row_begin = 0, tape_row_end = 0;
@@ -212,6 +213,7 @@ int run_colors(rgx_ctx* ctx, const rgx_scene* sc, const float eye[3], cudaStream
     c.perm = ctx->vals_out;
     c.rgba = ctx->rgba;
     c.sigma_threshold = ctx->sigma_threshold;
+    ctx->rgba_serial++;
     cudaError_t e = launch_colors(c, s);
     return e == cudaSuccess ? RGX_OK : cuda_fail(ctx, e, "colour kernel");
 }
@@ -519,6 +521,7 @@ static int forward_impl(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* 
     if (recorded) {
         cudaMemcpyAsync(ctx->tape_used_host, ctx->tape_used, sizeof(unsigned long long), cudaMemcpyDeviceToHost, s);
         ctx->tape_valid = true;
+        ctx->tape_rgba_serial = ctx->rgba_serial;
         ctx->tape_build_id = ctx->build_id;
         ctx->tape_cam = *cam;
         ctx->tape_row_begin = march->row_begin; ctx->tape_row_end = march->row_end;
@@ -553,7 +556,12 @@ int rgx_backward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, co
     if (scene->n == 0) return RGX_OK;
     cudaSetDevice(ctx->device);
     cudaStream_t s = (cudaStream_t)stream;
-    if ((rc = run_colors(ctx, scene, cam->eye, s))) return rc;
+    // a backward that replays the recording of this very view finds the forward's per-view colours still in place
+    const bool replays = ctx->tape_valid && ctx->tape_build_id == ctx->build_id &&
+                         ctx->tape_row_begin == march->row_begin && ctx->tape_row_end == march->row_end &&
+                         std::memcmp(&ctx->tape_cam, cam, sizeof(rgx_camera)) == 0 &&
+                         !(march->flags & (RGX_FLAG_BRUTE_FORCE | RGX_FLAG_PER_RAY_SEARCH));
+    if (!(replays && ctx->rgba_serial == ctx->tape_rgba_serial) && (rc = run_colors(ctx, scene, cam->eye, s))) return rc;
     cudaError_t e = cudaMemsetAsync(ctx->grad_rows, 0, sizeof(float4) * 4 * (size_t)ctx->n_pad * (size_t)ctx->grad_copies, s);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "backward memset");
     if (!(march->flags & (RGX_FLAG_BRUTE_FORCE | RGX_FLAG_PER_RAY_SEARCH))) {
