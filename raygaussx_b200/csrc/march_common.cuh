@@ -1,7 +1,7 @@
 // Device helpers shared by the march kernels: ray set-up, ray/box and
-// ray/ellipsoid tests, the three ways of enumerating the Gaussians of a query
-// (exhaustive, per-ray hierarchy search, shared candidate list), the slab
-// schedule and the per-sample evaluation.
+// ray/ellipsoid tests, enumeration of the Gaussians of a query by exhaustive loop
+// or per-ray hierarchy search (the tile-list enumeration is in march_lists.cu),
+// the slab schedule, the per-sample evaluation and the gradient of a hit.
 #pragma once
 #include "rgx_internal.cuh"
 #include "device_math.cuh"
@@ -288,64 +288,6 @@ __device__ __forceinline__ float search_closest(const MarchLaunch& L, const Ray&
         }
     }
     return best;
-}
-
-// Candidate list of a tile window: ascending sorted indices with, per entry, a
-// conservative range of distances from the eye (= ray parameters) that its box spans.
-struct CandList {
-    const int* id;
-    const float* lo;
-    const float* hi;
-    int n;
-    int* pend;      // per-warp scratch, 2 * kFan ints
-};
-
-// Any-hit search over a candidate list that is known to contain every Gaussian the
-// query can hit.  Entries are first filtered by their depth range (shared memory
-// only); survivors are compacted, in order, into full groups of 32 for the exact test.
-template <bool COUNT, class LeafFn>
-__device__ __forceinline__ void search_list(const MarchLaunch& L, const Ray& r, float tmin, float tmax,
-                                            const CandList& c, int lane, Tally& tl, LeafFn&& leaf) {
-    int npend = 0;
-    for (int base = 0; base < c.n; base += kFan) {
-        int k = base + lane;
-        bool pass = k < c.n && c.lo[k] <= tmax && c.hi[k] >= tmin;
-        unsigned m = __ballot_sync(kFull, pass);
-        if (pass) c.pend[npend + __popc(m & ((1u << lane) - 1u))] = c.id[k];
-        npend += __popc(m);
-        __syncwarp();
-        if (npend >= kFan) {
-            int j = c.pend[lane];
-            LeafTest t = test_gaussian(L, r, j, true, tmin, tmax, tl, COUNT);
-            bool go = leaf(t, j);
-            int moved = (lane + kFan < npend) ? c.pend[lane + kFan] : 0;
-            __syncwarp();
-            c.pend[lane] = moved;
-            npend -= kFan;
-            __syncwarp();
-            if (!go) return;
-        }
-    }
-    if (npend > 0) {
-        bool valid = lane < npend;
-        int j = valid ? c.pend[lane] : 0;
-        LeafTest t = test_gaussian(L, r, j, valid, tmin, tmax, tl, COUNT);
-        leaf(t, j);
-        __syncwarp();
-    }
-}
-
-// Closest hit among the candidates, +inf if none.
-template <bool COUNT>
-__device__ __forceinline__ float closest_in_list(const MarchLaunch& L, const Ray& r, float tmin, float tmax,
-                                                 const CandList& c, int lane, Tally& tl) {
-    float best = INFINITY;
-    if (!(tmin <= tmax)) return best;
-    search_list<COUNT>(L, r, tmin, tmax, c, lane, tl, [&](const LeafTest& t, int) {
-        if (t.hit) best = fminf(best, t.t_hit);
-        return true;
-    });
-    return warp_min_f(best);
 }
 
 // ---------------------------------------------------------------- per-ray state machine shared by both passes

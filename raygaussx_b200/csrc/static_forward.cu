@@ -145,10 +145,9 @@ extern "C" RGX_API int rgx_forward_static(int device, const rgx_scene* scene, co
     hier.num_levels = lv.num_levels;
     for (int l = 0; l < kMaxLevels; ++l) { hier.offset[l] = lv.offset[l]; hier.count[l] = lv.count[l]; }
 
-    cudaError_t e;
     if (n == 0) {
         hier.count[0] = hier.count[1] = 0;
-        if ((e = cudaMemsetAsync(b.box, 0, sizeof(SceneBox), s)) != cudaSuccess) return RGX_E_CUDA;
+        if (cudaMemsetAsync(b.box, 0, sizeof(SceneBox), s) != cudaSuccess) return RGX_E_CUDA;
     } else {
         b.sc = *scene;
         b.sigma_threshold = sigma_threshold;
@@ -157,14 +156,14 @@ extern "C" RGX_API int rgx_forward_static(int device, const rgx_scene* scene, co
         b.n_pad = n_pad;
         b.num_levels = lv.num_levels;
         for (int l = 0; l < kMaxLevels; ++l) { b.offset[l] = lv.offset[l]; b.count[l] = lv.count[l]; }
-        if ((e = launch_build(b, s)) != cudaSuccess) return RGX_E_CUDA;
+        if (launch_build(b, s) != cudaSuccess) return RGX_E_CUDA;
         ColorLaunch c{};
         c.sc = *scene;
         c.eye[0] = cam->eye[0]; c.eye[1] = cam->eye[1]; c.eye[2] = cam->eye[2];
         c.perm = b.vals_out;
         c.rgba = rgba;
         c.sigma_threshold = sigma_threshold;
-        if ((e = launch_colors(c, s)) != cudaSuccess) return RGX_E_CUDA;
+        if (launch_colors(c, s) != cudaSuccess) return RGX_E_CUDA;
     }
     MarchLaunch L{};
     L.h = hier;
@@ -177,6 +176,6 @@ extern "C" RGX_API int rgx_forward_static(int device, const rgx_scene* scene, co
     L.box = b.box;
     L.counters = nullptr;
     L.rgb = rgb; L.alpha = alpha; L.depth = depth;
-    if ((e = launch_march_forward(L, s)) != cudaSuccess) return RGX_E_CUDA;
+    if (launch_march_forward(L, s) != cudaSuccess) return RGX_E_CUDA;
     return RGX_OK;
 }

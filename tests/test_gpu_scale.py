@@ -76,3 +76,46 @@ def test_full_size_backward_properties(big):
         # Only the order of fp32 atomic additions differs; Gaussians that cover much of the image sum
         # ~10^5 contributions of both signs, which bounds the agreement well above one ulp.
         assert ((a - b).abs().max() / a.abs().max()).item() < 3e-3
+
+
+@pytest.mark.parametrize("cam_index", [0, 1, 2])
+def test_tile_lists_find_every_hit_with_the_camera_inside_the_scene(cam_index):
+    """The unbounded scene surrounds its cameras: Gaussians behind the eye, Gaussians that straddle the eye
+    plane, Gaussians that fill the view.  The per-view tile lists must still hold every hit of every ray:
+    same hit hash and counts as the per-ray search of the hierarchy."""
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device: there is no CPU path")
+    from raygaussx_b200 import render_optix as ro
+    dev = torch.device("cuda")
+    sc = scenes.unbounded_scene(n=200_000, n_cameras=3, width=314, height=207)
+    tens = [t.to(dev).contiguous() for t in sc.tensors()]
+    cam = sc.cameras[cam_index]
+    cam.to(dev)
+    cs = ro.camera_struct(cam)
+    r = ro.get_renderer()
+    r.build(*tens[:4])
+    got = {}
+    for label, flags in (("lists", 0), ("per_ray", _lib.FLAG_PER_RAY_SEARCH)):
+        r.reset_counters()
+        rgb, _, _ = r.forward(*tens, cs, march(ro, sc, cs, flags=flags | _lib.FLAG_COUNT_WORK))
+        got[label] = (rgb.clone(), r.read_counters())
+    a, b = got["lists"][1], got["per_ray"][1]
+    assert a["hits_hash"] == b["hits_hash"]
+    for k in ("rays", "slabs", "slabs_hit", "closest_queries", "hits", "overflow_slabs"):
+        assert a[k] == b[k], k
+    # hits are met in a different order, sums differ in the last bit, and with them now and then the step size:
+    # a sample at the very edge of an ellipsoid may fall on the other side
+    assert abs(a["pairs_inside"] - b["pairs_inside"]) <= 1e-6 * b["pairs_inside"]
+    assert a["hits"] > 50 * a["rays"]                      # the case is not trivial
+    assert (got["lists"][0] - got["per_ray"][0]).abs().max().item() < 1e-5
+    # a recorded forward and its replayed backward against a searched backward, at this size
+    rgb, _, _ = r.forward(*tens, cs, march(ro, sc, cs, flags=_lib.FLAG_SAVE_HITS))
+    dl = torch.sign(rgb - 0.5) / (3 * rgb.shape[0])
+    replayed = [torch.zeros_like(t) for t in tens]
+    r.backward(*tens, cs, march(ro, sc, cs), rgb, dl, tuple(replayed))
+    r.forward(*tens, cs, march(ro, sc, cs, flags=_lib.FLAG_SAVE_HITS, rows=(0, 8)))      # overwrites the recording
+    searched = [torch.zeros_like(t) for t in tens]
+    r.backward(*tens, cs, march(ro, sc, cs), rgb, dl, tuple(searched))
+    torch.cuda.synchronize()
+    for x, y in zip(replayed[:5], searched[:5]):
+        assert ((x - y).abs().max() / y.abs().max().clamp_min(1e-30)).item() < 2e-3
