@@ -43,6 +43,7 @@ struct rgx_ctx {
     uint32_t *bin_vals_in = nullptr, *bin_vals_out = nullptr;
     int *tile_first = nullptr, *tile_last = nullptr, *tile_cnt = nullptr, *tile_pcnt = nullptr, *tile_pbegin = nullptr;
     int *tile_iota = nullptr, *tile_cnt_sorted = nullptr, *tile_order = nullptr;
+    int* tile_unrecorded = nullptr;   // per tile: some ray of the latest recording forward could not be recorded
     int* ent_id = nullptr;
     float2 *ent_range = nullptr, *ent_blk = nullptr;
     float4* tile_dir = nullptr;
@@ -261,7 +262,7 @@ void rgx_destroy(rgx_ctx* ctx) {
                     ctx->g2, ctx->quat, ctx->sdens, ctx->rgba, ctx->grad_rows, ctx->hk, ctx->refit_counters,
                     ctx->cub_temp, ctx->bounds, ctx->box, ctx->counters, ctx->bin_keys_in, ctx->bin_keys_out, ctx->bin_vals_in, ctx->bin_vals_out,
                     ctx->tile_first, ctx->tile_last, ctx->tile_cnt, ctx->tile_pcnt, ctx->tile_pbegin, ctx->ent_id,
-                    ctx->ent_range, ctx->ent_blk, ctx->bin_cub, ctx->bin_total_dev, ctx->tape, ctx->tape_used, ctx->ray_head, ctx->tile_dir, ctx->tile_iota, ctx->tile_cnt_sorted, ctx->tile_order, ctx->big_slot, ctx->big_rect};
+                    ctx->ent_range, ctx->ent_blk, ctx->bin_cub, ctx->bin_total_dev, ctx->tape, ctx->tape_used, ctx->ray_head, ctx->tile_dir, ctx->tile_iota, ctx->tile_cnt_sorted, ctx->tile_order, ctx->big_slot, ctx->big_rect, ctx->tile_unrecorded};
     for (void* p : ptrs)
         if (p) cudaFree(p);
     if (ctx->bin_total_host) cudaFreeHost(ctx->bin_total_host);
@@ -365,7 +366,7 @@ static int ensure_lists(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m,
     if (ntiles + 1 > ctx->bin_tiles_cap) {
         size_t c = (size_t)ntiles + 1 + 64;
         RGB_(tile_first, c); RGB_(tile_last, c); RGB_(tile_cnt, c); RGB_(tile_pcnt, c); RGB_(tile_pbegin, c);
-        RGB_(tile_dir, c); RGB_(tile_iota, c); RGB_(tile_cnt_sorted, c); RGB_(tile_order, c);
+        RGB_(tile_dir, c); RGB_(tile_iota, c); RGB_(tile_cnt_sorted, c); RGB_(tile_order, c); RGB_(tile_unrecorded, c);
         ctx->bin_tiles_cap = (int)c;
     }
     auto grow_pairs = [&](size_t pairs) -> cudaError_t {
@@ -506,10 +507,12 @@ static int forward_impl(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* 
                 ctx->tape_cap = want;
             }
         }
-        if ((e = cudaMemsetAsync(ctx->tape_used, 0, sizeof(unsigned long long), s)) != cudaSuccess)
+        if ((e = cudaMemsetAsync(ctx->tape_used, 0, sizeof(unsigned long long), s)) != cudaSuccess ||
+            (e = cudaMemsetAsync(ctx->tile_unrecorded, 0, sizeof(int) * (size_t)(L.lists.tiles_x * L.lists.tiles_y), s)) != cudaSuccess)
             return cuda_fail(ctx, e, "tape");
         if (ctx->tape) {
             L.tape = ctx->tape; L.tape_used = ctx->tape_used; L.tape_cap = ctx->tape_cap; L.ray_head = ctx->ray_head;
+            L.tile_unrecorded = ctx->tile_unrecorded;
         }
     }
     const bool recorded = L.tape != nullptr;
@@ -572,6 +575,7 @@ int rgx_backward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, co
         ctx->tape_row_begin == march->row_begin && ctx->tape_row_end == march->row_end &&
         std::memcmp(&ctx->tape_cam, cam, sizeof(rgx_camera)) == 0) {
         L.tape = ctx->tape; L.tape_used = ctx->tape_used; L.tape_cap = ctx->tape_cap; L.ray_head = ctx->ray_head;
+        L.tile_unrecorded = ctx->tile_unrecorded;
     }
     L.rgb_in = rgb; L.dl_drgb = dL_drgb; L.grad_rows = ctx->grad_rows; L.grad_copies = ctx->grad_copies;
     {

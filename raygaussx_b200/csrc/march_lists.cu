@@ -285,7 +285,10 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 3) march_forward_lists_k
         }
         if (lane == 0) {                                                           // :326-339
             write_ray(L, ray_id, st, bg);
-            if (save) L.ray_head[ray_id] = tape_ok ? tape_head : -2;
+            if (save) {
+                L.ray_head[ray_id] = tape_ok ? tape_head : -2;
+                if (!tape_ok) L.tile_unrecorded[tile] = 1;
+            }
         }
         if (COUNT) tl.v[C_CYC_TOTAL] += clock64() - c_ray;
     }
@@ -475,6 +478,7 @@ __global__ void __launch_bounds__(kThreads) march_backward_lists_kernel(const __
     WarpStage& ws = sh.ws[warp];
     int* pend = sh.pend[warp];
     const int tile = L.lists.tile_order ? __ldg(&L.lists.tile_order[blockIdx.x]) : blockIdx.x;
+    if (L.tape && !L.tile_unrecorded[tile]) return;             // every ray of the tile was recorded: the replay kernel's
     const int tile_x = tile % L.lists.tiles_x, tile_y = tile / L.lists.tiles_x;
     const float eps = L.m.transmittance_eps;
     const SceneBox box = *L.box;

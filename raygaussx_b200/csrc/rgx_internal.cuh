@@ -112,6 +112,7 @@ struct MarchLaunch {
     unsigned long long* tape_used;
     long long tape_cap;
     long long* ray_head;
+    int* tile_unrecorded;   // per tile (of the lists): set by the forward when a ray of the tile got ray_head = -2
     float4* grad_rows;    // [grad_copies, n_pad, 4] float4 of accumulated moments, layout in emit_global
     int grad_copies;      // power of two
 };
