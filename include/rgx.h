@@ -203,6 +203,12 @@ RGX_API int rgx_set_profiling(rgx_ctx* ctx, int enable);
 RGX_API int rgx_read_kernel_times(rgx_ctx* ctx, float* forward_ms, int* forward_launches, float* backward_ms,
                                   int* backward_launches);
 
+/* Test hook (no counterpart in the reference): the workspace allocation that follows `nth` more successful
+ * ones fails as if the device were out of memory, without touching the device (nth < 0 switches the hook
+ * off).  After any failed allocation the call in progress returns RGX_E_CUDA, and the next call on the context
+ * releases the whole workspace, so that RGX_E_NOT_BUILT is returned until rgx_build is called again. */
+RGX_API int rgx_debug_fail_allocation(rgx_ctx* ctx, int nth);
+
 /* Per-view tile-list construction (binning + sort), timed like the march kernels while
  * profiling is enabled: summed milliseconds and number of constructions since the last
  * read, and the number of (tile, Gaussian) pairs of the latest one. */

@@ -12,6 +12,8 @@ using namespace rgx;
 struct rgx_ctx {
     int device = 0;
     std::string error;
+    bool alloc_failed = false;  // an allocation failed: the workspace is dropped at the next entry point
+    int fail_alloc_in = -1;     // test hook: the allocation after this many more fails (rgx_debug_fail_allocation)
     // workspace (device), grown on demand
     int cap_n_pad = 0;          // capacity in sorted slots
     int cap_boxes = 0;
@@ -100,12 +102,58 @@ cudaError_t regrow(rgx_ctx* ctx, T*& p, size_t count) {
         ctx->alloc_bytes.erase((void*)p);
     }
     p = nullptr;
-    cudaError_t e = cudaMalloc((void**)&p, count * sizeof(T));
+    cudaError_t e = cudaErrorMemoryAllocation;
+    if (ctx->fail_alloc_in == 0) ctx->fail_alloc_in = -1;                      // injected failure, nothing is allocated
+    else {
+        if (ctx->fail_alloc_in > 0) --ctx->fail_alloc_in;
+        e = cudaMalloc((void**)&p, count * sizeof(T));
+    }
     if (e == cudaSuccess) {
         ctx->bytes += count * sizeof(T);
         ctx->alloc_bytes[(void*)p] = count * sizeof(T);
+    } else {
+        p = nullptr;
+        ctx->alloc_failed = true;       // capacities no longer describe the arrays: see release_workspace
+        (void)cudaGetLastError();
     }
     return e;
+}
+
+// Frees every device array of the context and forgets what was built.  Called at the next entry point after
+// an allocation failed half way through growing the workspace, so that no stale capacity can send a null or
+// short array to a kernel: the caller gets RGX_E_NOT_BUILT until it calls rgx_build again.
+void release_workspace(rgx_ctx* ctx) {
+    cudaDeviceSynchronize();
+    void** ptrs[] = {(void**)&ctx->keys_in, (void**)&ctx->keys_out, (void**)&ctx->vals_in, (void**)&ctx->vals_out,
+                     (void**)&ctx->bx, (void**)&ctx->by, (void**)&ctx->bz, (void**)&ctx->g0, (void**)&ctx->g1,
+                     (void**)&ctx->g2, (void**)&ctx->quat, (void**)&ctx->sdens, (void**)&ctx->rgba,
+                     (void**)&ctx->grad_rows, (void**)&ctx->hk, (void**)&ctx->refit_counters, (void**)&ctx->cub_temp,
+                     (void**)&ctx->bounds, (void**)&ctx->box, (void**)&ctx->counters, (void**)&ctx->bin_keys_in,
+                     (void**)&ctx->bin_keys_out, (void**)&ctx->bin_vals_in, (void**)&ctx->bin_vals_out,
+                     (void**)&ctx->tile_first, (void**)&ctx->tile_last, (void**)&ctx->tile_cnt, (void**)&ctx->tile_pcnt,
+                     (void**)&ctx->tile_pbegin, (void**)&ctx->ent_id, (void**)&ctx->ent_range, (void**)&ctx->ent_blk,
+                     (void**)&ctx->bin_cub, (void**)&ctx->bin_total_dev, (void**)&ctx->tape, (void**)&ctx->tape_used,
+                     (void**)&ctx->ray_head, (void**)&ctx->tile_dir, (void**)&ctx->tile_iota,
+                     (void**)&ctx->tile_cnt_sorted, (void**)&ctx->tile_order, (void**)&ctx->big_slot,
+                     (void**)&ctx->big_rect, (void**)&ctx->tile_unrecorded};
+    for (void** p : ptrs) {
+        if (*p) cudaFree(*p);
+        *p = nullptr;
+    }
+    ctx->alloc_bytes.clear();
+    ctx->bytes = 0;
+    ctx->cap_n_pad = ctx->cap_boxes = 0;
+    ctx->cap_cub = 0;
+    ctx->bin_tiles_cap = 0;
+    ctx->bin_pair_cap = ctx->bin_ent_cap = ctx->bin_cub_cap = 0;
+    ctx->big_cap = 0;
+    ctx->tape_cap = 0;
+    ctx->ray_head_cap = 0;
+    ctx->built = false;
+    ctx->lists_valid = false;
+    ctx->tape_valid = false;
+    ctx->lists = TileLists{};
+    ctx->alloc_failed = false;
 }
 
 struct Levels {
@@ -134,6 +182,7 @@ Levels plan_levels(int n) {
 
 int ensure_workspace(rgx_ctx* ctx, int n_pad, int boxes) {
     cudaError_t e = cudaSuccess;
+    if (ctx->alloc_failed) release_workspace(ctx);
     if (!ctx->bounds) {
         if ((e = regrow(ctx, ctx->bounds, 12)) != cudaSuccess) return cuda_fail(ctx, e, "workspace");
         if ((e = regrow(ctx, ctx->box, 1)) != cudaSuccess) return cuda_fail(ctx, e, "workspace");
@@ -173,6 +222,7 @@ int ensure_workspace(rgx_ctx* ctx, int n_pad, int boxes) {
 
 int check_scene(rgx_ctx* ctx, const rgx_scene* sc, bool need_color) {
     if (!ctx) return RGX_E_INVALID;
+    if (ctx->alloc_failed) { cudaSetDevice(ctx->device); release_workspace(ctx); }
     if (!sc) return fail(ctx, RGX_E_INVALID, "scene is null");
     if (sc->n < 0) return fail(ctx, RGX_E_INVALID, "negative Gaussian count");
     if (sc->n > (1 << 30)) return fail(ctx, RGX_E_TOO_LARGE, "more than 2^30 Gaussians");
@@ -258,13 +308,7 @@ int rgx_create(int device, rgx_ctx** out) {
 void rgx_destroy(rgx_ctx* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
-    void* ptrs[] = {ctx->keys_in, ctx->keys_out, ctx->vals_in, ctx->vals_out, ctx->bx, ctx->by, ctx->bz, ctx->g0, ctx->g1,
-                    ctx->g2, ctx->quat, ctx->sdens, ctx->rgba, ctx->grad_rows, ctx->hk, ctx->refit_counters,
-                    ctx->cub_temp, ctx->bounds, ctx->box, ctx->counters, ctx->bin_keys_in, ctx->bin_keys_out, ctx->bin_vals_in, ctx->bin_vals_out,
-                    ctx->tile_first, ctx->tile_last, ctx->tile_cnt, ctx->tile_pcnt, ctx->tile_pbegin, ctx->ent_id,
-                    ctx->ent_range, ctx->ent_blk, ctx->bin_cub, ctx->bin_total_dev, ctx->tape, ctx->tape_used, ctx->ray_head, ctx->tile_dir, ctx->tile_iota, ctx->tile_cnt_sorted, ctx->tile_order, ctx->big_slot, ctx->big_rect, ctx->tile_unrecorded};
-    for (void* p : ptrs)
-        if (p) cudaFree(p);
+    release_workspace(ctx);
     if (ctx->bin_total_host) cudaFreeHost(ctx->bin_total_host);
     if (ctx->tape_used_host) cudaFreeHost(ctx->tape_used_host);
     for (auto* v : {&ctx->timed, &ctx->spare})
@@ -503,6 +547,7 @@ static int forward_impl(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* 
                 (void)cudaGetLastError();
                 ctx->tape = nullptr;
                 ctx->tape_cap = 0;
+                ctx->alloc_failed = false;     // nothing else depends on this array
             } else {
                 ctx->tape_cap = want;
             }
@@ -612,6 +657,7 @@ int rgx_gaussian_colors(rgx_ctx* ctx, const rgx_scene* scene, const float eye[3]
 
 int rgx_scene_box(rgx_ctx* ctx, float bb_min[3], float bb_max[3], rgx_stream stream) {
     if (!ctx || !bb_min || !bb_max) return RGX_E_INVALID;
+    if (ctx->alloc_failed) { cudaSetDevice(ctx->device); release_workspace(ctx); }
     if (!ctx->built) return fail(ctx, RGX_E_NOT_BUILT, "rgx_build has not been called");
     cudaSetDevice(ctx->device);
     SceneBox h;
@@ -620,6 +666,12 @@ int rgx_scene_box(rgx_ctx* ctx, float bb_min[3], float bb_max[3], rgx_stream str
     if (e != cudaSuccess) return cuda_fail(ctx, e, "scene box read-back");
     std::memcpy(bb_min, h.lo, sizeof(h.lo));
     std::memcpy(bb_max, h.hi, sizeof(h.hi));
+    return RGX_OK;
+}
+
+int rgx_debug_fail_allocation(rgx_ctx* ctx, int nth) {
+    if (!ctx) return RGX_E_INVALID;
+    ctx->fail_alloc_in = nth;
     return RGX_OK;
 }
 

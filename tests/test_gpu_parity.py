@@ -267,3 +267,59 @@ def test_c_abi_rejects_bad_arguments(ro):
     with pytest.raises(_lib.RgxError) as e:
         r.forward(*t2, cs, ro._settings_march(st, cs))          # built for a different Gaussian count
     assert e.value.code == _lib.RGX_E_NOT_BUILT
+
+
+def test_a_failed_allocation_leaves_a_usable_context(ro):
+    """An allocation that fails half way through growing the workspace (injected on the host: nothing is
+    asked of the device) must not leave stale capacities behind: the call fails, the next one reports that
+    nothing is built, and after a new build the context renders as before."""
+    import ctypes as C
+    sc = make_scene("small_static")
+    dev = torch.device("cuda")
+    tens = [t.to(dev).contiguous() for t in sc.tensors()]
+    cam = sc.cameras[0]
+    cam.to(dev)
+    cs = ro.camera_struct(cam)
+    march = ro._settings_march(settings_for(ro, sc, cam), cs)
+    r = ro.Renderer(dev)                                  # a context of its own: the hook is per context
+    fail_in = lambda n: _lib.check(r._ctx, r._lib.rgx_debug_fail_allocation(r._ctx, C.c_int(n)))
+    # 1. in the build of a fresh context, at several depths of the workspace set-up
+    for nth in (0, 3, 9, 17):
+        fail_in(nth)
+        with pytest.raises(_lib.RgxError) as err:
+            r.build(*tens[:4])
+        assert err.value.code == _lib.RGX_E_CUDA
+        fail_in(-1)
+        with pytest.raises(_lib.RgxError) as err:         # nothing is built: the forward says so, touches nothing
+            r.forward(*tens, cs, march)
+        assert err.value.code == _lib.RGX_E_NOT_BUILT
+    r.build(*tens[:4])
+    want, _, _ = r.forward(*tens, cs, march)
+    # 2. in the tile lists of a view
+    cam2 = make_scene("small_static").cameras[0]
+    cam2.image_width, cam2.image_height = 24, 20          # another view: its lists have to be made
+    cam2.to(dev)
+    cs2 = ro.camera_struct(cam2)
+    march2 = ro._settings_march(settings_for(ro, sc, cam2), cs2)
+    fail_in(0)
+    with pytest.raises(_lib.RgxError):
+        r.forward(*tens, cs2, march2)
+    fail_in(-1)
+    with pytest.raises(_lib.RgxError) as err:
+        r.forward(*tens, cs, march)
+    assert err.value.code == _lib.RGX_E_NOT_BUILT
+    r.build(*tens[:4])
+    again, _, _ = r.forward(*tens, cs, march)
+    assert torch.equal(want, again)
+    # 3. a recording that cannot be allocated is not an error: the forward renders without it, the backward searches
+    fail_in(2)                                            # counter, per-ray heads, then the recording itself
+    rgb, _, _ = r.forward(*tens, cs, ro._settings_march(settings_for(ro, sc, cam), cs, flags=_lib.FLAG_SAVE_HITS))
+    fail_in(-1)
+    assert torch.equal(rgb, want)
+    dl = loss_gradient(rgb.cpu().double(), rgb.shape[0])
+    searched = backward(ro, r, sc, tens, cs, rgb, dl)
+    r.forward(*tens, cs, ro._settings_march(settings_for(ro, sc, cam), cs, flags=_lib.FLAG_SAVE_HITS))
+    replayed = backward(ro, r, sc, tens, cs, rgb, dl)
+    for a, b in zip(searched[:5], replayed[:5]):
+        assert rel_max(a.cpu(), b.cpu()) < 1e-4
+    del r
