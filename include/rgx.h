@@ -203,6 +203,14 @@ RGX_API int rgx_set_profiling(rgx_ctx* ctx, int enable);
 RGX_API int rgx_read_kernel_times(rgx_ctx* ctx, float* forward_ms, int* forward_launches, float* backward_ms,
                                   int* backward_launches);
 
+/* Replaces: distCUDA2 of the reference's simple-knn submodule (submodules/simple-knn/simple_knn.cu,
+ * SimpleKNN::knn; called from classes/point_cloud.py:252,592 to size the first Gaussians).
+ * points [n,3] -> mean_dist2 [n]: the mean of the squared distances from each point to its three nearest
+ * other points, exact (Morton sort, two levels of boxes of 32, one warp per 32 queries).  With fewer than
+ * four points the missing neighbours count as FLT_MAX, as in the reference.  Needs no context; allocates
+ * and frees its scratch (about 70 bytes per point) inside the call and synchronises the stream. */
+RGX_API int rgx_knn_mean_dist2(int device, const float* points, int n, float* mean_dist2, rgx_stream stream);
+
 /* Test hook (no counterpart in the reference): the workspace allocation that follows `nth` more successful
  * ones fails as if the device were out of memory, without touching the device (nth < 0 switches the hook
  * off).  After any failed allocation the call in progress returns RGX_E_CUDA, and the next call on the context

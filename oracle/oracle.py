@@ -532,6 +532,24 @@ def march(positions, scales, quaternions, densities, rgb_g, cam: CameraParams, m
 
 
 # --------------------------------------------------------------------------- operator
+def knn_mean_dist2(points):
+    """Mean of the squared distances from every point to its three nearest other points, by brute force in
+    float64 (what SimpleKNN::knn computes, submodules/simple-knn/simple_knn.cu: a point is excluded by its
+    index, so a duplicate counts with distance zero; missing neighbours count as FLT_MAX)."""
+    import numpy as np
+    p = np.asarray(points, dtype=np.float64)
+    n = p.shape[0]
+    out = np.empty(n, dtype=np.float64)
+    flt_max = float(np.finfo(np.float32).max)
+    for i in range(n):
+        d = ((p - p[i]) ** 2).sum(axis=1)
+        d = np.delete(d, i)
+        best = np.sort(d)[:3].tolist()
+        best += [flt_max] * (3 - len(best))
+        out[i] = (best[0] + best[1] + best[2]) / 3.0
+    return out
+
+
 def quantize_frame(rgb):
     """8-bit colour of the reference's viewer (cuda_gui/helpers.h:45-58): clamp to [0, 1],
     times 256 in float32, truncated, at most 255; alpha byte 255.  ``rgb`` [..., 3] -> uint8 [..., 4]."""

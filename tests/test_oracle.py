@@ -199,3 +199,16 @@ def test_counters_and_ray_subsets():
     ids = torch.tensor([0, 7, 35])
     part, _ = oracle.render_forward(*sc.tensors(), cam, sc.march, ray_ids=ids)
     assert (part.rgb - full.rgb[ids]).abs().max() < 1e-12
+
+
+def test_knn_mean_dist2_known_answers():
+    from oracle import oracle as orc
+    # unit-spaced points on a line: inner points see 1, 1, 4; the ends 1, 4, 9
+    pts = np.stack([np.arange(6.0), np.zeros(6), np.zeros(6)], axis=1)
+    got = orc.knn_mean_dist2(pts)
+    assert np.allclose(got, [14 / 3, 6 / 3, 6 / 3, 6 / 3, 6 / 3, 14 / 3])
+    # a duplicate counts with distance zero; fewer than four points: missing neighbours are FLT_MAX
+    assert np.allclose(orc.knn_mean_dist2(np.array([[0.0, 0, 0], [0, 0, 0], [1, 0, 0], [0, 2, 0]])),
+                       [5 / 3, 5 / 3, 7 / 3, 13 / 3])
+    two = orc.knn_mean_dist2(np.array([[0.0, 0, 0], [3, 4, 0]]))
+    assert np.all(two > 1e38)
