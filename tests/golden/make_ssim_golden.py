@@ -40,4 +40,6 @@ def main(ref):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_ssim_golden.py <path to the reference checkout>")
+    main(sys.argv[1])
