@@ -304,7 +304,12 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 3) march_forward_lists_k
 // slab, walks only the samples that lie inside that Gaussian's truncation ellipsoid
 // (a handful of the 32 on average) and keeps the four moment sums in registers -- no
 // staging in shared memory and no reduction across lanes.
-constexpr int kRun = 4;     // samples per work item of the replay
+#ifndef RGX_RUN
+#define RGX_RUN 4
+#endif
+constexpr int kRun = RGX_RUN;     // samples per work item of the replay
+
+constexpr int kBatch = 8;   // slabs of a ray whose hits are worked off together
 
 struct ReplayStage {        // per warp: one group of up to 32 hits
     float4 a[kFan];         // whitened ray point at the reference parameter, hk
@@ -312,14 +317,139 @@ struct ReplayStage {        // per warp: one group of up to 32 hits
     float4 c[kFan];         // chat_i, sigma, first and last sample (as int bits)
     int slot[kFan];
     int upto[kFan];         // inclusive prefix of the number of runs
+    int slab[kFan];         // which slab of the batch the hit belongs to
+};
+
+struct ReplayBatch {        // per warp: up to kBatch consecutive slabs of the ray
+    float beta[kBatch][kSlab];
+    float gamma[kBatch][kSlab];
+    float tbuffer[kBatch];
+    float dt[kBatch];
+    long long hits[kBatch];  // where the slab's hit list starts on the tape
+    int upto[kBatch];        // inclusive prefix of the hit counts
 };
 
 struct ReplayShared {
     int next_ray;
-    float beta[kWarps][kSlab];
-    float gamma[kWarps][kSlab];
+    ReplayBatch batch[kWarps];
     ReplayStage stage[kWarps];
 };
+
+// Second pass of the backward for the hits of a batch of slabs (see the kernel's comment).
+// SINGLE: the batch is one slab (the common case where a slab fills the lanes by itself).
+template <bool SINGLE>
+__device__ __forceinline__ void replay_batch(const MarchLaunch& L, const Ray& r, float3 dl, const ReplayBatch& bt,
+                                             ReplayStage& sp, int nslab, int lane, float tbuffer1, float dt1,
+                                             long long hits1, int nhit1) {
+    // a single slab's values come in registers (tbuffer1 ...), those of a batch from shared memory
+    const int total_hits = SINGLE ? nhit1 : bt.upto[nslab - 1];
+    for (int base = 0; base < total_hits; base += kFan) {
+        // step 1, one hit per lane: where the ray is inside the Gaussian, cut into runs of kRun samples
+        int nitem = 0;
+        const int g = base + lane;
+        if (g < total_hits) {
+            int k = 0;
+            if (!SINGLE) {
+#pragma unroll
+                for (int t = 0; t < kBatch - 1; ++t) k += (t < nslab - 1 && bt.upto[t] <= g) ? 1 : 0;
+            }
+            const int j = SINGLE ? L.tape[hits1 + g] : L.tape[bt.hits[k] + (g - (k > 0 ? bt.upto[k - 1] : 0))];
+            const float tbuffer = SINGLE ? tbuffer1 : bt.tbuffer[k], dt = SINGLE ? dt1 : bt.dt[k];
+            const float inv_dt = __fdividef(1.0f, dt);
+            const float tend = __fadd_rn(tbuffer, __fmul_rn(dt, (float)kSlab));
+            float3 Oe, de;
+            whiten_ray(r, __ldg(&L.g.g0[j]), __ldg(&L.g.g1[j]), __ldg(&L.g.g2[j]), Oe, de);
+            const float hk = __ldg(&L.g.hk[j]);
+            const float4 c = __ldg(&L.g.rgba[j]);
+            const float ci = __fdividef(fmaf(dl.x, c.x, fmaf(dl.y, c.y, __fmul_rn(dl.z, c.z))), c.w);
+            // closest approach and half width of the stretch inside the ellipsoid |Oe + t de| < 1
+            const float inv_a = __fdividef(1.0f, dot3(de, de));
+            const float tca = __fmul_rn(-dot3(Oe, de), inv_a);
+            const float3 P = make_float3(fmaf(tca, de.x, Oe.x), fmaf(tca, de.y, Oe.y), fmaf(tca, de.z, Oe.z));
+            const float hw = __fsqrt_rn(__fmul_rn(fmaxf(1.0f - dot3(P, P), 0.f), inv_a));
+            // samples (s + 1/2) dt inside it, one more on each side against rounding; the test q < 1 decides
+            const float x_lo = fmaf(__fadd_rn(__fadd_rn(tca, -hw), -tbuffer), inv_dt, -0.5f);
+            const float x_hi = fmaf(__fadd_rn(__fadd_rn(tca, hw), -tbuffer), inv_dt, -0.5f);
+            const int s_lo = (int)fminf(fmaxf(ceilf(x_lo) - 1.0f, 0.f), (float)kSlab);
+            const int s_hi = (int)fmaxf(fminf(floorf(x_hi) + 1.0f, (float)(kSlab - 1)), -1.f);
+            // moments about the closest approach clamped to the slab, so that they stay small
+            const float tcr = fminf(fmaxf(tca, tbuffer), tend);
+            sp.a[lane] = make_float4(fmaf(tcr, de.x, Oe.x), fmaf(tcr, de.y, Oe.y), fmaf(tcr, de.z, Oe.z), hk);
+            sp.b[lane] = make_float4(de.x, de.y, de.z, __fadd_rn(tbuffer, -tcr));
+            sp.c[lane] = make_float4(ci, c.w, __int_as_float(s_lo), __int_as_float(s_hi));
+            sp.slot[lane] = j;
+            if (!SINGLE) sp.slab[lane] = k;
+            nitem = s_hi >= s_lo ? (s_hi - s_lo + kRun) / kRun : 0;
+        }
+        int incl = nitem;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(kFull, incl, o);
+            if (lane >= o) incl += t;
+        }
+        const int total = __shfl_sync(kFull, incl, 31);
+        sp.upto[lane] = incl;
+        __syncwarp();
+        // step 2, one run per lane, whichever hit it belongs to: the four moment sums of the run,
+        // which share the reference point with the other runs of the hit and so simply add up
+        for (int i0 = 0; i0 < total; i0 += kFan) {
+            const int i = i0 + lane;
+            const bool active = i < total;
+            int h = 0;
+            float sb = 0.f, n0 = 0.f, n1 = 0.f, n2 = 0.f;
+            float4 A = make_float4(0.f, 0.f, 0.f, 0.f), B = A, C = A;
+            if (active) {
+#pragma unroll
+                for (int step = 16; step > 0; step >>= 1)
+                    if (sp.upto[h + step - 1] <= i) h += step;          // first hit whose runs end after i
+                A = sp.a[h]; B = sp.b[h]; C = sp.c[h];
+                const int k = SINGLE ? 0 : sp.slab[h];
+                const float dt = SINGLE ? dt1 : bt.dt[k];
+                const float* sbeta = bt.beta[k];
+                const float* sgamma = bt.gamma[k];
+                const int s_hi = __float_as_int(C.w);
+                const int nrun = (s_hi - __float_as_int(C.z) + kRun) / kRun;
+                const int s0 = __float_as_int(C.z) + kRun * (i - (sp.upto[h] - nrun));
+#pragma unroll
+                for (int q4 = 0; q4 < kRun; ++q4) {
+                    const int s = s0 + q4;
+                    if (s <= s_hi) {
+                        const float tc = __fadd_rn(__fmul_rn((float)s + 0.5f, dt), B.w);
+                        const float yx = fmaf(tc, B.x, A.x), yy = fmaf(tc, B.y, A.y), yz = fmaf(tc, B.z, A.z);
+                        const float q = fmaf(yx, yx, fmaf(yy, yy, __fmul_rn(yz, yz)));
+                        if (q < 1.0f) {
+                            const float ex = ex2_approx(__fmul_rn(-A.w, q));
+                            const float be = sbeta[s];
+                            const float ga = __fmul_rn(ex, fmaf(C.x, be, sgamma[s]));   // g * (alpha + beta*(chat_i - chat_s))
+                            const float g1 = __fmul_rn(ga, tc);
+                            sb = fmaf(ex, be, sb);
+                            n0 = __fadd_rn(n0, ga);
+                            n1 = __fadd_rn(n1, g1);
+                            n2 = fmaf(g1, tc, n2);
+                        }
+                    }
+                }
+            }
+            // runs of one hit sit in neighbouring lanes (at most 32 / kRun of them): add them up so that
+            // the Gaussian's row gets one update per hit, not one per run
+            const int seg = active ? h : -1 - lane;
+#pragma unroll
+            for (int d = 1; d < kSlab / kRun; d <<= 1) {
+                const int seg_o = __shfl_down_sync(kFull, seg, d);
+                const float o_sb = __shfl_down_sync(kFull, sb, d), o_n0 = __shfl_down_sync(kFull, n0, d),
+                            o_n1 = __shfl_down_sync(kFull, n1, d), o_n2 = __shfl_down_sync(kFull, n2, d);
+                if (lane + d < 32 && seg_o == seg) {
+                    sb = __fadd_rn(sb, o_sb); n0 = __fadd_rn(n0, o_n0); n1 = __fadd_rn(n1, o_n1); n2 = __fadd_rn(n2, o_n2);
+                }
+            }
+            const int seg_prev = __shfl_up_sync(kFull, seg, 1);
+            const bool first = lane == 0 || seg_prev != seg;
+            if (active && first && (sb != 0.f || n0 != 0.f || n1 != 0.f || n2 != 0.f))
+                emit_global(L, dl, sp.slot[h], expand_gradient(C.y, A, B, sb, n0, n1, n2));
+        }
+        __syncwarp();                      // the next group reuses the staging arrays
+    }
+}
 
 __global__ void __launch_bounds__(kThreads) march_backward_replay_kernel(const __grid_constant__ MarchLaunch L) {
     __shared__ ReplayShared sh;
@@ -328,8 +458,7 @@ __global__ void __launch_bounds__(kThreads) march_backward_replay_kernel(const _
     const int tile_x = tile % L.lists.tiles_x, tile_y = tile / L.lists.tiles_x;
     const float eps = L.m.transmittance_eps;
     const SceneBox box = *L.box;
-    float* sbeta = sh.beta[warp];
-    float* sgamma = sh.gamma[warp];
+    ReplayBatch& bt = sh.batch[warp];
     ReplayStage& sp = sh.stage[warp];
     if (tid == 0) sh.next_ray = 0;
     __syncthreads();
@@ -353,116 +482,32 @@ __global__ void __launch_bounds__(kThreads) march_backward_replay_kernel(const _
         float D = fmaf(dl.x, L.rgb_in[3 * (size_t)ray_id],
                        fmaf(dl.y, L.rgb_in[3 * (size_t)ray_id + 1], __fmul_rn(dl.z, L.rgb_in[3 * (size_t)ray_id + 2])));
         float T = 1.0f;
+        int nslab = 0, nhits = 0;
         while (off >= 0) {
+            // first pass of a slab, from the recording: transmittance and the per-sample terms
             const int4 hd = *reinterpret_cast<const int4*>(L.tape + off);
             const float tbuffer = __int_as_float(hd.x);
             const int nhit = hd.y;
             const float4 sums = reinterpret_cast<const float4*>(L.tape + off + 4)[lane];
-            const int* hits = L.tape + off + kTapeHead;
+            const long long hits_at = off + kTapeHead;
             off = ((long long)hd.w << 32) | (unsigned int)hd.z;
             // same step size as the forward: T is rebuilt from the recorded sums bit for bit
             const SlabPlan p = plan_slab(L.m, tbuffer, T, tbuffer, texit);
             const float dc = fmaf(dl.x, sums.y, fmaf(dl.y, sums.z, __fmul_rn(dl.z, sums.w)));
-            const SlabBackTerms bt = slab_back_terms(sums.x, dc, p.dt, T, D, eps, lane);
-            D = __fadd_rn(D, -bt.d_total);
-            T = slab_exit_T(bt.tr, eps);
-            __syncwarp();                          // the previous slab's readers are done
-            sbeta[lane] = bt.beta;
-            sgamma[lane] = bt.gamma;
-            __syncwarp();
-            const float inv_dt = __fdividef(1.0f, p.dt);
-            const float tend = __fadd_rn(tbuffer, p.slab);
-            for (int base = 0; base < nhit; base += kFan) {
-                // step 1, one hit per lane: where the ray is inside the Gaussian, cut into runs of kRun samples
-                int nitem = 0;
-                if (base + lane < nhit) {
-                    const int j = hits[base + lane];
-                    float3 Oe, de;
-                    whiten_ray(r, __ldg(&L.g.g0[j]), __ldg(&L.g.g1[j]), __ldg(&L.g.g2[j]), Oe, de);
-                    const float hk = __ldg(&L.g.hk[j]);
-                    const float4 c = __ldg(&L.g.rgba[j]);
-                    const float ci = __fdividef(fmaf(dl.x, c.x, fmaf(dl.y, c.y, __fmul_rn(dl.z, c.z))), c.w);
-                    // closest approach and half width of the stretch inside the ellipsoid |Oe + t de| < 1
-                    const float inv_a = __fdividef(1.0f, dot3(de, de));
-                    const float tca = __fmul_rn(-dot3(Oe, de), inv_a);
-                    const float3 P = make_float3(fmaf(tca, de.x, Oe.x), fmaf(tca, de.y, Oe.y), fmaf(tca, de.z, Oe.z));
-                    const float hw = __fsqrt_rn(__fmul_rn(fmaxf(1.0f - dot3(P, P), 0.f), inv_a));
-                    // samples (s + 1/2) dt inside it, one more on each side against rounding; the test q < 1 decides
-                    const float x_lo = fmaf(__fadd_rn(__fadd_rn(tca, -hw), -tbuffer), inv_dt, -0.5f);
-                    const float x_hi = fmaf(__fadd_rn(__fadd_rn(tca, hw), -tbuffer), inv_dt, -0.5f);
-                    const int s_lo = (int)fminf(fmaxf(ceilf(x_lo) - 1.0f, 0.f), (float)kSlab);
-                    const int s_hi = (int)fmaxf(fminf(floorf(x_hi) + 1.0f, (float)(kSlab - 1)), -1.f);
-                    // moments about the closest approach clamped to the slab, so that they stay small
-                    const float tcr = fminf(fmaxf(tca, tbuffer), tend);
-                    sp.a[lane] = make_float4(fmaf(tcr, de.x, Oe.x), fmaf(tcr, de.y, Oe.y), fmaf(tcr, de.z, Oe.z), hk);
-                    sp.b[lane] = make_float4(de.x, de.y, de.z, __fadd_rn(tbuffer, -tcr));
-                    sp.c[lane] = make_float4(ci, c.w, __int_as_float(s_lo), __int_as_float(s_hi));
-                    sp.slot[lane] = j;
-                    nitem = s_hi >= s_lo ? (s_hi - s_lo + kRun) / kRun : 0;
-                }
-                int incl = nitem;
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const int t = __shfl_up_sync(kFull, incl, o);
-                    if (lane >= o) incl += t;
-                }
-                const int total = __shfl_sync(kFull, incl, 31);
-                sp.upto[lane] = incl;
+            const SlabBackTerms terms = slab_back_terms(sums.x, dc, p.dt, T, D, eps, lane);
+            D = __fadd_rn(D, -terms.d_total);
+            T = slab_exit_T(terms.tr, eps);
+            bt.beta[nslab][lane] = terms.beta;
+            bt.gamma[nslab][lane] = terms.gamma;
+            nhits += nhit;
+            if (lane == 0) { bt.tbuffer[nslab] = tbuffer; bt.dt[nslab] = p.dt; bt.hits[nslab] = hits_at; bt.upto[nslab] = nhits; }
+            ++nslab;
+            if (nhits >= kFan || nslab == kBatch || off < 0) {       // enough hits to fill the lanes, or nothing more to wait for
                 __syncwarp();
-                // step 2, one run per lane, whichever hit it belongs to: the four moment sums of the run,
-                // which share the reference point with the other runs of the hit and so simply add up
-                for (int i0 = 0; i0 < total; i0 += kFan) {
-                    const int i = i0 + lane;
-                    const bool active = i < total;
-                    int h = 0;
-                    float sb = 0.f, n0 = 0.f, n1 = 0.f, n2 = 0.f;
-                    float4 A = make_float4(0.f, 0.f, 0.f, 0.f), B = A, C = A;
-                    if (active) {
-#pragma unroll
-                        for (int step = 16; step > 0; step >>= 1)
-                            if (sp.upto[h + step - 1] <= i) h += step;          // first hit whose runs end after i
-                        A = sp.a[h]; B = sp.b[h]; C = sp.c[h];
-                        const int s_hi = __float_as_int(C.w);
-                        const int nrun = (s_hi - __float_as_int(C.z) + kRun) / kRun;
-                        const int s0 = __float_as_int(C.z) + kRun * (i - (sp.upto[h] - nrun));
-#pragma unroll
-                        for (int k = 0; k < kRun; ++k) {
-                            const int s = s0 + k;
-                            if (s <= s_hi) {
-                                const float tc = __fadd_rn(__fmul_rn((float)s + 0.5f, p.dt), B.w);
-                                const float yx = fmaf(tc, B.x, A.x), yy = fmaf(tc, B.y, A.y), yz = fmaf(tc, B.z, A.z);
-                                const float q = fmaf(yx, yx, fmaf(yy, yy, __fmul_rn(yz, yz)));
-                                if (q < 1.0f) {
-                                    const float ex = ex2_approx(__fmul_rn(-A.w, q));
-                                    const float be = sbeta[s];
-                                    const float ga = __fmul_rn(ex, fmaf(C.x, be, sgamma[s]));   // g * (alpha + beta*(chat_i - chat_s))
-                                    const float g1 = __fmul_rn(ga, tc);
-                                    sb = fmaf(ex, be, sb);
-                                    n0 = __fadd_rn(n0, ga);
-                                    n1 = __fadd_rn(n1, g1);
-                                    n2 = fmaf(g1, tc, n2);
-                                }
-                            }
-                        }
-                    }
-                    // runs of one hit sit in neighbouring lanes (at most 32 / kRun of them): add them up so that
-                    // the Gaussian's row gets one update per hit, not one per run
-                    const int seg = active ? h : -1 - lane;
-#pragma unroll
-                    for (int d = 1; d < kSlab / kRun; d <<= 1) {
-                        const int seg_o = __shfl_down_sync(kFull, seg, d);
-                        const float o_sb = __shfl_down_sync(kFull, sb, d), o_n0 = __shfl_down_sync(kFull, n0, d),
-                                    o_n1 = __shfl_down_sync(kFull, n1, d), o_n2 = __shfl_down_sync(kFull, n2, d);
-                        if (lane + d < 32 && seg_o == seg) {
-                            sb = __fadd_rn(sb, o_sb); n0 = __fadd_rn(n0, o_n0); n1 = __fadd_rn(n1, o_n1); n2 = __fadd_rn(n2, o_n2);
-                        }
-                    }
-                    const int seg_prev = __shfl_up_sync(kFull, seg, 1);
-                    const bool first = lane == 0 || seg_prev != seg;
-                    if (active && first && (sb != 0.f || n0 != 0.f || n1 != 0.f || n2 != 0.f))
-                        emit_global(L, dl, sp.slot[h], expand_gradient(C.y, A, B, sb, n0, n1, n2));
-                }
-                __syncwarp();                      // the next group reuses the staging arrays
+                if (nslab == 1) replay_batch<true>(L, r, dl, bt, sp, 1, lane, tbuffer, p.dt, hits_at, nhit);
+                else replay_batch<false>(L, r, dl, bt, sp, nslab, lane, 0.f, 0.f, 0, 0);
+                nslab = 0;
+                nhits = 0;
             }
         }
     }
