@@ -39,13 +39,15 @@ TRANSMITTANCE_EPSILON = 0.001
 
 
 class RenderOptixSettings:
-    """Positional signature of render_optix.py:68-71.  ``transmittance_eps`` and
-    ``exact_sh_grad`` are keyword-only additions with the reference's behaviour as default."""
+    """Positional signature of render_optix.py:68-71.  ``transmittance_eps``, ``exact_sh_grad`` and ``rows`` are
+    keyword-only additions with the reference's behaviour as default.  ``rows = (first, last + 1)`` restricts
+    the render to those image rows (of the supersampled image): the other rays of the returned image are left
+    unwritten and take no part in the backward -- how a view is shared between ranks."""
 
     def __init__(self, context, update, gas, program_grps_fwd, pipeline_fwd, program_grps_bwd, pipeline_bwd, dt_step,
                  dynamic_sampling, viewpoint_cam, max_prim_slice, num_sph_gauss, iteration=0, jitter=False,
                  rnd_sample=0, supersampling=(1, 1), white_background=False, hit_prim_idx=None, *,
-                 transmittance_eps=TRANSMITTANCE_EPSILON, exact_sh_grad=False):
+                 transmittance_eps=TRANSMITTANCE_EPSILON, exact_sh_grad=False, rows=None):
         self.context = context
         self.update = update
         self.gas = gas
@@ -66,6 +68,7 @@ class RenderOptixSettings:
         self.hit_prim_idx = hit_prim_idx
         self.transmittance_eps = transmittance_eps
         self.exact_sh_grad = exact_sh_grad
+        self.rows = rows
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -293,7 +296,7 @@ class RenderOptixFunction(torch.autograd.Function):
             r.build(*tensors[:4], sigma_threshold=SIGMA_THRESHOLD,
                     morton_bits=getattr(settings, "morton_bits", 10))
         # keep what the rays met, so that the backward of this view does not have to search again
-        march = _settings_march(settings, cam, flags=_lib.FLAG_SAVE_HITS)
+        march = _settings_march(settings, cam, flags=_lib.FLAG_SAVE_HITS, rows=getattr(settings, "rows", None))
         rgb, _, _ = r.forward(*tensors, cam, march)
         ctx.settings = settings
         ctx.save_for_backward(*tensors, rgb)
@@ -307,7 +310,7 @@ class RenderOptixFunction(torch.autograd.Function):
         r = get_renderer(rgb.device)
         cam = camera_struct(settings.viewpoint_cam, settings.supersampling)
         flags = _lib.FLAG_EXACT_SH_GRAD if getattr(settings, "exact_sh_grad", False) else 0
-        march = _settings_march(settings, cam, flags=flags)
+        march = _settings_march(settings, cam, flags=flags, rows=getattr(settings, "rows", None))
         grads = [torch.empty_like(t) for t in tensors]
         r.backward(*tensors, cam, march, rgb, dl, tuple(grads))
         g_pos, g_scale, g_quat, g_dens, g_sh, g_sg, g_sharp, g_axis = grads

@@ -323,3 +323,32 @@ def test_a_failed_allocation_leaves_a_usable_context(ro):
     for a, b in zip(searched[:5], replayed[:5]):
         assert rel_max(a.cpu(), b.cpu()) < 1e-4
     del r
+
+
+def test_autograd_row_ranges_add_up_to_the_whole_view(ro):
+    """``rows`` in the settings: the two halves of a view, rendered and back-propagated one after the other
+    through the autograd entry point, give the image and the gradients of the whole view."""
+    sc = make_scene("small_dynamic_white")
+    dev = torch.device("cuda")
+    sc.to(dev)
+    cam = sc.cameras[0]
+    h, w = cam.image_height, cam.image_width
+    g = torch.Generator().manual_seed(4)
+    weight = torch.randn(h * w, 3, generator=g).to(dev)
+
+    def run(row_sets):
+        leaves = [t.clone().requires_grad_(True) for t in sc.tensors()[:5]]
+        image = torch.zeros(h * w, 3, device=dev)
+        for rows in row_sets:
+            st = settings_for(ro, sc, cam, rows=rows)
+            out = ro.RenderOptixFunction.apply(*leaves, *sc.tensors()[5:], st)
+            lo, hi = (0, h * w) if rows is None else (rows[0] * w, rows[1] * w)
+            (out[lo:hi] * weight[lo:hi]).sum().backward()
+            image[lo:hi] = out[lo:hi].detach()
+        return image, [l.grad.clone() for l in leaves]
+
+    whole_img, whole = run([None])
+    parts_img, parts = run([(0, 5), (5, h)])
+    assert torch.equal(whole_img, parts_img)
+    for a, b in zip(whole, parts):
+        assert rel_max(a.cpu(), b.cpu()) < 1e-5
