@@ -366,9 +366,10 @@ def main():
             cpu_baseline = {"value": None, "unit": "Mrays/s", "cores": os.cpu_count() or 1, "kind": "reference",
                             "sample": f"failed: {exc}"}
 
-    # hand-written kernels: 6 of the build, then per row block colours, 7 of the tile lists, forward,
-    # 2 of the backward, finalise (the library's CUB sort and scan kernels are not counted)
-    launches_per_step = 6 + 12 * len(shard_rows(args.views, args.height, 0, world))
+    # hand-written kernels: 6 of the build, then per row block colours (forward only: the replaying backward keeps
+    # them), 8 of the tile lists (directions, 2 x emit, ranges, counts, fill, scatter, blocks), forward march,
+    # 2 of the backward march, finalise (the library's CUB sort and scan kernels are not counted)
+    launches_per_step = 6 + 13 * len(shard_rows(args.views, args.height, 0, world))
     out = {
         "metric": METRIC, "value": value, "unit": "Mrays/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",

@@ -217,6 +217,11 @@ RGX_API int rgx_knn_mean_dist2(int device, const float* points, int n, float* me
  * releases the whole workspace, so that RGX_E_NOT_BUILT is returned until rgx_build is called again. */
 RGX_API int rgx_debug_fail_allocation(rgx_ctx* ctx, int nth);
 
+/* Test hook (no counterpart in the reference): recording forwards use at most `ints` 4-byte words of the
+ * recording's memory (negative: no limit), so that the rays that find no room -- which the backward then
+ * searches again instead of replaying -- can be produced at will. */
+RGX_API int rgx_debug_cap_recording(rgx_ctx* ctx, long long ints);
+
 /* Per-view tile-list construction (binning + sort), timed like the march kernels while
  * profiling is enabled: summed milliseconds and number of constructions since the last
  * read, and the number of (tile, Gaussian) pairs of the latest one. */

@@ -14,6 +14,7 @@ struct rgx_ctx {
     std::string error;
     bool alloc_failed = false;  // an allocation failed: the workspace is dropped at the next entry point
     int fail_alloc_in = -1;     // test hook: the allocation after this many more fails (rgx_debug_fail_allocation)
+    long long tape_limit = -1;  // test hook: at most this many ints of the recording are used (rgx_debug_cap_recording)
     // workspace (device), grown on demand
     int cap_n_pad = 0;          // capacity in sorted slots
     int cap_boxes = 0;
@@ -558,6 +559,7 @@ static int forward_impl(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* 
         if (ctx->tape) {
             L.tape = ctx->tape; L.tape_used = ctx->tape_used; L.tape_cap = ctx->tape_cap; L.ray_head = ctx->ray_head;
             L.tile_unrecorded = ctx->tile_unrecorded;
+            if (ctx->tape_limit >= 0 && ctx->tape_limit < L.tape_cap) L.tape_cap = ctx->tape_limit;
         }
     }
     const bool recorded = L.tape != nullptr;
@@ -672,6 +674,12 @@ int rgx_scene_box(rgx_ctx* ctx, float bb_min[3], float bb_max[3], rgx_stream str
 int rgx_debug_fail_allocation(rgx_ctx* ctx, int nth) {
     if (!ctx) return RGX_E_INVALID;
     ctx->fail_alloc_in = nth;
+    return RGX_OK;
+}
+
+int rgx_debug_cap_recording(rgx_ctx* ctx, long long ints) {
+    if (!ctx) return RGX_E_INVALID;
+    ctx->tape_limit = ints;
     return RGX_OK;
 }
 

@@ -352,3 +352,31 @@ def test_autograd_row_ranges_add_up_to_the_whole_view(ro):
     assert torch.equal(whole_img, parts_img)
     for a, b in zip(whole, parts):
         assert rel_max(a.cpu(), b.cpu()) < 1e-5
+
+
+@pytest.mark.parametrize("cap", [0, 5000, 20000, 60000])
+def test_partly_recorded_forward_mixes_replay_and_search(ro, cap):
+    """With room for only some rays on the recording, the backward replays those and searches the others
+    again, tile by tile; whatever the mix, the gradients are those of a backward that searches everything."""
+    import ctypes as C
+    sc = make_scene("config1")
+    dev = torch.device("cuda")
+    tens = [t.to(dev).contiguous() for t in sc.tensors()]
+    cam = sc.cameras[0]
+    cam.to(dev)
+    cs = ro.camera_struct(cam)
+    r = ro.Renderer(dev)
+    r.build(*tens[:4])
+    plain = ro._settings_march(settings_for(ro, sc, cam), cs)
+    save = ro._settings_march(settings_for(ro, sc, cam), cs, flags=_lib.FLAG_SAVE_HITS)
+    want, _, _ = r.forward(*tens, cs, plain)
+    dl = loss_gradient(want.cpu().double(), want.shape[0])
+    searched = backward(ro, r, sc, tens, cs, want, dl)
+    _lib.check(r._ctx, r._lib.rgx_debug_cap_recording(r._ctx, C.c_longlong(cap)))
+    rgb, _, _ = r.forward(*tens, cs, save)
+    assert torch.equal(rgb, want)                      # recording never changes the image
+    mixed = backward(ro, r, sc, tens, cs, rgb, dl)
+    for a, b in zip(searched[:5], mixed[:5]):
+        assert rel_max(a.cpu(), b.cpu()) < 1e-4
+    _lib.check(r._ctx, r._lib.rgx_debug_cap_recording(r._ctx, C.c_longlong(-1)))
+    del r
