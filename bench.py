@@ -376,7 +376,7 @@ def main():
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "gaussians": args.gaussians, "image": f"{args.width}x{args.height}",
                    "views_per_step": args.views, "sh_degree": 3, "sharding": f"rows/{world}",
-                   "l2": "inputs larger than L2 (Gaussian records 0.65 GB, gradient rows 1.5 GB, 3 GB recorded per view)"},
+                   "l2": "inputs larger than L2 (Gaussian records 0.65 GB, gradient rows 0.8 GB, 3 GB recorded per view)"},
         "views_per_s": args.views / (ms_per_step * 1e-3),
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
         "roofline": roofline, "cpu_baseline": cpu_baseline,

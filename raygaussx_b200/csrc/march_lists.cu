@@ -304,10 +304,7 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 3) march_forward_lists_k
 // slab, walks only the samples that lie inside that Gaussian's truncation ellipsoid
 // (a handful of the 32 on average) and keeps the four moment sums in registers -- no
 // staging in shared memory and no reduction across lanes.
-#ifndef RGX_RUN
-#define RGX_RUN 4
-#endif
-constexpr int kRun = RGX_RUN;     // samples per work item of the replay
+constexpr int kRun = 4;     // samples per work item of the replay (2: 12.9 ms, 4: 11.1 ms, 8: 11.1 / 7.8 ms on the two test scenes)
 
 constexpr int kBatch = 8;   // slabs of a ray whose hits are worked off together
 
