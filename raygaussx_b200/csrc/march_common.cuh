@@ -425,7 +425,7 @@ template <bool COUNT, bool BWD, class Enum>
 __device__ __forceinline__ int slab_sums(const MarchLaunch& L, const rgx_march& m, float tbuffer, float tau,
                                          int ray_id, int slab_index, float3 dl, WarpStage& ws, int lane, Tally& tl,
                                          Enum&& enumerate, float& s, float& c0, float& c1, float& c2,
-                                         bool& overflow, int* hit_list = nullptr, int hit_cap = 0) {
+                                         bool& overflow, int* const* hit_list = nullptr, int hit_cap = 0) {
     int nstage = 0, nhit = 0;
     bool ovf = false;
     s = c0 = c1 = c2 = 0.f;
@@ -442,7 +442,10 @@ __device__ __forceinline__ int slab_sums(const MarchLaunch& L, const rgx_march& 
         }
         if (take) {
             int slot = nstage + rank;
-            if (hit_list && nhit + rank < hit_cap) hit_list[nhit + rank] = j;    // remembered for the second pass
+            if (hit_list) {                      // remembered for the second pass; *hit_list may be null
+                int* list = *hit_list;
+                if (list && nhit + rank < hit_cap) list[nhit + rank] = j;
+            }
             float4 c = __ldg(&L.g.rgba[j]);
             ws.recA[slot] = make_float4(fmaf(tbuffer, t.de.x, t.Oe.x), fmaf(tbuffer, t.de.y, t.Oe.y),
                                         fmaf(tbuffer, t.de.z, t.Oe.z), __ldg(&L.g.hk[j]));

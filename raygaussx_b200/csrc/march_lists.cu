@@ -43,6 +43,17 @@ struct ListShared {
     WarpStage ws[kWarps];
 };
 
+// Where a warp stands on the tape.  Kept in shared memory, not in registers: it is touched once per slab,
+// the registers it would take are wanted all the time by the search and the evaluation.
+struct TapeState {
+    long long off;      // next free int of the warp's current block
+    long long head;     // first chunk of the current ray (-1: none yet)
+    long long prev;     // latest chunk of the current ray
+    int* hits;          // where the current slab's hits go (null: the slab is not recorded)
+    int left;           // ints left in the block
+    int ok;             // 0: the current ray cannot be recorded (no room)
+};
+
 struct TileView {      // one tile's list
     const int* id;
     const float2* range;
@@ -183,6 +194,7 @@ __device__ __forceinline__ bool ray_pixel(const MarchLaunch& L, int tile_x, int 
 template <bool COUNT, bool SAVE>
 __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 3) march_forward_lists_kernel(const __grid_constant__ MarchLaunch L) {
     __shared__ ListShared sh;
+    __shared__ TapeState tape_state[SAVE ? kWarps : 1];
     constexpr bool save = SAVE;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     WarpStage& ws = sh.ws[warp];
@@ -196,10 +208,10 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 3) march_forward_lists_k
     Tally tl;
 #pragma unroll
     for (int i = 0; i < C_NUM; ++i) tl.v[i] = 0;
+    TapeState& tq = tape_state[SAVE ? warp : 0];
     if (tid == 0) sh.next_ray = 0;
+    if (save && lane == 0) { tq.off = 0; tq.left = 0; tq.hits = nullptr; }
     __syncthreads();
-    long long blk_off = 0;      // the warp's current block of the tape and what is left of it
-    int blk_left = 0;
 
     while (true) {
         int ray = 0;
@@ -215,8 +227,10 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 3) march_forward_lists_k
         clip_scene(box, r, tenter, texit);
         RayColor st = {1.0f, 0.f, 0.f, 0.f, 0.f};
         int cursor = 0;
-        long long tape_head = -1, tape_prev = -1;    // first and latest chunk of this ray on the tape
-        bool tape_ok = true;
+        if (save) {
+            if (lane == 0) { tq.head = -1; tq.prev = -1; tq.ok = 1; }
+            __syncwarp();
+        }
         if (COUNT) tl.v[C_RAYS] += 1;
         // cycle counters of the counting variant: whole ray, closest-hit queries, slab queries (the
         // evaluation of the staged hits is timed inside slab_sums), compositing
@@ -237,35 +251,42 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 3) march_forward_lists_k
                 bool overflow;
                 // room on the tape for the largest chunk this slab can make; the hits are written there as they
                 // are met and the unused rest is handed back
-                int* chunk = nullptr;
-                if (save && tape_ok) {
-                    const int worst = (kTapeHead + L.m.max_prim_slice + 3) & ~3;
-                    if (worst > blk_left && worst <= kTapeBlock) {
-                        unsigned long long o = 0;
-                        if (lane == 0) o = atomicAdd(L.tape_used, (unsigned long long)kTapeBlock);
-                        o = __shfl_sync(kFull, o, 0);
-                        if ((long long)(o + kTapeBlock) <= L.tape_cap) { blk_off = (long long)o; blk_left = kTapeBlock; }
+                if (save) {
+                    if (lane == 0) {
+                        tq.hits = nullptr;
+                        if (tq.ok) {
+                            const int worst = (kTapeHead + L.m.max_prim_slice + 3) & ~3;
+                            if (worst > tq.left && worst <= kTapeBlock) {
+                                const unsigned long long o = atomicAdd(L.tape_used, (unsigned long long)kTapeBlock);
+                                if ((long long)(o + kTapeBlock) <= L.tape_cap) { tq.off = (long long)o; tq.left = kTapeBlock; }
+                            }
+                            if (worst <= tq.left) tq.hits = L.tape + tq.off + kTapeHead;
+                            else tq.ok = 0;                // no room: the backward will search this ray
+                        }
                     }
-                    if (worst <= blk_left) chunk = L.tape + blk_off;
-                    else tape_ok = false;                  // no room: the backward will search this ray
+                    __syncwarp();
                 }
                 const long long c_q = COUNT ? clock64() : 0;
                 int nhit = slab_sums<COUNT, false>(L, L.m, tbuffer, tau, ray_id, slab_index, make_float3(0.f, 0.f, 0.f),
                                                    ws, lane, tl, [&](auto&& leaf) {
                     search_tile<COUNT>(L, r, p.tmin, p.tmax, tv, cursor, pend, lane, tl, leaf);
-                }, s, cr, cg, cb, overflow, chunk ? chunk + kTapeHead : nullptr, chunk ? L.m.max_prim_slice : 0);
+                }, s, cr, cg, cb, overflow, save ? &tq.hits : nullptr, L.m.max_prim_slice);
                 if (COUNT) { tl.v[C_HITS] += nhit; tl.v[C_OVF] += overflow ? 1 : 0; tl.v[C_CYC_SEARCH] += clock64() - c_q; }
-                if (chunk && nhit > 0) {
-                    const int need = (kTapeHead + nhit + 3) & ~3;
-                    if (lane == 0) {
-                        *reinterpret_cast<int4*>(chunk) = make_int4(__float_as_int(tbuffer), nhit, -1, -1);
-                        if (tape_prev >= 0)
-                            *reinterpret_cast<int2*>(L.tape + tape_prev + 2) = make_int2((int)(blk_off & 0xffffffffll), (int)(blk_off >> 32));
-                    }
+                if (save && nhit > 0 && tq.hits) {
+                    int* chunk = tq.hits - kTapeHead;
                     reinterpret_cast<float4*>(chunk + 4)[lane] = make_float4(s, cr, cg, cb);
-                    if (tape_head < 0) tape_head = blk_off;
-                    tape_prev = blk_off;
-                    blk_off += need; blk_left -= need;
+                    __syncwarp();
+                    if (lane == 0) {
+                        const int need = (kTapeHead + nhit + 3) & ~3;
+                        *reinterpret_cast<int4*>(chunk) = make_int4(__float_as_int(tbuffer), nhit, -1, -1);
+                        if (tq.prev >= 0)
+                            *reinterpret_cast<int2*>(L.tape + tq.prev + 2) = make_int2((int)(tq.off & 0xffffffffll), (int)(tq.off >> 32));
+                        if (tq.head < 0) tq.head = tq.off;
+                        tq.prev = tq.off;
+                        tq.off += need;
+                        tq.left -= need;
+                    }
+                    __syncwarp();
                 }
                 if (nhit == 0) {                                                  // :297-319
                     tbuffer = __fadd_rn(tbuffer, p.slab);
@@ -286,8 +307,8 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 3) march_forward_lists_k
         if (lane == 0) {                                                           // :326-339
             write_ray(L, ray_id, st, bg);
             if (save) {
-                L.ray_head[ray_id] = tape_ok ? tape_head : -2;
-                if (!tape_ok) L.tile_unrecorded[tile] = 1;
+                L.ray_head[ray_id] = tq.ok ? tq.head : -2;
+                if (!tq.ok) L.tile_unrecorded[tile] = 1;
             }
         }
         if (COUNT) tl.v[C_CYC_TOTAL] += clock64() - c_ray;
@@ -565,7 +586,7 @@ __global__ void __launch_bounds__(kThreads) march_backward_lists_kernel(const __
             bool overflow;
             int* hits = hit_lists[warp];
             int nhit = slab_sums<false, true>(L, L.m, tbuffer, tau, ray_id, slab_index, dl, ws, lane, tl, enumerate, s, dc,
-                                              u0, u1, overflow, hits, kHitList);
+                                              u0, u1, overflow, &hits, kHitList);
             if (nhit == 0) {
                 tbuffer = __fadd_rn(tbuffer, p.slab);
                 float nxt = closest_in_tile<false>(L, r, tbuffer, texit, tv, cursor, pend, lane, tl);
