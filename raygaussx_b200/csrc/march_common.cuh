@@ -525,6 +525,27 @@ __device__ __forceinline__ void composite_forward(const SlabPlan& p, float tbuff
     st.T = slab_exit_T(tr, eps);
 }
 
+// The same with the ray's colour and depth kept in shared memory (x, y, z = colour, w = depth; lane 0 owns
+// them): they are touched once per slab, and the registers are wanted elsewhere all the time.
+__device__ __forceinline__ void composite_forward_shared(const SlabPlan& p, float tbuffer, float tau, float eps, int lane,
+                                                         float s, float cr, float cg, float cb, bool want_depth,
+                                                         float& T, float4* acc) {
+    SlabTrans tr = slab_transmittance(s, p.dt, T, eps, lane);
+    float one_m_w = 1.0f - tr.w;
+    float f = tr.live ? __fmul_rn(tr.Ts, __fmul_rn(p.dt, __fdividef(one_m_w, fmaxf(tr.x, 1e-6f)))) : 0.f;
+    const float sr = warp_sum(__fmul_rn(f, cr)), sg = warp_sum(__fmul_rn(f, cg)), sb = warp_sum(__fmul_rn(f, cb));
+    float sd = 0.f;
+    if (want_depth) {
+        float ts = __fadd_rn(tbuffer, tau);
+        sd = warp_sum(tr.live ? __fmul_rn(__fmul_rn(tr.Ts, one_m_w), ts) : 0.f);
+    }
+    if (lane == 0) {
+        float4 a = *acc;
+        *acc = make_float4(__fadd_rn(a.x, sr), __fadd_rn(a.y, sg), __fadd_rn(a.z, sb), __fadd_rn(a.w, sd));
+    }
+    T = slab_exit_T(tr, eps);
+}
+
 // 8-bit colour of the reference's viewer (cuda_gui/helpers.h:45-58): clamp to [0,1], times 256,
 // truncate, at most 255; no gamma.
 __device__ __forceinline__ unsigned char quantize8(float x) {

@@ -38,6 +38,7 @@ constexpr int kTapeBlock = 4096;   // ints a warp reserves at a time; slabs are 
 
 struct ListShared {
     int next_ray;
+    float4 color[kWarps];      // forward: the ray's colour and depth so far (lane 0 of the warp owns it)
     int pend[kWarps][2 * kFan];
     int prim_of[kWarps][kFan];
     WarpStage ws[kWarps];
@@ -225,7 +226,8 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 3) march_forward_lists_k
         make_ray(L.cam, px, py, r);
         float tenter, texit;
         clip_scene(box, r, tenter, texit);
-        RayColor st = {1.0f, 0.f, 0.f, 0.f, 0.f};
+        float T = 1.0f;
+        if (lane == 0) sh.color[warp] = make_float4(0.f, 0.f, 0.f, 0.f);
         int cursor = 0;
         if (save) {
             if (lane == 0) { tq.head = -1; tq.prev = -1; tq.ok = 1; }
@@ -241,8 +243,8 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 3) march_forward_lists_k
             tenter = first;
             float tbuffer = tenter;
             int slab_index = 0;
-            while (tbuffer < texit && st.T > eps && slab_index < kMaxSlabs) {     // :266
-                SlabPlan p = plan_slab(L.m, tbuffer, st.T, tenter, texit);
+            while (tbuffer < texit && T > eps && slab_index < kMaxSlabs) {        // :266
+                SlabPlan p = plan_slab(L.m, tbuffer, T, tenter, texit);
                 if (COUNT) tl.v[C_SLABS] += 1;
                 ++slab_index;
                 if (!p.traced) { tbuffer = __fadd_rn(tbuffer, p.slab); continue; }
@@ -299,12 +301,14 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 3) march_forward_lists_k
                 }
                 if (COUNT) tl.v[C_SLABS_HIT] += 1;
                 const long long c_c = COUNT ? clock64() : 0;
-                composite_forward(p, tbuffer, tau, eps, lane, s, cr, cg, cb, L.depth != nullptr, st);
+                composite_forward_shared(p, tbuffer, tau, eps, lane, s, cr, cg, cb, L.depth != nullptr, T, &sh.color[warp]);
                 if (COUNT) tl.v[C_CYC_COMP] += clock64() - c_c;
                 tbuffer = __fadd_rn(tbuffer, p.slab);                             // :324
             }
         }
         if (lane == 0) {                                                           // :326-339
+            const float4 acc = sh.color[warp];
+            const RayColor st = {T, acc.x, acc.y, acc.z, acc.w};
             write_ray(L, ray_id, st, bg);
             if (save) {
                 L.ray_head[ray_id] = tq.ok ? tq.head : -2;
