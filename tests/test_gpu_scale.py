@@ -119,3 +119,38 @@ def test_tile_lists_find_every_hit_with_the_camera_inside_the_scene(cam_index):
     torch.cuda.synchronize()
     for x, y in zip(replayed[:5], searched[:5]):
         assert ((x - y).abs().max() / y.abs().max().clamp_min(1e-30)).item() < 2e-3
+
+
+@pytest.mark.parametrize("cam_index", [0, 1])
+def test_tile_lists_hold_every_hit_of_needle_like_gaussians(cam_index):
+    """The stress recipe at reduced size: anisotropy up to 100:1 at random orientations, dense clusters, early
+    termination at 1e-4.  Needles project to thin diagonal footprints, the hardest case for the tile
+    rectangles and the per-(tile, Gaussian) ranges; the hit sets must still equal the per-ray search's."""
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device: there is no CPU path")
+    from raygaussx_b200 import render_optix as ro
+    dev = torch.device("cuda")
+    sc = scenes.stress_scene(n_uniform=60_000, n_cluster=10_000, n_cameras=2, width=320, height=180)
+    tens = [t.to(dev).contiguous() for t in sc.tensors()]
+    cam = sc.cameras[cam_index]
+    cam.to(dev)
+    cs = ro.camera_struct(cam)
+    r = ro.get_renderer()
+    r.build(*tens[:4])
+    got = {}
+    for label, flags in (("lists", 0), ("per_ray", _lib.FLAG_PER_RAY_SEARCH)):
+        r.reset_counters()
+        rgb, alpha, depth = r.forward(*tens, cs, march(ro, sc, cs, flags=flags | _lib.FLAG_COUNT_WORK), want_alpha=True,
+                                      want_depth=True)
+        got[label] = (rgb.clone(), alpha.clone(), depth.clone(), r.read_counters())
+    a, b = got["lists"][3], got["per_ray"][3]
+    assert a["hits_hash"] == b["hits_hash"]
+    for k in ("rays", "slabs", "slabs_hit", "closest_queries", "hits", "overflow_slabs"):
+        assert a[k] == b[k], k
+    assert a["hits"] > 10 * a["rays"]
+    for x, y in zip(got["lists"][:3], got["per_ray"][:3]):
+        assert (x - y).abs().max().item() < 2e-5
+    # the viewer's frame of the same view: bytes of the float image
+    frame, _ = r.forward_frame(*tens, cs, march(ro, sc, cs))
+    want = (got["lists"][0].clamp(0, 1) * 256).to(torch.int32).clamp(max=255).reshape(cs.height, cs.width, 3)
+    assert (frame[..., :3].to(torch.int32) - want).abs().max().item() <= 1      # one step where the two images round apart
