@@ -523,10 +523,10 @@ static int forward_impl(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* 
         const long long rays = (long long)cam->width * cam->height;
         const long long rows_rays = (long long)cam->width * (march->row_end - march->row_begin);
         if (!ctx->tape_used) {
-            if ((e = regrow(ctx, ctx->tape_used, 1)) != cudaSuccess) return cuda_fail(ctx, e, "tape");
-            if ((e = cudaMallocHost((void**)&ctx->tape_used_host, sizeof(unsigned long long))) != cudaSuccess)
+            if ((e = regrow(ctx, ctx->tape_used, 4)) != cudaSuccess) return cuda_fail(ctx, e, "tape");
+            if ((e = cudaMallocHost((void**)&ctx->tape_used_host, 4 * sizeof(unsigned long long))) != cudaSuccess)
                 return cuda_fail(ctx, e, "tape");
-            *ctx->tape_used_host = 0;
+            for (int i = 0; i < 4; ++i) ctx->tape_used_host[i] = 0;
         }
         if (rays > ctx->ray_head_cap) {
             if ((e = regrow(ctx, ctx->ray_head, (size_t)rays)) != cudaSuccess) return cuda_fail(ctx, e, "tape");
@@ -555,7 +555,7 @@ static int forward_impl(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* 
                 ctx->tape_cap = want;
             }
         }
-        if ((e = cudaMemsetAsync(ctx->tape_used, 0, sizeof(unsigned long long), s)) != cudaSuccess ||
+        if ((e = cudaMemsetAsync(ctx->tape_used, 0, 4 * sizeof(unsigned long long), s)) != cudaSuccess ||
             (e = cudaMemsetAsync(ctx->tile_unrecorded, 0, sizeof(int) * (size_t)(L.lists.tiles_x * L.lists.tiles_y), s)) != cudaSuccess)
             return cuda_fail(ctx, e, "tape");
         if (ctx->tape) {
@@ -571,7 +571,7 @@ static int forward_impl(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* 
     }
     if (e != cudaSuccess) return cuda_fail(ctx, e, "forward march");
     if (recorded) {
-        cudaMemcpyAsync(ctx->tape_used_host, ctx->tape_used, sizeof(unsigned long long), cudaMemcpyDeviceToHost, s);
+        cudaMemcpyAsync(ctx->tape_used_host, ctx->tape_used, 4 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, s);
         ctx->tape_valid = true;
         ctx->tape_rgba_serial = ctx->rgba_serial;
         ctx->tape_build_id = ctx->build_id;
@@ -625,6 +625,10 @@ int rgx_backward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, co
         std::memcmp(&ctx->tape_cam, cam, sizeof(rgx_camera)) == 0) {
         L.tape = ctx->tape; L.tape_used = ctx->tape_used; L.tape_cap = ctx->tape_cap; L.ray_head = ctx->ray_head;
         L.tile_unrecorded = ctx->tile_unrecorded;
+        // Slabs with few hits are worked off several at a time.  The statistics are those of the latest recording
+        // whose read-back has arrived (this view's, or an earlier one's: a hint, either kernel gives the same result).
+        const unsigned long long slabs = ctx->tape_used_host[1], nhits = ctx->tape_used_host[2];
+        L.replay_batched = slabs == 0 || nhits < 24ull * slabs;
     }
     L.rgb_in = rgb; L.dl_drgb = dL_drgb; L.grad_rows = ctx->grad_rows; L.grad_copies = ctx->grad_copies;
     {

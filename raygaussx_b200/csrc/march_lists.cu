@@ -53,6 +53,7 @@ struct TapeState {
     int* hits;          // where the current slab's hits go (null: the slab is not recorded)
     int left;           // ints left in the block
     int ok;             // 0: the current ray cannot be recorded (no room)
+    unsigned int slabs, nhits;   // recorded by this warp so far (for the backward's choice of kernel)
 };
 
 struct TileView {      // one tile's list
@@ -211,7 +212,7 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 3) march_forward_lists_k
     for (int i = 0; i < C_NUM; ++i) tl.v[i] = 0;
     TapeState& tq = tape_state[SAVE ? warp : 0];
     if (tid == 0) sh.next_ray = 0;
-    if (save && lane == 0) { tq.off = 0; tq.left = 0; tq.hits = nullptr; }
+    if (save && lane == 0) { tq.off = 0; tq.left = 0; tq.hits = nullptr; tq.slabs = 0u; tq.nhits = 0u; }
     __syncthreads();
 
     while (true) {
@@ -287,6 +288,8 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 3) march_forward_lists_k
                         tq.prev = tq.off;
                         tq.off += need;
                         tq.left -= need;
+                        tq.slabs += 1u;
+                        tq.nhits += (unsigned int)nhit;
                     }
                     __syncwarp();
                 }
@@ -318,6 +321,10 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 3) march_forward_lists_k
         if (COUNT) tl.v[C_CYC_TOTAL] += clock64() - c_ray;
     }
     if (COUNT) flush_tally(L, tl, lane);
+    if (save && lane == 0 && tq.slabs) {
+        atomicAdd(L.tape_used + 1, (unsigned long long)tq.slabs);
+        atomicAdd(L.tape_used + 2, (unsigned long long)tq.nhits);
+    }
 }
 
 // ---------------------------------------------------------------- backward, by replaying the forward's recording
@@ -342,25 +349,27 @@ struct ReplayStage {        // per warp: one group of up to 32 hits
     int slab[kFan];         // which slab of the batch the hit belongs to
 };
 
-struct ReplayBatch {        // per warp: up to kBatch consecutive slabs of the ray
-    float beta[kBatch][kSlab];
-    float gamma[kBatch][kSlab];
-    float tbuffer[kBatch];
-    float dt[kBatch];
-    long long hits[kBatch];  // where the slab's hit list starts on the tape
-    int upto[kBatch];        // inclusive prefix of the hit counts
+template <int NB>
+struct ReplayBatchT {       // per warp: up to NB consecutive slabs of the ray
+    float beta[NB][kSlab];
+    float gamma[NB][kSlab];
+    float tbuffer[NB];
+    float dt[NB];
+    long long hits[NB];      // where the slab's hit list starts on the tape
+    int upto[NB];            // inclusive prefix of the hit counts
 };
 
+template <int NB>
 struct ReplayShared {
     int next_ray;
-    ReplayBatch batch[kWarps];
+    ReplayBatchT<NB> batch[kWarps];
     ReplayStage stage[kWarps];
 };
 
 // Second pass of the backward for the hits of a batch of slabs (see the kernel's comment).
 // SINGLE: the batch is one slab (the common case where a slab fills the lanes by itself).
-template <bool SINGLE>
-__device__ __forceinline__ void replay_batch(const MarchLaunch& L, const Ray& r, float3 dl, const ReplayBatch& bt,
+template <bool SINGLE, int NB>
+__device__ __forceinline__ void replay_batch(const MarchLaunch& L, const Ray& r, float3 dl, const ReplayBatchT<NB>& bt,
                                              ReplayStage& sp, int nslab, int lane, float tbuffer1, float dt1,
                                              long long hits1, int nhit1) {
     // a single slab's values come in registers (tbuffer1 ...), those of a batch from shared memory
@@ -373,7 +382,7 @@ __device__ __forceinline__ void replay_batch(const MarchLaunch& L, const Ray& r,
             int k = 0;
             if (!SINGLE) {
 #pragma unroll
-                for (int t = 0; t < kBatch - 1; ++t) k += (t < nslab - 1 && bt.upto[t] <= g) ? 1 : 0;
+                for (int t = 0; t < NB - 1; ++t) k += (t < nslab - 1 && bt.upto[t] <= g) ? 1 : 0;
             }
             const int j = SINGLE ? L.tape[hits1 + g] : L.tape[bt.hits[k] + (g - (k > 0 ? bt.upto[k - 1] : 0))];
             const float tbuffer = SINGLE ? tbuffer1 : bt.tbuffer[k], dt = SINGLE ? dt1 : bt.dt[k];
@@ -473,14 +482,16 @@ __device__ __forceinline__ void replay_batch(const MarchLaunch& L, const Ray& r,
     }
 }
 
+// NB: slabs batched.  1 where slabs fill the lanes by themselves (fewer registers, one more CTA per SM).
+template <int NB>
 __global__ void __launch_bounds__(kThreads) march_backward_replay_kernel(const __grid_constant__ MarchLaunch L) {
-    __shared__ ReplayShared sh;
+    __shared__ ReplayShared<NB> sh;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tile = L.lists.tile_order ? __ldg(&L.lists.tile_order[blockIdx.x]) : blockIdx.x;
     const int tile_x = tile % L.lists.tiles_x, tile_y = tile / L.lists.tiles_x;
     const float eps = L.m.transmittance_eps;
     const SceneBox box = *L.box;
-    ReplayBatch& bt = sh.batch[warp];
+    ReplayBatchT<NB>& bt = sh.batch[warp];
     ReplayStage& sp = sh.stage[warp];
     if (tid == 0) sh.next_ray = 0;
     __syncthreads();
@@ -524,9 +535,9 @@ __global__ void __launch_bounds__(kThreads) march_backward_replay_kernel(const _
             nhits += nhit;
             if (lane == 0) { bt.tbuffer[nslab] = tbuffer; bt.dt[nslab] = p.dt; bt.hits[nslab] = hits_at; bt.upto[nslab] = nhits; }
             ++nslab;
-            if (nhits >= kFan || nslab == kBatch || off < 0) {       // enough hits to fill the lanes, or nothing more to wait for
+            if (NB == 1 || nhits >= kFan || nslab == NB || off < 0) {   // enough hits to fill the lanes, or nothing more to wait for
                 __syncwarp();
-                if (nslab == 1) replay_batch<true>(L, r, dl, bt, sp, 1, lane, tbuffer, p.dt, hits_at, nhit);
+                if (NB == 1 || nslab == 1) replay_batch<true>(L, r, dl, bt, sp, 1, lane, tbuffer, p.dt, hits_at, nhit);
                 else replay_batch<false>(L, r, dl, bt, sp, nslab, lane, 0.f, 0.f, 0, 0);
                 nslab = 0;
                 nhits = 0;
@@ -647,7 +658,10 @@ cudaError_t launch_march_backward(const MarchLaunch& m, cudaStream_t s) {
     if (!use_lists(m)) return launch_march_backward_per_ray(m, s);
     const int grid = m.lists.tiles_x * m.lists.tiles_y;
     if (grid <= 0) return cudaSuccess;
-    if (m.tape) march_backward_replay_kernel<<<grid, kThreads, 0, s>>>(m);          // recorded rays
+    if (m.tape) {                                                                  // recorded rays
+        if (m.replay_batched) march_backward_replay_kernel<kBatch><<<grid, kThreads, 0, s>>>(m);
+        else march_backward_replay_kernel<1><<<grid, kThreads, 0, s>>>(m);
+    }
     march_backward_lists_kernel<<<grid, kThreads, 0, s>>>(m);                      // the others (a quick no-op per recorded ray)
     return cudaGetLastError();
 }

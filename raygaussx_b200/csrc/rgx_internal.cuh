@@ -109,7 +109,8 @@ struct MarchLaunch {
     // [tbuffer bits, hit count, next chunk offset lo, hi, sorted slots...]; ray_head[ray] = first chunk,
     // -1 = no slab with hits, -2 = not recorded (the backward searches again).
     int* tape;
-    unsigned long long* tape_used;
+    unsigned long long* tape_used;   // [3]: ints reserved, slabs recorded, hits recorded
+    int replay_batched;              // backward: work several slabs of a ray off together (few hits per slab)
     long long tape_cap;
     long long* ray_head;
     int* tile_unrecorded;   // per tile (of the lists): set by the forward when a ray of the tile got ray_head = -2
