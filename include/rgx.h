@@ -222,6 +222,17 @@ RGX_API int rgx_debug_fail_allocation(rgx_ctx* ctx, int nth);
  * searches again instead of replaying -- can be produced at will. */
 RGX_API int rgx_debug_cap_recording(rgx_ctx* ctx, long long ints);
 
+/* Two-depth lists (no counterpart in the reference).  A forward that is not followed by a backward (no
+ * RGX_FLAG_SAVE_HITS, no counting) and whose view has at least `min_pairs_per_ray` (tile, Gaussian) pairs per
+ * ray -- a dense scene whose rays end long before they have seen most of them -- sorts and marches only the pairs
+ * that begin nearest to the eye first, about `budget_per_ray` per ray, and sorts the rest only for the tiles in
+ * which some ray got further; the image is bit for bit that of the one-depth march.  Defaults 48 and 16;
+ * min_pairs_per_ray < 0 switches the path off, 0 forces it; budget_per_ray = 0 keeps the current value.
+ * rgx_read_two_depth returns and clears (pairs emitted, pairs sorted for the first depth, rays that went further,
+ * pairs sorted for the second depth) of the latest such forward, zeros if there was none. */
+RGX_API int rgx_debug_two_depth(rgx_ctx* ctx, int min_pairs_per_ray, int budget_per_ray);
+RGX_API int rgx_read_two_depth(rgx_ctx* ctx, long long out[4]);
+
 /* Per-view tile-list construction (binning + sort), timed like the march kernels while
  * profiling is enabled: summed milliseconds and number of constructions since the last
  * read, and the number of (tile, Gaussian) pairs of the latest one. */

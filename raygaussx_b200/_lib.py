@@ -68,6 +68,8 @@ SYMBOLS = {
     "rgx_scene_box": (C.c_int, [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float), C.c_void_p]),
     "rgx_debug_fail_allocation": (C.c_int, [C.c_void_p, C.c_int]),
     "rgx_debug_cap_recording": (C.c_int, [C.c_void_p, C.c_longlong]),
+    "rgx_debug_two_depth": (C.c_int, [C.c_void_p, C.c_int, C.c_int]),
+    "rgx_read_two_depth": (C.c_int, [C.c_void_p, C.POINTER(C.c_longlong)]),
     "rgx_knn_mean_dist2": (C.c_int, [C.c_int, _fp, C.c_int, _fp, C.c_void_p]),
     "rgx_reset_counters": (C.c_int, [C.c_void_p, C.c_void_p]),
     "rgx_read_counters": (C.c_int, [C.c_void_p, C.POINTER(Counters), C.c_void_p]),

@@ -56,6 +56,14 @@ struct rgx_ctx {
     int big_cap = 0, sm_count = 0;
     unsigned long long* bin_total_dev = nullptr;
     unsigned long long* bin_total_host = nullptr;      // pinned
+    // two-depth lists of forward-only views (binning.cu, march_lists.cu HZ variant)
+    uint64_t* sel_keys = nullptr; uint32_t* sel_vals = nullptr; size_t sel_cap = 0;
+    unsigned int* hz_hist = nullptr; unsigned int* hz_hist_host = nullptr;       // 2048 buckets; host copy pinned
+    int *tile_more = nullptr, *tile_resume = nullptr; int hz_tiles_cap = 0;
+    float4* hz_state = nullptr; long long hz_state_cap = 0;
+    unsigned long long* hz_scalars = nullptr; unsigned long long* hz_scalars_host = nullptr;   // [0] selected pairs, [1] stopped rays (low 32 bits)
+    int hz_min_pairs_per_ray = 48, hz_budget_per_ray = 16;                        // when to use them, how deep the first phase goes
+    long long hz_last[4] = {0, 0, 0, 0};                                          // pairs emitted, sorted in phase 1, rays stopped, sorted in phase 2
     // what the current lists were made for
     int last_pairs = 0;
     float binning_ms = 0.f; int binning_runs = 0;
@@ -136,7 +144,9 @@ void release_workspace(rgx_ctx* ctx) {
                      (void**)&ctx->bin_cub, (void**)&ctx->bin_total_dev, (void**)&ctx->tape, (void**)&ctx->tape_used,
                      (void**)&ctx->ray_head, (void**)&ctx->tile_dir, (void**)&ctx->tile_iota,
                      (void**)&ctx->tile_cnt_sorted, (void**)&ctx->tile_order, (void**)&ctx->big_slot,
-                     (void**)&ctx->big_rect, (void**)&ctx->tile_unrecorded};
+                     (void**)&ctx->big_rect, (void**)&ctx->tile_unrecorded, (void**)&ctx->sel_keys, (void**)&ctx->sel_vals,
+                     (void**)&ctx->hz_hist, (void**)&ctx->tile_more, (void**)&ctx->tile_resume, (void**)&ctx->hz_state,
+                     (void**)&ctx->hz_scalars};
     for (void** p : ptrs) {
         if (*p) cudaFree(*p);
         *p = nullptr;
@@ -150,6 +160,7 @@ void release_workspace(rgx_ctx* ctx) {
     ctx->big_cap = 0;
     ctx->tape_cap = 0;
     ctx->ray_head_cap = 0;
+    ctx->sel_cap = 0; ctx->hz_tiles_cap = 0; ctx->hz_state_cap = 0;
     ctx->built = false;
     ctx->lists_valid = false;
     ctx->tape_valid = false;
@@ -314,6 +325,8 @@ void rgx_destroy(rgx_ctx* ctx) {
     release_workspace(ctx);
     if (ctx->bin_total_host) cudaFreeHost(ctx->bin_total_host);
     if (ctx->tape_used_host) cudaFreeHost(ctx->tape_used_host);
+    if (ctx->hz_hist_host) cudaFreeHost(ctx->hz_hist_host);
+    if (ctx->hz_scalars_host) cudaFreeHost(ctx->hz_scalars_host);
     for (auto* v : {&ctx->timed, &ctx->spare})
         for (auto& t : *v) { cudaEventDestroy(t.a); cudaEventDestroy(t.b); }
     delete ctx;
@@ -385,20 +398,23 @@ static bool camera_dual(const rgx_camera& c, float dual[3][3]) {
     return true;
 }
 
-// Makes ctx->lists valid for this camera and row range (no-op if they already are).
-static int ensure_lists(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, cudaStream_t s) {
-    if (ctx->lists_valid && ctx->lists_build_id == ctx->build_id && ctx->lists_row_begin == m->row_begin &&
-        ctx->lists_row_end == m->row_end && std::memcmp(&ctx->lists_cam, cam, sizeof(rgx_camera)) == 0)
-        return RGX_OK;
-    ctx->lists_valid = false;
-    if (m->row_end <= m->row_begin || ctx->n == 0) return RGX_OK;   // nothing to march
+static bool lists_cached(const rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m) {
+    return ctx->lists_valid && ctx->lists_build_id == ctx->build_id && ctx->lists_row_begin == m->row_begin &&
+           ctx->lists_row_end == m->row_end && std::memcmp(&ctx->lists_cam, cam, sizeof(rgx_camera)) == 0;
+}
+
+#define RGB_(p, cnt) if ((e = regrow(ctx, ctx->p, (cnt))) != cudaSuccess) return cuda_fail(ctx, e, "tile-list workspace " #p)
+
+// All (tile, Gaussian) pairs of the view, unsorted, in ctx->bin_keys_in / bin_vals_in; fills `b` for the calls
+// that follow.  Includes the view's one host round trip (the number of pairs).
+static int emit_pairs(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, cudaStream_t s, BinLaunch& b, int& total,
+                      int& ntiles) {
     cudaError_t e = cudaSuccess;
     const int tiles_x = (cam->width + kBinTile - 1) / kBinTile;
     if (tiles_x > 65535) return fail(ctx, RGX_E_TOO_LARGE, "image wider than 65535 tiles");
     const int ty_first = m->row_begin / kBinTile, ty_last = (m->row_end - 1) / kBinTile;
     const int tiles_y = ty_last - ty_first + 1;
-    const int ntiles = tiles_x * tiles_y;
-#define RGB_(p, cnt) if ((e = regrow(ctx, ctx->p, (cnt))) != cudaSuccess) return cuda_fail(ctx, e, "tile-list workspace " #p)
+    ntiles = tiles_x * tiles_y;
     if (!ctx->bin_total_dev) {
         RGB_(bin_total_dev, 4);
         if ((e = cudaMallocHost((void**)&ctx->bin_total_host, 4 * sizeof(unsigned long long))) != cudaSuccess)
@@ -428,7 +444,7 @@ static int ensure_lists(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m,
     // first view of a context: room for eight tiles per Gaussian; a view that needs more runs the emission twice
     if (ctx->bin_pair_cap == 0 && (e = grow_pairs((size_t)ctx->n_pad * 8)) != cudaSuccess)
         return cuda_fail(ctx, e, "tile-list workspace pairs");
-    BinLaunch b{};
+    b = BinLaunch{};
     b.n = ctx->n; b.n_pad = ctx->n_pad;
     b.bx = ctx->bx; b.by = ctx->by; b.bz = ctx->bz;
     b.g0 = ctx->g0; b.g1 = ctx->g1; b.g2 = ctx->g2; b.quat = ctx->quat; b.sdens = ctx->sdens; b.hk = ctx->hk;
@@ -439,7 +455,6 @@ static int ensure_lists(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m,
     b.tiles_x = tiles_x; b.tiles_y = tiles_y; b.ty_first = ty_first;
     b.total_dev = ctx->bin_total_dev;
     b.big_slot = ctx->big_slot; b.big_rect = ctx->big_rect; b.big_grid = ctx->sm_count * 4;
-    ScopedTimer timer(ctx, s, 2);
     unsigned long long total64 = 0;
     for (int attempt = 0; attempt < 2; ++attempt) {
         b.keys_in = ctx->bin_keys_in; b.vals_in = ctx->bin_vals_in; b.pair_cap = ctx->bin_pair_cap;
@@ -453,8 +468,14 @@ static int ensure_lists(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m,
         if (total64 <= ctx->bin_pair_cap) break;
         if ((e = grow_pairs((size_t)total64)) != cudaSuccess) return cuda_fail(ctx, e, "tile-list workspace pairs");
     }
-    const int total = (int)total64;
-    const size_t ent_need = (((size_t)total + 32u * (size_t)ntiles + 31) / 32) * 32 + 32;
+    total = (int)total64;
+    return RGX_OK;
+}
+
+// Sorts `count` pairs (keys, vals) into the per-tile lists and points ctx->lists at them.
+static int fill_lists(rgx_ctx* ctx, BinLaunch& b, uint64_t* keys, uint32_t* vals, int count, int ntiles, cudaStream_t s) {
+    cudaError_t e = cudaSuccess;
+    const size_t ent_need = (((size_t)count + 32u * (size_t)ntiles + 31) / 32) * 32 + 32;
     if (ent_need > ctx->bin_ent_cap) {
         size_t c = ent_need + ent_need / 4;
         c = ((c + 31) / 32) * 32;
@@ -466,25 +487,149 @@ static int ensure_lists(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m,
         RGB_(bin_cub, cub_need);
         ctx->bin_cub_cap = cub_need;
     }
-#undef RGB_
-    b.keys_in = ctx->bin_keys_in; b.keys_out = ctx->bin_keys_out; b.vals_in = ctx->bin_vals_in; b.vals_out = ctx->bin_vals_out;
+    b.keys_in = keys; b.vals_in = vals;
+    b.keys_out = ctx->bin_keys_out; b.vals_out = ctx->bin_vals_out;
     b.pair_cap = ctx->bin_pair_cap;
     b.tile_first = ctx->tile_first; b.tile_last = ctx->tile_last; b.tile_cnt = ctx->tile_cnt; b.tile_pcnt = ctx->tile_pcnt;
     b.tile_pbegin = ctx->tile_pbegin;
     b.tile_iota = ctx->tile_iota; b.tile_cnt_sorted = ctx->tile_cnt_sorted; b.tile_order = ctx->tile_order;
     b.ent_id = ctx->ent_id; b.ent_range = ctx->ent_range; b.blk = ctx->ent_blk;
     b.cub_temp = ctx->bin_cub; b.cub_bytes = ctx->bin_cub_cap;
-    if ((e = launch_bin_fill(b, total, s)) != cudaSuccess) return cuda_fail(ctx, e, "tile-list fill");
+    if ((e = launch_bin_fill(b, count, s)) != cudaSuccess) return cuda_fail(ctx, e, "tile-list fill");
     ctx->lists.ent_id = ctx->ent_id; ctx->lists.ent_range = ctx->ent_range; ctx->lists.blk = ctx->ent_blk;
     ctx->lists.tile_pbegin = ctx->tile_pbegin; ctx->lists.tile_cnt = ctx->tile_cnt; ctx->lists.tile_order = ctx->tile_order;
-    ctx->lists.tiles_x = tiles_x; ctx->lists.tiles_y = tiles_y; ctx->lists.ty_first = ty_first;
+    ctx->lists.tiles_x = b.tiles_x; ctx->lists.tiles_y = b.tiles_y; ctx->lists.ty_first = b.ty_first;
+    return RGX_OK;
+}
+
+static void lists_now_valid(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, int total) {
     ctx->lists_cam = *cam;
     ctx->lists_row_begin = m->row_begin; ctx->lists_row_end = m->row_end;
     ctx->lists_build_id = ctx->build_id;
     ctx->lists_valid = true;
     ctx->last_pairs = total;
+}
+
+// Makes ctx->lists valid for this camera and row range (no-op if they already are).
+static int ensure_lists(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, cudaStream_t s) {
+    if (lists_cached(ctx, cam, m)) return RGX_OK;
+    ctx->lists_valid = false;
+    if (m->row_end <= m->row_begin || ctx->n == 0) return RGX_OK;   // nothing to march
+    ScopedTimer timer(ctx, s, 2);
+    BinLaunch b;
+    int total = 0, ntiles = 0;
+    int rc = emit_pairs(ctx, cam, m, s, b, total, ntiles);
+    if (rc) return rc;
+    if ((rc = fill_lists(ctx, b, ctx->bin_keys_in, ctx->bin_vals_in, total, ntiles, s))) return rc;
+    lists_now_valid(ctx, cam, m, total);
     return RGX_OK;
 }
+
+// Forward-only march of a view with many more (tile, Gaussian) pairs than its rays will look at: the lists
+// are made in two depths (binning.cu) and the march runs in two phases (march_lists.cu, HZ variant).
+// handled = false: the view does not qualify; its complete lists have been made instead.
+static int forward_two_depth(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, MarchLaunch& L, cudaStream_t s,
+                             bool& handled) {
+    handled = false;
+    cudaError_t e = cudaSuccess;
+    ctx->lists_valid = false;
+    BinLaunch b;
+    int total = 0, ntiles = 0, rc;
+    {
+        ScopedTimer timer(ctx, s, 2);
+        if ((rc = emit_pairs(ctx, cam, m, s, b, total, ntiles))) return rc;
+    }
+    const long long rays = (long long)cam->width * (m->row_end - m->row_begin);
+    auto plain = [&]() -> int {
+        ScopedTimer timer(ctx, s, 2);
+        int r2 = fill_lists(ctx, b, ctx->bin_keys_in, ctx->bin_vals_in, total, ntiles, s);
+        if (r2 == RGX_OK) lists_now_valid(ctx, cam, m, total);
+        return r2;
+    };
+    if ((long long)total < (long long)ctx->hz_min_pairs_per_ray * rays || total == 0) return plain();
+    // workspace of the two-depth path
+    if (!ctx->hz_hist) {
+        RGB_(hz_hist, 2048); RGB_(hz_scalars, 4);
+        if ((e = cudaMallocHost((void**)&ctx->hz_hist_host, 2048 * sizeof(unsigned int))) != cudaSuccess ||
+            (e = cudaMallocHost((void**)&ctx->hz_scalars_host, 4 * sizeof(unsigned long long))) != cudaSuccess)
+            return cuda_fail(ctx, e, "pinned histogram");
+    }
+    if (ctx->bin_pair_cap > ctx->sel_cap) {
+        RGB_(sel_keys, ctx->bin_pair_cap); RGB_(sel_vals, ctx->bin_pair_cap);
+        ctx->sel_cap = ctx->bin_pair_cap;
+    }
+    if (ntiles > ctx->hz_tiles_cap) {
+        RGB_(tile_more, (size_t)ntiles + 64); RGB_(tile_resume, (size_t)ntiles + 64);
+        ctx->hz_tiles_cap = ntiles + 64;
+    }
+    const long long all_rays = (long long)cam->width * cam->height;
+    if (2 * all_rays > ctx->hz_state_cap) {
+        RGB_(hz_state, (size_t)(2 * all_rays));
+        ctx->hz_state_cap = 2 * all_rays;
+    }
+    // where the pairs begin: the first phase takes the nearest ones, about hz_budget_per_ray per ray
+    if ((e = cudaMemsetAsync(ctx->hz_hist, 0, 2048 * sizeof(unsigned int), s)) != cudaSuccess ||
+        (e = cudaMemsetAsync(ctx->tile_more, 0, sizeof(int) * (size_t)ntiles, s)) != cudaSuccess ||
+        (e = cudaMemsetAsync(ctx->tile_resume, 0, sizeof(int) * (size_t)ntiles, s)) != cudaSuccess ||
+        (e = cudaMemsetAsync(ctx->hz_scalars, 0, 4 * sizeof(unsigned long long), s)) != cudaSuccess ||
+        (e = launch_bin_hist(b, total, ctx->hz_hist, s)) != cudaSuccess ||
+        (e = cudaMemcpyAsync(ctx->hz_hist_host, ctx->hz_hist, 2048 * sizeof(unsigned int), cudaMemcpyDeviceToHost, s)) != cudaSuccess ||
+        (e = cudaStreamSynchronize(s)) != cudaSuccess)
+        return cuda_fail(ctx, e, "near-distance histogram");
+    const long long budget = (long long)ctx->hz_budget_per_ray * rays;
+    long long cum = 0;
+    int cut = -1;
+    for (int i = 0; i < 2048; ++i) {
+        if (ctx->hz_hist_host[i] == 0) continue;
+        if (cut >= 0 && cum + ctx->hz_hist_host[i] > budget) break;
+        cum += ctx->hz_hist_host[i];
+        cut = i;
+    }
+    if (cut < 0 || cum >= total) return plain();               // everything begins within the budget: one depth is enough
+    const float horizon = bin_hist_bucket_end(cut);
+    const int count1 = (int)cum;
+    if ((e = launch_bin_select(b, total, 0, (unsigned int)cut, nullptr, ctx->sel_keys, ctx->sel_vals, ctx->hz_scalars, ctx->tile_more, s)) != cudaSuccess)
+        return cuda_fail(ctx, e, "pair selection");
+    uint64_t* all_keys = ctx->bin_keys_in;
+    uint32_t* all_vals = ctx->bin_vals_in;
+    if ((rc = fill_lists(ctx, b, ctx->sel_keys, ctx->sel_vals, count1, ntiles, s))) return rc;
+    L.lists = ctx->lists;
+    L.hz_phase = 1; L.horizon = horizon; L.hz_state = ctx->hz_state; L.tile_more = ctx->tile_more;
+    L.tile_resume = ctx->tile_resume; L.hz_count = reinterpret_cast<unsigned int*>(ctx->hz_scalars + 1);
+    {
+        ScopedTimer timer(ctx, s, 0);
+        e = launch_march_forward(L, s);
+    }
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "forward march, first depth");
+    if ((e = cudaMemcpyAsync(ctx->hz_scalars_host, ctx->hz_scalars, 4 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, s)) != cudaSuccess ||
+        (e = cudaStreamSynchronize(s)) != cudaSuccess)
+        return cuda_fail(ctx, e, "first depth read-back");
+    const long long stopped = (long long)(ctx->hz_scalars_host[1] & 0xffffffffull);
+    long long count2 = 0;
+    if (stopped > 0) {
+        // the complete lists of the tiles in which a ray stopped
+        b.keys_in = all_keys; b.vals_in = all_vals;
+        if ((e = cudaMemsetAsync(ctx->hz_scalars, 0, sizeof(unsigned long long), s)) != cudaSuccess ||
+            (e = launch_bin_select(b, total, 1, 0u, ctx->tile_resume, ctx->sel_keys, ctx->sel_vals, ctx->hz_scalars, nullptr, s)) != cudaSuccess ||
+            (e = cudaMemcpyAsync(ctx->hz_scalars_host, ctx->hz_scalars, sizeof(unsigned long long), cudaMemcpyDeviceToHost, s)) != cudaSuccess ||
+            (e = cudaStreamSynchronize(s)) != cudaSuccess)
+            return cuda_fail(ctx, e, "second depth selection");
+        count2 = (long long)ctx->hz_scalars_host[0];
+        if ((rc = fill_lists(ctx, b, ctx->sel_keys, ctx->sel_vals, (int)count2, ntiles, s))) return rc;
+        L.lists = ctx->lists;
+        L.hz_phase = 2;
+        {
+            ScopedTimer timer(ctx, s, 0);
+            e = launch_march_forward(L, s);
+        }
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "forward march, second depth");
+    }
+    ctx->hz_last[0] = total; ctx->hz_last[1] = count1; ctx->hz_last[2] = stopped; ctx->hz_last[3] = count2;
+    ctx->last_pairs = total;
+    handled = true;
+    return RGX_OK;
+}
+#undef RGB_
 
 static int prepare_march(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, const rgx_march* march,
                          MarchLaunch& L) {
@@ -511,11 +656,19 @@ static int forward_impl(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* 
     cudaSetDevice(ctx->device);
     cudaStream_t s = (cudaStream_t)stream;
     if ((rc = run_colors(ctx, scene, cam->eye, s))) return rc;
+    L.rgb = rgb; L.alpha = alpha; L.depth = depth; L.frame = frame;
     if (!(march->flags & (RGX_FLAG_BRUTE_FORCE | RGX_FLAG_PER_RAY_SEARCH))) {
-        if ((rc = ensure_lists(ctx, cam, march, s))) return rc;
+        // a forward that nothing follows (no recording, no counting) and whose lists are yet to be made may take
+        // the two-depth path, if the view turns out to have far more pairs than rays
+        const bool forward_only = !(march->flags & (RGX_FLAG_SAVE_HITS | RGX_FLAG_COUNT_WORK)) && ctx->n > 0 &&
+                                  march->row_end > march->row_begin && ctx->hz_min_pairs_per_ray >= 0;
+        if (forward_only && !lists_cached(ctx, cam, march)) {
+            bool handled = false;
+            if ((rc = forward_two_depth(ctx, cam, march, L, s, handled))) return rc;
+            if (handled) return RGX_OK;
+        } else if ((rc = ensure_lists(ctx, cam, march, s))) return rc;
         L.lists = ctx->lists;
     }
-    L.rgb = rgb; L.alpha = alpha; L.depth = depth; L.frame = frame;
     cudaError_t e;
     const bool record = (march->flags & RGX_FLAG_SAVE_HITS) && L.lists.ent_id != nullptr && ctx->n > 0;
     if (march->flags & RGX_FLAG_SAVE_HITS) ctx->tape_valid = false;
@@ -680,6 +833,19 @@ int rgx_scene_box(rgx_ctx* ctx, float bb_min[3], float bb_max[3], rgx_stream str
 int rgx_debug_fail_allocation(rgx_ctx* ctx, int nth) {
     if (!ctx) return RGX_E_INVALID;
     ctx->fail_alloc_in = nth;
+    return RGX_OK;
+}
+
+int rgx_debug_two_depth(rgx_ctx* ctx, int min_pairs_per_ray, int budget_per_ray) {
+    if (!ctx || budget_per_ray < 0) return RGX_E_INVALID;
+    ctx->hz_min_pairs_per_ray = min_pairs_per_ray;
+    if (budget_per_ray > 0) ctx->hz_budget_per_ray = budget_per_ray;
+    return RGX_OK;
+}
+
+int rgx_read_two_depth(rgx_ctx* ctx, long long out[4]) {
+    if (!ctx || !out) return RGX_E_INVALID;
+    for (int i = 0; i < 4; ++i) { out[i] = ctx->hz_last[i]; ctx->hz_last[i] = 0; }
     return RGX_OK;
 }
 

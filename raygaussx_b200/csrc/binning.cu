@@ -16,6 +16,7 @@
 #include <cub/device/device_radix_sort.cuh>
 #include <cub/device/device_scan.cuh>
 #include <cub/block/block_scan.cuh>
+#include <cstring>
 
 namespace rgx {
 
@@ -495,6 +496,74 @@ __global__ void __launch_bounds__(256) bin_blocks_kernel(BinLaunch b, size_t n_b
     if (lane == 0) b.blk[blk] = make_float2(lo, hi);
 }
 
+// ---------------------------------------------------------------- lists in two depths (forward-only views whose rays end early)
+//
+// A dense view can have hundreds of (tile, Gaussian) pairs per ray of which the rays, ending after a slab
+// or two, look at a few.  For such a view the pairs are not sorted all at once: a histogram of their near
+// distances picks a depth, only the pairs that begin before it are sorted and marched, and the rest is
+// sorted only for the tiles in which some ray got that far (march_lists.cu, horizon variant).
+
+constexpr int kHistBits = 11;      // leading bits of the quantised near distance: 8 of the exponent, 3 of the mantissa
+
+__global__ void __launch_bounds__(256) bin_hist_kernel(const uint64_t* __restrict__ keys, int total, int shift,
+                                                       unsigned int* hist) {
+    __shared__ unsigned int local[1 << kHistBits];
+    for (int i = threadIdx.x; i < (1 << kHistBits); i += blockDim.x) local[i] = 0u;
+    __syncthreads();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
+        atomicAdd(&local[(unsigned)(keys[i] >> shift) & ((1u << kHistBits) - 1u)], 1u);
+    __syncthreads();
+    for (int i = threadIdx.x; i < (1 << kHistBits); i += blockDim.x)
+        if (local[i]) atomicAdd(&hist[i], local[i]);
+}
+
+// MODE 0: keeps the pairs whose near distance lies in histogram bucket <= cut, and marks the tiles that have
+// pairs beyond.  MODE 1: keeps the pairs of the tiles flagged in tile_flag.  Output order is arbitrary (the
+// keys are unique and get sorted).  One atomic per block.
+template <int MODE>
+__global__ void __launch_bounds__(256) bin_select_kernel(const uint64_t* __restrict__ keys, const uint32_t* __restrict__ vals,
+                                                         int total, KeyLayout kl, unsigned int cut, const int* __restrict__ tile_flag,
+                                                         uint64_t* out_k, uint32_t* out_v, unsigned long long* counter,
+                                                         int* tile_more) {
+    constexpr int kPer = 8;
+    using Scan = cub::BlockScan<int, 256>;
+    __shared__ typename Scan::TempStorage scan_tmp;
+    __shared__ unsigned long long base_s;
+    const long long blk0 = (long long)blockIdx.x * 256 * kPer;
+    uint64_t k[kPer];
+    unsigned keep = 0u;
+    int mine = 0;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+        const long long idx = blk0 + (long long)i * 256 + threadIdx.x;
+        k[i] = 0;
+        if (idx < total) {
+            k[i] = keys[idx];
+            const int t = (int)(k[i] >> (kl.near_bits + kl.id_bits));
+            bool kp;
+            if (MODE == 0) {
+                kp = ((unsigned)(k[i] >> (kl.id_bits + kl.near_bits - kHistBits)) & ((1u << kHistBits) - 1u)) <= cut;
+                if (!kp) tile_more[t] = 1;
+            } else {
+                kp = tile_flag[t] != 0;
+            }
+            if (kp) { keep |= 1u << i; ++mine; }
+        }
+    }
+    int offset, block_total;
+    Scan(scan_tmp).ExclusiveSum(mine, offset, block_total);
+    if (threadIdx.x == 0) base_s = block_total ? atomicAdd(counter, (unsigned long long)block_total) : 0ull;
+    __syncthreads();
+    unsigned long long at = base_s + (unsigned long long)offset;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i)
+        if (keep & (1u << i)) {
+            out_k[at] = k[i];
+            out_v[at] = vals[blk0 + (long long)i * 256 + threadIdx.x];
+            ++at;
+        }
+}
+
 }  // namespace
 
 size_t binning_cub_temp_bytes(size_t pair_cap, int ntiles) {
@@ -552,6 +621,35 @@ cudaError_t launch_bin_fill(const BinLaunch& b, int total, cudaStream_t s) {
     if (total > 0) bin_scatter_kernel<<<(total + tb - 1) / tb, tb, 0, s>>>(b, total, kl);
     const size_t n_blocks = (n_entries + 31) / 32;
     bin_blocks_kernel<<<(unsigned)((n_blocks + 7) / 8), 256, 0, s>>>(b, n_blocks);
+    return cudaGetLastError();
+}
+
+// Histogram of the pairs' near distances (2^11 buckets, see bin_hist_kernel), added into hist.
+cudaError_t launch_bin_hist(const BinLaunch& b, int total, unsigned int* hist, cudaStream_t s) {
+    const KeyLayout kl = key_layout(b.tiles_x * ((b.cam.height + b.tile - 1) / b.tile), b.n_pad);
+    if (kl.near_bits < kHistBits) return cudaErrorInvalidValue;
+    if (total > 0) bin_hist_kernel<<<592, 256, 0, s>>>(b.keys_in, total, kl.id_bits + kl.near_bits - kHistBits, hist);
+    return cudaGetLastError();
+}
+
+// Upper end of histogram bucket `bucket` as a distance: every pair in buckets <= bucket begins before it.
+float bin_hist_bucket_end(int bucket) {
+    // the key keeps the float's bits below the sign; bucket = its leading kHistBits bits
+    if (bucket + 1 >= (255 << (kHistBits - 8))) return INFINITY;
+    const unsigned int bits = ((unsigned int)(bucket + 1) << (31 - kHistBits));
+    float f;
+    std::memcpy(&f, &bits, sizeof(f));
+    return f;
+}
+
+// Selection of pairs into (out_k, out_v); counter (zeroed by the caller) receives their number.
+cudaError_t launch_bin_select(const BinLaunch& b, int total, int mode, unsigned int cut, const int* tile_flag, uint64_t* out_k,
+                              uint32_t* out_v, unsigned long long* counter, int* tile_more, cudaStream_t s) {
+    const KeyLayout kl = key_layout(b.tiles_x * ((b.cam.height + b.tile - 1) / b.tile), b.n_pad);
+    if (total <= 0) return cudaSuccess;
+    const int blocks = (int)(((long long)total + 2047) / 2048);
+    if (mode == 0) bin_select_kernel<0><<<blocks, 256, 0, s>>>(b.keys_in, b.vals_in, total, kl, cut, tile_flag, out_k, out_v, counter, tile_more);
+    else bin_select_kernel<1><<<blocks, 256, 0, s>>>(b.keys_in, b.vals_in, total, kl, cut, tile_flag, out_k, out_v, counter, tile_more);
     return cudaGetLastError();
 }
 

@@ -193,7 +193,13 @@ __device__ __forceinline__ bool ray_pixel(const MarchLaunch& L, int tile_x, int 
 }
 
 // ---------------------------------------------------------------- forward
-template <bool COUNT, bool SAVE>
+// HZ: the two-depth variant for forward-only views whose rays end early (binning.cu).  In its first phase
+// (L.hz_phase == 1) the tile lists hold only the pairs that begin before L.horizon; a ray that would need more
+// -- its next slab reaches past the horizon, or a closest-hit query finds nothing before it, in a tile that has
+// pairs beyond (L.tile_more) -- puts its state aside (L.hz_state), flags its tile (L.tile_resume) and stops.
+// The second phase (L.hz_phase == 2) has the complete lists of the flagged tiles and takes those rays up where
+// they stopped: same slabs, same hits in the same order, same image.
+template <bool COUNT, bool SAVE, bool HZ = false>
 __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 3) march_forward_lists_kernel(const __grid_constant__ MarchLaunch L) {
     __shared__ ListShared sh;
     __shared__ TapeState tape_state[SAVE ? kWarps : 1];
@@ -202,6 +208,7 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 3) march_forward_lists_k
     WarpStage& ws = sh.ws[warp];
     int* pend = sh.pend[warp];
     const int tile = L.lists.tile_order ? __ldg(&L.lists.tile_order[blockIdx.x]) : blockIdx.x;   // longest lists first
+    if (HZ && L.hz_phase == 2 && !L.tile_resume[tile]) return;      // no ray of this tile stopped at the horizon
     const int tile_x = tile % L.lists.tiles_x, tile_y = tile / L.lists.tiles_x;
     const float eps = L.m.transmittance_eps;
     const float bg = L.m.white_background ? 1.0f : 0.0f;
@@ -238,14 +245,55 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 3) march_forward_lists_k
         // cycle counters of the counting variant: whole ray, closest-hit queries, slab queries (the
         // evaluation of the staged hits is timed inside slab_sums), compositing
         const long long c_ray = COUNT ? clock64() : 0;
-        float first = closest_in_tile<COUNT>(L, r, tenter, texit, tv, cursor, pend, lane, tl);
+        // two-depth variant: 0 = march from the start, 1 = resume at a slab, 2 = resume at the first query,
+        // 3 = resume at a query after an empty slab; what was put aside is (tbuffer, T, tenter, mode) + colour
+        int hz_mode = 0;
+        bool hz_more = false, hz_susp = false;
+        float4 hz_a = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (HZ) {
+            hz_more = L.hz_phase == 1 && L.tile_more[tile] != 0;
+            if (L.hz_phase == 2) {
+                hz_a = L.hz_state[2 * (size_t)ray_id];
+                hz_mode = (int)hz_a.w;
+                if (hz_mode == 0) continue;                                       // finished in the first phase
+                if (hz_mode != 2) {
+                    T = hz_a.y;
+                    if (lane == 0) sh.color[warp] = L.hz_state[2 * (size_t)ray_id + 1];
+                }
+            }
+        }
+        float first;
+        if (HZ && (hz_mode == 1 || hz_mode == 3)) first = hz_a.z;                  // the first hit is known
+        else first = closest_in_tile<COUNT>(L, r, tenter, texit, tv, cursor, pend, lane, tl);
         if (COUNT) tl.v[C_CYC_SEEK] += clock64() - c_ray;
-        if (first < INFINITY && first < texit) {                                  // :249-260
+        if (HZ && hz_more && !(first < L.horizon)) {                             // nothing before the horizon: ask again later
+            hz_susp = true;
+            if (lane == 0) {
+                L.hz_state[2 * (size_t)ray_id] = make_float4(tenter, 1.0f, tenter, 2.0f);
+                L.tile_resume[tile] = 1;
+                atomicAdd(L.hz_count, 1u);
+            }
+        } else if (first < INFINITY && first < texit) {                           // :249-260
             tenter = first;
             float tbuffer = tenter;
             int slab_index = 0;
+            if (HZ && hz_mode == 1) tbuffer = hz_a.x;
+            if (HZ && hz_mode == 3) {                                             // the query after an empty slab, again
+                const float nxt = closest_in_tile<COUNT>(L, r, hz_a.x, texit, tv, cursor, pend, lane, tl);
+                tbuffer = nxt < INFINITY ? nxt : texit;                           // nothing further: the loop below does not start
+            }
             while (tbuffer < texit && T > eps && slab_index < kMaxSlabs) {        // :266
                 SlabPlan p = plan_slab(L.m, tbuffer, T, tenter, texit);
+                if (HZ && hz_more && !(p.tmax < L.horizon)) {                        // this slab needs pairs from beyond
+                    hz_susp = true;
+                    if (lane == 0) {
+                        L.hz_state[2 * (size_t)ray_id] = make_float4(tbuffer, T, tenter, 1.0f);
+                        L.hz_state[2 * (size_t)ray_id + 1] = sh.color[warp];
+                        L.tile_resume[tile] = 1;
+                        atomicAdd(L.hz_count, 1u);
+                    }
+                    break;
+                }
                 if (COUNT) tl.v[C_SLABS] += 1;
                 ++slab_index;
                 if (!p.traced) { tbuffer = __fadd_rn(tbuffer, p.slab); continue; }
@@ -298,6 +346,16 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 3) march_forward_lists_k
                     const long long c_s = COUNT ? clock64() : 0;
                     float nxt = closest_in_tile<COUNT>(L, r, tbuffer, texit, tv, cursor, pend, lane, tl);
                     if (COUNT) tl.v[C_CYC_SEEK] += clock64() - c_s;
+                    if (HZ && hz_more && !(nxt < L.horizon)) {                   // the next hit, if any, is beyond the horizon
+                        hz_susp = true;
+                        if (lane == 0) {
+                            L.hz_state[2 * (size_t)ray_id] = make_float4(tbuffer, T, tenter, 3.0f);
+                            L.hz_state[2 * (size_t)ray_id + 1] = sh.color[warp];
+                            L.tile_resume[tile] = 1;
+                            atomicAdd(L.hz_count, 1u);
+                        }
+                        break;
+                    }
                     if (!(nxt < INFINITY)) break;
                     tbuffer = nxt;
                     continue;
@@ -309,10 +367,11 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 3) march_forward_lists_k
                 tbuffer = __fadd_rn(tbuffer, p.slab);                             // :324
             }
         }
-        if (lane == 0) {                                                           // :326-339
+        if (lane == 0 && !(HZ && hz_susp)) {                                       // :326-339
             const float4 acc = sh.color[warp];
             const RayColor st = {T, acc.x, acc.y, acc.z, acc.w};
             write_ray(L, ray_id, st, bg);
+            if (HZ && L.hz_phase == 1) L.hz_state[2 * (size_t)ray_id] = make_float4(0.f, 0.f, 0.f, 0.f);   // done
             if (save) {
                 L.ray_head[ray_id] = tq.ok ? tq.head : -2;
                 if (!tq.ok) L.tile_unrecorded[tile] = 1;
@@ -647,6 +706,10 @@ cudaError_t launch_march_forward(const MarchLaunch& m, cudaStream_t s) {
     const int grid = m.lists.tiles_x * m.lists.tiles_y;
     if (grid <= 0) return cudaSuccess;
     const bool count = (m.m.flags & RGX_FLAG_COUNT_WORK) != 0, save = m.tape != nullptr;
+    if (m.hz_phase != 0) {
+        march_forward_lists_kernel<false, false, true><<<grid, kThreads, 0, s>>>(m);
+        return cudaGetLastError();
+    }
     if (count && save) march_forward_lists_kernel<true, true><<<grid, kThreads, 0, s>>>(m);
     else if (count) march_forward_lists_kernel<true, false><<<grid, kThreads, 0, s>>>(m);
     else if (save) march_forward_lists_kernel<false, true><<<grid, kThreads, 0, s>>>(m);

@@ -114,6 +114,13 @@ struct MarchLaunch {
     long long tape_cap;
     long long* ray_head;
     int* tile_unrecorded;   // per tile (of the lists): set by the forward when a ray of the tile got ray_head = -2
+    // two-depth forward (march_lists.cu, HZ variant): 0 = off, 1 = first phase (lists up to `horizon`), 2 = second
+    int hz_phase;
+    float horizon;
+    float4* hz_state;         // [R, 2] what a ray put aside: (tbuffer, T, tenter, mode), colour and depth
+    const int* tile_more;     // per tile: has pairs that begin beyond the horizon
+    int* tile_resume;         // per tile: some ray stopped at the horizon
+    unsigned int* hz_count;   // rays that stopped
     float4* grad_rows;    // [grad_copies, n_pad, 4] float4 of accumulated moments, layout in emit_global
     int grad_copies;      // power of two
 };
@@ -168,6 +175,10 @@ cudaError_t launch_finalize(const FinalizeLaunch& f, cudaStream_t s);
 size_t binning_cub_temp_bytes(size_t pair_cap, int ntiles);
 cudaError_t launch_bin_emit(const BinLaunch& b, cudaStream_t s);
 cudaError_t launch_bin_fill(const BinLaunch& b, int total, cudaStream_t s);
+cudaError_t launch_bin_hist(const BinLaunch& b, int total, unsigned int* hist, cudaStream_t s);
+float bin_hist_bucket_end(int bucket);
+cudaError_t launch_bin_select(const BinLaunch& b, int total, int mode, unsigned int cut, const int* tile_flag, uint64_t* out_k,
+                              uint32_t* out_v, unsigned long long* counter, int* tile_more, cudaStream_t s);
 cudaError_t launch_march_forward(const MarchLaunch& m, cudaStream_t s);
 cudaError_t launch_march_backward(const MarchLaunch& m, cudaStream_t s);
 

@@ -154,3 +154,63 @@ def test_tile_lists_hold_every_hit_of_needle_like_gaussians(cam_index):
     frame, _ = r.forward_frame(*tens, cs, march(ro, sc, cs))
     want = (got["lists"][0].clamp(0, 1) * 256).to(torch.int32).clamp(max=255).reshape(cs.height, cs.width, 3)
     assert (frame[..., :3].to(torch.int32) - want).abs().max().item() <= 1      # one step where the two images round apart
+
+
+def two_depth(r, min_pairs, budget):
+    import ctypes as C
+    _lib.check(r._ctx, r._lib.rgx_debug_two_depth(r._ctx, C.c_int(min_pairs), C.c_int(budget)))
+
+
+def read_two_depth(r):
+    import ctypes as C
+    out = (C.c_longlong * 4)()
+    _lib.check(r._ctx, r._lib.rgx_read_two_depth(r._ctx, out))
+    return list(out)
+
+
+@pytest.mark.parametrize("kind,budget", [("stress", 1), ("stress", 8), ("stress", 64), ("unbounded", 2), ("unbounded", 16),
+                                         ("tiny", 1), ("tiny", 4)])
+def test_two_depth_forward_is_bit_identical(kind, budget):
+    """Lists made in two depths, march in two phases: the same slabs meet the same hits in the same order, so
+    colour, alpha and depth equal the one-depth march bit for bit -- whatever share of the rays has to go on
+    into the second depth."""
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device: there is no CPU path")
+    from raygaussx_b200 import render_optix as ro
+    dev = torch.device("cuda")
+    if kind == "stress":
+        sc = scenes.stress_scene(n_uniform=60_000, n_cluster=10_000, n_cameras=2, width=320, height=180)
+    elif kind == "unbounded":
+        sc = scenes.unbounded_scene(n=200_000, n_cameras=2, width=314, height=207)
+    else:
+        sc = scenes.tiny_scene(n=512, width=40, height=24, log_scale_mean=-2.5, dynamic_sampling=True, dt_step=0.005)
+    tens = [t.to(dev).contiguous() for t in sc.tensors()]
+    r = ro.Renderer(dev)
+    r.build(*tens[:4])
+    try:
+        for cam in sc.cameras[:2]:
+            cam.to(dev)
+            cs = ro.camera_struct(cam)
+            r.build(*tens[:4])
+            two_depth(r, -1, 0)                                   # off
+            want = r.forward(*tens, cs, march(ro, sc, cs), want_alpha=True, want_depth=True)
+            assert read_two_depth(r) == [0, 0, 0, 0]
+            r.build(*tens[:4])                                    # a new build: the next forward makes its lists anew
+            two_depth(r, 0, budget)                               # forced, `budget` pairs per ray in the first depth
+            got = r.forward(*tens, cs, march(ro, sc, cs), want_alpha=True, want_depth=True)
+            emitted, first, stopped, second = read_two_depth(r)
+            for a, b in zip(want, got):
+                assert torch.equal(a, b)
+            if emitted:                                           # (a budget that covers every pair falls back to one depth)
+                assert 0 < first < emitted and second <= emitted
+                assert (stopped == 0) == (second == 0)
+            # a row range through the same path
+            rows = (8, cs.height - 3)
+            part = torch.zeros_like(want[0])
+            r.forward(*tens, cs, march(ro, sc, cs, rows=rows), out=part)
+            lo, hi = rows[0] * cs.width, rows[1] * cs.width
+            assert torch.equal(part[lo:hi], want[0][lo:hi])
+            read_two_depth(r)                                     # clears the figures of the row-range forward
+    finally:
+        two_depth(r, 48, 16)
+        del r
