@@ -183,6 +183,15 @@ RGX_API int rgx_forward_frame(rgx_ctx* ctx, const rgx_scene* scene, const rgx_ca
 RGX_API int rgx_backward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, const rgx_march* march,
                  const float* rgb, const float* dL_drgb, const rgx_grads* grads, rgx_stream stream);
 
+/* Announces the view of the next rgx_forward (no counterpart in the reference, where OptiX traversal needs no
+ * per-view preparation).  The rgx_backward that follows makes that view's tile lists on a stream of the context's
+ * own, beside its replay of the recording and the gradient assembly, which read no lists; the announced forward
+ * then finds them made (it waits for them on its stream).  Purely an optimisation: results are those of the
+ * calls without it, a wrong announcement costs one unused list construction.  The announcement holds for one
+ * rgx_backward; NULL, NULL withdraws it.  rgx_lists_made_ahead: how many lists were made this way so far. */
+RGX_API int rgx_hint_next_view(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* march);
+RGX_API int rgx_lists_made_ahead(const rgx_ctx* ctx);
+
 /* Per-Gaussian view-dependent colour only (render_optix.py:19-32): rgb_out [n,3]
  * in the caller's Gaussian order. */
 RGX_API int rgx_gaussian_colors(rgx_ctx* ctx, const rgx_scene* scene, const float eye[3], float* rgb_out,

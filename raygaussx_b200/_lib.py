@@ -64,6 +64,8 @@ SYMBOLS = {
                                     C.c_void_p]),
     "rgx_backward": (C.c_int, [C.c_void_p, C.POINTER(Scene), C.POINTER(Camera), C.POINTER(March), _fp, _fp,
                                C.POINTER(Grads), C.c_void_p]),
+    "rgx_hint_next_view": (C.c_int, [C.c_void_p, C.POINTER(Camera), C.POINTER(March)]),
+    "rgx_lists_made_ahead": (C.c_int, [C.c_void_p]),
     "rgx_gaussian_colors": (C.c_int, [C.c_void_p, C.POINTER(Scene), C.POINTER(C.c_float), _fp, C.c_void_p]),
     "rgx_scene_box": (C.c_int, [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float), C.c_void_p]),
     "rgx_debug_fail_allocation": (C.c_int, [C.c_void_p, C.c_int]),

@@ -85,6 +85,15 @@ struct rgx_ctx {
     unsigned long long tape_build_id = 0;
     rgx_camera tape_cam{};
     int tape_row_begin = 0, tape_row_end = 0;
+    int* tape_tile_order = nullptr; int tape_order_cap = 0;   // order of the recording forward's CTAs, kept for the replay
+    // lists of the view announced by rgx_hint_next_view, made on a stream of the context's own while the backward replays
+    cudaStream_t side = nullptr;
+    cudaEvent_t ev_main = nullptr, ev_lists = nullptr;
+    bool lists_event_set = false;      // ev_lists marks the end of the latest work on `side`
+    bool hint_set = false;
+    rgx_camera hint_cam{};
+    rgx_march hint_march{};
+    int prefetched = 0;                // lists made ahead so far (instrumentation)
     // optional kernel timing
     bool profiling = false;
     struct Timed { cudaEvent_t a, b; int kind; };
@@ -146,7 +155,7 @@ void release_workspace(rgx_ctx* ctx) {
                      (void**)&ctx->tile_cnt_sorted, (void**)&ctx->tile_order, (void**)&ctx->big_slot,
                      (void**)&ctx->big_rect, (void**)&ctx->tile_unrecorded, (void**)&ctx->sel_keys, (void**)&ctx->sel_vals,
                      (void**)&ctx->hz_hist, (void**)&ctx->tile_more, (void**)&ctx->tile_resume, (void**)&ctx->hz_state,
-                     (void**)&ctx->hz_scalars};
+                     (void**)&ctx->hz_scalars, (void**)&ctx->tape_tile_order};
     for (void** p : ptrs) {
         if (*p) cudaFree(*p);
         *p = nullptr;
@@ -160,6 +169,9 @@ void release_workspace(rgx_ctx* ctx) {
     ctx->big_cap = 0;
     ctx->tape_cap = 0;
     ctx->ray_head_cap = 0;
+    ctx->tape_order_cap = 0;
+    ctx->lists_event_set = false;
+    ctx->hint_set = false;
     ctx->sel_cap = 0; ctx->hz_tiles_cap = 0; ctx->hz_state_cap = 0;
     ctx->built = false;
     ctx->lists_valid = false;
@@ -302,6 +314,11 @@ struct ScopedTimer {   // brackets one kernel launch with events when profiling 
     }
 };
 
+// Work of the context's own stream (lists made ahead) is ordered before whatever `s` gets next.
+void join_side(rgx_ctx* ctx, cudaStream_t s) {
+    if (ctx->lists_event_set) cudaStreamWaitEvent(s, ctx->ev_lists, 0);
+}
+
 }  // namespace
 
 extern "C" {
@@ -327,6 +344,9 @@ void rgx_destroy(rgx_ctx* ctx) {
     if (ctx->tape_used_host) cudaFreeHost(ctx->tape_used_host);
     if (ctx->hz_hist_host) cudaFreeHost(ctx->hz_hist_host);
     if (ctx->hz_scalars_host) cudaFreeHost(ctx->hz_scalars_host);
+    if (ctx->side) cudaStreamDestroy(ctx->side);
+    if (ctx->ev_main) cudaEventDestroy(ctx->ev_main);
+    if (ctx->ev_lists) cudaEventDestroy(ctx->ev_lists);
     for (auto* v : {&ctx->timed, &ctx->spare})
         for (auto& t : *v) { cudaEventDestroy(t.a); cudaEventDestroy(t.b); }
     delete ctx;
@@ -348,6 +368,8 @@ int rgx_build(rgx_ctx* ctx, const rgx_scene* scene, float sigma_threshold, int m
     const int n = scene->n;
     const int n_pad = ((n + kFan - 1) / kFan) * kFan;
     Levels lv = plan_levels(n > 0 ? n : 1);
+    join_side(ctx, s);
+    ctx->hint_set = false;
     if ((rc = ensure_workspace(ctx, n_pad > 0 ? n_pad : kFan, lv.total))) return rc;
     ctx->built = false;
     ctx->build_id++;
@@ -405,10 +427,19 @@ static bool lists_cached(const rgx_ctx* ctx, const rgx_camera* cam, const rgx_ma
 
 #define RGB_(p, cnt) if ((e = regrow(ctx, ctx->p, (cnt))) != cudaSuccess) return cuda_fail(ctx, e, "tile-list workspace " #p)
 
-// All (tile, Gaussian) pairs of the view, unsorted, in ctx->bin_keys_in / bin_vals_in; fills `b` for the calls
-// that follow.  Includes the view's one host round trip (the number of pairs).
-static int emit_pairs(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, cudaStream_t s, BinLaunch& b, int& total,
-                      int& ntiles) {
+static cudaError_t grow_pairs(rgx_ctx* ctx, size_t pairs) {
+    size_t c = pairs + pairs / 4 + 1024;
+    cudaError_t err;
+    if ((err = regrow(ctx, ctx->bin_keys_in, c)) != cudaSuccess || (err = regrow(ctx, ctx->bin_keys_out, c)) != cudaSuccess ||
+        (err = regrow(ctx, ctx->bin_vals_in, c)) != cudaSuccess || (err = regrow(ctx, ctx->bin_vals_out, c)) != cudaSuccess)
+        return err;
+    ctx->bin_pair_cap = c;
+    return cudaSuccess;
+}
+
+// Emission of a view's (tile, Gaussian) pairs, unsorted, into ctx->bin_keys_in / bin_vals_in, in three steps so that
+// a caller can put other launches between the second and the third: workspace and launch parameters ...
+static int emit_setup(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, BinLaunch& b, int& ntiles) {
     cudaError_t e = cudaSuccess;
     const int tiles_x = (cam->width + kBinTile - 1) / kBinTile;
     if (tiles_x > 65535) return fail(ctx, RGX_E_TOO_LARGE, "image wider than 65535 tiles");
@@ -432,17 +463,8 @@ static int emit_pairs(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, c
         RGB_(tile_dir, c); RGB_(tile_iota, c); RGB_(tile_cnt_sorted, c); RGB_(tile_order, c); RGB_(tile_unrecorded, c);
         ctx->bin_tiles_cap = (int)c;
     }
-    auto grow_pairs = [&](size_t pairs) -> cudaError_t {
-        size_t c = pairs + pairs / 4 + 1024;
-        cudaError_t err;
-        if ((err = regrow(ctx, ctx->bin_keys_in, c)) != cudaSuccess || (err = regrow(ctx, ctx->bin_keys_out, c)) != cudaSuccess ||
-            (err = regrow(ctx, ctx->bin_vals_in, c)) != cudaSuccess || (err = regrow(ctx, ctx->bin_vals_out, c)) != cudaSuccess)
-            return err;
-        ctx->bin_pair_cap = c;
-        return cudaSuccess;
-    };
     // first view of a context: room for eight tiles per Gaussian; a view that needs more runs the emission twice
-    if (ctx->bin_pair_cap == 0 && (e = grow_pairs((size_t)ctx->n_pad * 8)) != cudaSuccess)
+    if (ctx->bin_pair_cap == 0 && (e = grow_pairs(ctx, (size_t)ctx->n_pad * 8)) != cudaSuccess)
         return cuda_fail(ctx, e, "tile-list workspace pairs");
     b = BinLaunch{};
     b.n = ctx->n; b.n_pad = ctx->n_pad;
@@ -455,21 +477,41 @@ static int emit_pairs(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, c
     b.tiles_x = tiles_x; b.tiles_y = tiles_y; b.ty_first = ty_first;
     b.total_dev = ctx->bin_total_dev;
     b.big_slot = ctx->big_slot; b.big_rect = ctx->big_rect; b.big_grid = ctx->sm_count * 4;
-    unsigned long long total64 = 0;
-    for (int attempt = 0; attempt < 2; ++attempt) {
-        b.keys_in = ctx->bin_keys_in; b.vals_in = ctx->bin_vals_in; b.pair_cap = ctx->bin_pair_cap;
-        if ((e = launch_bin_emit(b, s)) != cudaSuccess) return cuda_fail(ctx, e, "tile-list pairs");
-        // the one host round trip of a view: the sort needs the number of pairs
-        if ((e = cudaMemcpyAsync(ctx->bin_total_host, ctx->bin_total_dev, sizeof(unsigned long long), cudaMemcpyDeviceToHost, s)) != cudaSuccess ||
-            (e = cudaStreamSynchronize(s)) != cudaSuccess)
-            return cuda_fail(ctx, e, "tile-list pair count read-back");
-        total64 = ctx->bin_total_host[0];
-        if (total64 > (1ull << 30)) return fail(ctx, RGX_E_TOO_LARGE, "more than 2^30 (tile, Gaussian) pairs in this view");
-        if (total64 <= ctx->bin_pair_cap) break;
-        if ((e = grow_pairs((size_t)total64)) != cudaSuccess) return cuda_fail(ctx, e, "tile-list workspace pairs");
-    }
-    total = (int)total64;
     return RGX_OK;
+}
+
+// ... the kernels and the copy of the pair count to the host, enqueued ...
+static int emit_launch(rgx_ctx* ctx, BinLaunch& b, cudaStream_t s) {
+    cudaError_t e;
+    b.keys_in = ctx->bin_keys_in; b.vals_in = ctx->bin_vals_in; b.pair_cap = ctx->bin_pair_cap;
+    if ((e = launch_bin_emit(b, s)) != cudaSuccess) return cuda_fail(ctx, e, "tile-list pairs");
+    if ((e = cudaMemcpyAsync(ctx->bin_total_host, ctx->bin_total_dev, sizeof(unsigned long long), cudaMemcpyDeviceToHost, s)) != cudaSuccess)
+        return cuda_fail(ctx, e, "tile-list pair count read-back");
+    return RGX_OK;
+}
+
+// ... and the view's one host round trip: the sort needs the number of pairs.  A view whose pairs did not fit is
+// emitted again into larger arrays.
+static int emit_finish(rgx_ctx* ctx, BinLaunch& b, cudaStream_t s, int& total) {
+    cudaError_t e;
+    for (int attempt = 0;; ++attempt) {
+        if ((e = cudaStreamSynchronize(s)) != cudaSuccess) return cuda_fail(ctx, e, "tile-list pair count read-back");
+        const unsigned long long total64 = ctx->bin_total_host[0];
+        if (total64 > (1ull << 30)) return fail(ctx, RGX_E_TOO_LARGE, "more than 2^30 (tile, Gaussian) pairs in this view");
+        total = (int)total64;
+        if (total64 <= ctx->bin_pair_cap) return RGX_OK;
+        if (attempt > 0) return fail(ctx, RGX_E_CUDA, "tile-list pairs did not fit twice");
+        if ((e = grow_pairs(ctx, (size_t)total64)) != cudaSuccess) return cuda_fail(ctx, e, "tile-list workspace pairs");
+        int rc = emit_launch(ctx, b, s);
+        if (rc) return rc;
+    }
+}
+
+static int emit_pairs(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, cudaStream_t s, BinLaunch& b, int& total,
+                      int& ntiles) {
+    int rc = emit_setup(ctx, cam, m, b, ntiles);
+    if (rc || (rc = emit_launch(ctx, b, s))) return rc;
+    return emit_finish(ctx, b, s, total);
 }
 
 // Sorts `count` pairs (keys, vals) into the per-tile lists and points ctx->lists at them.
@@ -523,6 +565,65 @@ static int ensure_lists(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m,
     if ((rc = fill_lists(ctx, b, ctx->bin_keys_in, ctx->bin_vals_in, total, ntiles, s))) return rc;
     lists_now_valid(ctx, cam, m, total);
     return RGX_OK;
+}
+
+// Lists of the announced view, made on the context's own stream while the stream of the caller replays a
+// recording (which reads no lists).  begin: after the last launch on `s` that reads the current lists;
+// end: after the caller has enqueued the rest of its work on `s`.  A view that would need a larger workspace for
+// its tiles is left to the forward that renders it, and so is one whose lists fail to be made.
+struct ListsAhead {
+    bool active = false;
+    BinLaunch b;
+    int ntiles = 0;
+};
+
+static void lists_ahead_begin(rgx_ctx* ctx, cudaStream_t s, ListsAhead& a) {
+    if (!ctx->hint_set) return;
+    ctx->hint_set = false;
+    const rgx_camera* cam = &ctx->hint_cam;
+    const rgx_march* m = &ctx->hint_march;
+    if ((m->flags & (RGX_FLAG_BRUTE_FORCE | RGX_FLAG_PER_RAY_SEARCH)) || ctx->n == 0 || m->row_end <= m->row_begin) return;
+    if (lists_cached(ctx, cam, m)) return;
+    const int tiles_x = (cam->width + kBinTile - 1) / kBinTile;
+    const int ntiles = tiles_x * ((m->row_end - 1) / kBinTile - m->row_begin / kBinTile + 1);
+    if (!ctx->bin_total_dev || ctx->bin_pair_cap == 0 || ctx->n_pad > ctx->big_cap || ntiles + 1 > ctx->bin_tiles_cap) return;
+    if (!ctx->side) {
+        int lo = 0, hi = 0;
+        cudaDeviceGetStreamPriorityRange(&lo, &hi);
+        if (cudaStreamCreateWithPriority(&ctx->side, cudaStreamNonBlocking, hi) != cudaSuccess ||
+            cudaEventCreateWithFlags(&ctx->ev_main, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&ctx->ev_lists, cudaEventDisableTiming) != cudaSuccess) {
+            (void)cudaGetLastError();
+            if (ctx->side) cudaStreamDestroy(ctx->side);
+            if (ctx->ev_main) cudaEventDestroy(ctx->ev_main);
+            if (ctx->ev_lists) cudaEventDestroy(ctx->ev_lists);
+            ctx->side = nullptr; ctx->ev_main = nullptr; ctx->ev_lists = nullptr;
+            return;
+        }
+    }
+    if (cudaEventRecord(ctx->ev_main, s) != cudaSuccess || cudaStreamWaitEvent(ctx->side, ctx->ev_main, 0) != cudaSuccess) return;
+    ctx->lists_valid = false;                      // from here on the list arrays belong to the announced view
+    if (emit_setup(ctx, cam, m, a.b, a.ntiles) || emit_launch(ctx, a.b, ctx->side)) {
+        cudaEventRecord(ctx->ev_lists, ctx->side);
+        ctx->lists_event_set = true;
+        return;
+    }
+    a.active = true;
+}
+
+static void lists_ahead_end(rgx_ctx* ctx, ListsAhead& a) {
+    if (!a.active) return;
+    int total = 0;
+    {
+        ScopedTimer timer(ctx, ctx->side, 2);
+        if (emit_finish(ctx, a.b, ctx->side, total) == RGX_OK &&
+            fill_lists(ctx, a.b, ctx->bin_keys_in, ctx->bin_vals_in, total, a.ntiles, ctx->side) == RGX_OK) {
+            lists_now_valid(ctx, &ctx->hint_cam, &ctx->hint_march, total);
+            ctx->prefetched++;
+        }
+    }
+    cudaEventRecord(ctx->ev_lists, ctx->side);
+    ctx->lists_event_set = true;
 }
 
 // Forward-only march of a view with many more (tile, Gaussian) pairs than its rays will look at: the lists
@@ -655,6 +756,7 @@ static int forward_impl(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* 
     if (!rgb && !frame) return fail(ctx, RGX_E_INVALID, "colour output is null");
     cudaSetDevice(ctx->device);
     cudaStream_t s = (cudaStream_t)stream;
+    join_side(ctx, s);
     if ((rc = run_colors(ctx, scene, cam->eye, s))) return rc;
     L.rgb = rgb; L.alpha = alpha; L.depth = depth; L.frame = frame;
     if (!(march->flags & (RGX_FLAG_BRUTE_FORCE | RGX_FLAG_PER_RAY_SEARCH))) {
@@ -685,6 +787,11 @@ static int forward_impl(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* 
             if ((e = regrow(ctx, ctx->ray_head, (size_t)rays)) != cudaSuccess) return cuda_fail(ctx, e, "tape");
             ctx->ray_head_cap = rays;
         }
+        const int ntiles = L.lists.tiles_x * L.lists.tiles_y;
+        if (ntiles > ctx->tape_order_cap) {
+            if ((e = regrow(ctx, ctx->tape_tile_order, (size_t)ntiles + 64)) != cudaSuccess) return cuda_fail(ctx, e, "tape");
+            ctx->tape_order_cap = ntiles + 64;
+        }
         // room: 1024 ints per ray to begin with; what the previous recording asked for and half as much again when
         // that came close to the end (the counter keeps counting past the end), within half of the free memory
         long long want = rows_rays * 1024 + 4096;
@@ -709,7 +816,8 @@ static int forward_impl(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* 
             }
         }
         if ((e = cudaMemsetAsync(ctx->tape_used, 0, 4 * sizeof(unsigned long long), s)) != cudaSuccess ||
-            (e = cudaMemsetAsync(ctx->tile_unrecorded, 0, sizeof(int) * (size_t)(L.lists.tiles_x * L.lists.tiles_y), s)) != cudaSuccess)
+            (e = cudaMemsetAsync(ctx->tile_unrecorded, 0, sizeof(int) * (size_t)ntiles, s)) != cudaSuccess ||
+            (e = cudaMemcpyAsync(ctx->tape_tile_order, L.lists.tile_order, sizeof(int) * (size_t)ntiles, cudaMemcpyDeviceToDevice, s)) != cudaSuccess)
             return cuda_fail(ctx, e, "tape");
         if (ctx->tape) {
             L.tape = ctx->tape; L.tape_used = ctx->tape_used; L.tape_cap = ctx->tape_cap; L.ray_head = ctx->ray_head;
@@ -761,6 +869,7 @@ int rgx_backward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, co
     if (scene->n == 0) return RGX_OK;
     cudaSetDevice(ctx->device);
     cudaStream_t s = (cudaStream_t)stream;
+    join_side(ctx, s);
     // a backward that replays the recording of this very view finds the forward's per-view colours still in place
     const bool replays = ctx->tape_valid && ctx->tape_build_id == ctx->build_id &&
                          ctx->tape_row_begin == march->row_begin && ctx->tape_row_end == march->row_end &&
@@ -778,17 +887,25 @@ int rgx_backward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, co
         std::memcmp(&ctx->tape_cam, cam, sizeof(rgx_camera)) == 0) {
         L.tape = ctx->tape; L.tape_used = ctx->tape_used; L.tape_cap = ctx->tape_cap; L.ray_head = ctx->ray_head;
         L.tile_unrecorded = ctx->tile_unrecorded;
+        L.replay_order = ctx->tape_tile_order;
         // Slabs with few hits are worked off several at a time.  The statistics are those of the latest recording
         // whose read-back has arrived (this view's, or an earlier one's: a hint, either kernel gives the same result).
         const unsigned long long slabs = ctx->tape_used_host[1], nhits = ctx->tape_used_host[2];
         L.replay_batched = slabs == 0 || nhits < 24ull * slabs;
     }
     L.rgb_in = rgb; L.dl_drgb = dL_drgb; L.grad_rows = ctx->grad_rows; L.grad_copies = ctx->grad_copies;
+    // rays without a recording first: theirs is the last launch that reads the view's lists, so the lists of an
+    // announced next view can be made beside the replay and the gradient assembly
+    ListsAhead ahead;
     {
         ScopedTimer timer(ctx, s, 1);
-        e = launch_march_backward(L, s);
+        e = launch_march_backward_search(L, s);
+        if (e == cudaSuccess) {
+            lists_ahead_begin(ctx, s, ahead);
+            e = launch_march_backward_replay(L, s);
+        }
     }
-    if (e != cudaSuccess) return cuda_fail(ctx, e, "backward march");
+    if (e != cudaSuccess) { lists_ahead_end(ctx, ahead); return cuda_fail(ctx, e, "backward march"); }
     FinalizeLaunch f{};
     f.sc = *scene;
     f.gr = *grads;
@@ -798,8 +915,23 @@ int rgx_backward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, co
     f.quat = ctx->quat; f.sdens = ctx->sdens; f.hk = ctx->hk;
     f.flags = march->flags;
     e = launch_finalize(f, s);
+    lists_ahead_end(ctx, ahead);
     return e == cudaSuccess ? RGX_OK : cuda_fail(ctx, e, "gradient finalise");
 }
+
+int rgx_hint_next_view(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* march) {
+    if (!ctx) return RGX_E_INVALID;
+    ctx->hint_set = false;
+    if (!cam && !march) return RGX_OK;
+    int rc = check_march(ctx, cam, march);
+    if (rc) return rc;
+    ctx->hint_cam = *cam;
+    ctx->hint_march = *march;
+    ctx->hint_set = true;
+    return RGX_OK;
+}
+
+int rgx_lists_made_ahead(const rgx_ctx* ctx) { return ctx ? ctx->prefetched : 0; }
 
 int rgx_gaussian_colors(rgx_ctx* ctx, const rgx_scene* scene, const float eye[3], float* rgb_out, rgx_stream stream) {
     int rc = check_scene(ctx, scene, true);

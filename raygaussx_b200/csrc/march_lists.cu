@@ -546,7 +546,7 @@ template <int NB>
 __global__ void __launch_bounds__(kThreads) march_backward_replay_kernel(const __grid_constant__ MarchLaunch L) {
     __shared__ ReplayShared<NB> sh;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int tile = L.lists.tile_order ? __ldg(&L.lists.tile_order[blockIdx.x]) : blockIdx.x;
+    const int tile = L.replay_order ? __ldg(&L.replay_order[blockIdx.x]) : blockIdx.x;
     const int tile_x = tile % L.lists.tiles_x, tile_y = tile / L.lists.tiles_x;
     const float eps = L.m.transmittance_eps;
     const SceneBox box = *L.box;
@@ -717,15 +717,20 @@ cudaError_t launch_march_forward(const MarchLaunch& m, cudaStream_t s) {
     return cudaGetLastError();
 }
 
-cudaError_t launch_march_backward(const MarchLaunch& m, cudaStream_t s) {
+cudaError_t launch_march_backward_search(const MarchLaunch& m, cudaStream_t s) {
     if (!use_lists(m)) return launch_march_backward_per_ray(m, s);
     const int grid = m.lists.tiles_x * m.lists.tiles_y;
     if (grid <= 0) return cudaSuccess;
-    if (m.tape) {                                                                  // recorded rays
-        if (m.replay_batched) march_backward_replay_kernel<kBatch><<<grid, kThreads, 0, s>>>(m);
-        else march_backward_replay_kernel<1><<<grid, kThreads, 0, s>>>(m);
-    }
-    march_backward_lists_kernel<<<grid, kThreads, 0, s>>>(m);                      // the others (a quick no-op per recorded ray)
+    march_backward_lists_kernel<<<grid, kThreads, 0, s>>>(m);   // a CTA whose tile was recorded completely returns at once
+    return cudaGetLastError();
+}
+
+cudaError_t launch_march_backward_replay(const MarchLaunch& m, cudaStream_t s) {
+    if (!use_lists(m) || !m.tape) return cudaSuccess;
+    const int grid = m.lists.tiles_x * m.lists.tiles_y;
+    if (grid <= 0) return cudaSuccess;
+    if (m.replay_batched) march_backward_replay_kernel<kBatch><<<grid, kThreads, 0, s>>>(m);
+    else march_backward_replay_kernel<1><<<grid, kThreads, 0, s>>>(m);
     return cudaGetLastError();
 }
 

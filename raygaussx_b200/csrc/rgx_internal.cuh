@@ -114,6 +114,7 @@ struct MarchLaunch {
     long long tape_cap;
     long long* ray_head;
     int* tile_unrecorded;   // per tile (of the lists): set by the forward when a ray of the tile got ray_head = -2
+    const int* replay_order;  // backward replay: tiles in the order of the recording forward's CTAs (own copy: the lists may be remade meanwhile)
     // two-depth forward (march_lists.cu, HZ variant): 0 = off, 1 = first phase (lists up to `horizon`), 2 = second
     int hz_phase;
     float horizon;
@@ -180,6 +181,9 @@ float bin_hist_bucket_end(int bucket);
 cudaError_t launch_bin_select(const BinLaunch& b, int total, int mode, unsigned int cut, const int* tile_flag, uint64_t* out_k,
                               uint32_t* out_v, unsigned long long* counter, int* tile_more, cudaStream_t s);
 cudaError_t launch_march_forward(const MarchLaunch& m, cudaStream_t s);
-cudaError_t launch_march_backward(const MarchLaunch& m, cudaStream_t s);
+// The backward in two launches: rays without a recording (searches the lists or the hierarchy), then the replay of
+// the recording, which reads neither lists nor hierarchy.
+cudaError_t launch_march_backward_search(const MarchLaunch& m, cudaStream_t s);
+cudaError_t launch_march_backward_replay(const MarchLaunch& m, cudaStream_t s);
 
 }  // namespace rgx

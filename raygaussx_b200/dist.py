@@ -99,21 +99,24 @@ def l1_loss_gradient(rgb: torch.Tensor, target: torch.Tensor, n_rays_total: int,
 
 
 def accumulation_step(renderer, tensors: Sequence[torch.Tensor], cameras, targets, march_of, grads: GradBuffer,
-                      rank: int = 0, world: int = 1, rebuild: bool = True, group=None, loss_out=None):
+                      rank: int = 0, world: int = 1, rebuild: bool = True, group=None, loss_out=None,
+                      lists_ahead: bool = True):
     """One gradient-accumulation step over ``cameras`` (rgx camera structs) with
     per-view device targets ``targets[v]`` of shape ``[R, 3]``.
 
     ``march_of(cam, rows, flags)`` returns the march struct for a camera and row
     range.  On return ``grads`` holds the gradient of ``mean_v L1_v`` summed over
     all ranks.  Kernels launched: the acceleration-structure build (once), then per
-    row block a forward, an elementwise loss gradient, and an accumulating backward.
+    row block a forward, an elementwise loss gradient, and an accumulating backward
+    (which, with ``lists_ahead``, also makes the next block's tile lists on a second stream).
     """
     from . import _lib
     if rebuild:
         renderer.build(*tensors[:4])
     grads.zero_()
     n_views = len(cameras)
-    for blk in shard_rows(n_views, cameras[0].height, rank, world):
+    blocks = list(shard_rows(n_views, cameras[0].height, rank, world))
+    for i, blk in enumerate(blocks):
         cam = cameras[blk.view]
         rows = (blk.row_begin, blk.row_end)
         r_total = cam.width * cam.height
@@ -124,6 +127,10 @@ def accumulation_step(renderer, tensors: Sequence[torch.Tensor], cameras, target
         dl[lo:hi] = l1_loss_gradient(seg, targets[blk.view][lo:hi], r_total, n_views)
         if loss_out is not None:
             loss_out += (seg - targets[blk.view][lo:hi]).abs().sum() / float(3 * r_total * n_views)
+        if lists_ahead and i + 1 < len(blocks):
+            nxt = blocks[i + 1]          # its tile lists are made beside this block's backward
+            ncam = cameras[nxt.view]
+            renderer.hint_next_view(ncam, march_of(ncam, (nxt.row_begin, nxt.row_end), _lib.FLAG_SAVE_HITS))
         renderer.backward(*tensors, cam, march_of(cam, rows, _lib.FLAG_ACCUMULATE), rgb, dl, grads.tensors())
     grads.all_reduce(group)
     return grads

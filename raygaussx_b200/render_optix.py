@@ -42,12 +42,15 @@ class RenderOptixSettings:
     """Positional signature of render_optix.py:68-71.  ``transmittance_eps``, ``exact_sh_grad`` and ``rows`` are
     keyword-only additions with the reference's behaviour as default.  ``rows = (first, last + 1)`` restricts
     the render to those image rows (of the supersampled image): the other rays of the returned image are left
-    unwritten and take no part in the backward -- how a view is shared between ranks."""
+    unwritten and take no part in the backward -- how a view is shared between ranks.  ``next_viewpoint_cam``
+    (with ``next_rows``) announces the view that will be rendered next with the same, unchanged Gaussians and
+    ``reuse_acceleration_structure`` set: the backward of this view then prepares it beside its own kernels."""
 
     def __init__(self, context, update, gas, program_grps_fwd, pipeline_fwd, program_grps_bwd, pipeline_bwd, dt_step,
                  dynamic_sampling, viewpoint_cam, max_prim_slice, num_sph_gauss, iteration=0, jitter=False,
                  rnd_sample=0, supersampling=(1, 1), white_background=False, hit_prim_idx=None, *,
-                 transmittance_eps=TRANSMITTANCE_EPSILON, exact_sh_grad=False, rows=None):
+                 transmittance_eps=TRANSMITTANCE_EPSILON, exact_sh_grad=False, rows=None,
+                 next_viewpoint_cam=None, next_rows=None, reuse_acceleration_structure=False):
         self.context = context
         self.update = update
         self.gas = gas
@@ -69,6 +72,9 @@ class RenderOptixSettings:
         self.transmittance_eps = transmittance_eps
         self.exact_sh_grad = exact_sh_grad
         self.rows = rows
+        self.next_viewpoint_cam = next_viewpoint_cam
+        self.next_rows = next_rows
+        self.reuse_acceleration_structure = reuse_acceleration_structure   # the caller vouches: same geometry as the last build
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -216,6 +222,15 @@ class Renderer:
         _lib.check(self._ctx, self._lib.rgx_backward(self._ctx, C.byref(sc), C.byref(cam), C.byref(march), _ptr(rgb),
                                                      _ptr(dl_drgb), C.byref(g), self._stream()))
 
+    def hint_next_view(self, cam: Optional[_Camera], march: Optional[_March]):
+        """Announce the view of the next forward: the next :meth:`backward` then makes its tile lists beside its own
+        kernels.  ``None, None`` withdraws the announcement."""
+        _lib.check(self._ctx, self._lib.rgx_hint_next_view(self._ctx, C.byref(cam) if cam is not None else None,
+                                                           C.byref(march) if march is not None else None))
+
+    def lists_made_ahead(self) -> int:
+        return int(self._lib.rgx_lists_made_ahead(self._ctx))
+
     def gaussian_colors(self, positions, color_features, sg_features, sharpness, lobe_axis, eye):
         n = positions.shape[0]
         out = torch.empty(n, 3, device=self.device, dtype=torch.float32)
@@ -312,6 +327,10 @@ class RenderOptixFunction(torch.autograd.Function):
         flags = _lib.FLAG_EXACT_SH_GRAD if getattr(settings, "exact_sh_grad", False) else 0
         march = _settings_march(settings, cam, flags=flags, rows=getattr(settings, "rows", None))
         grads = [torch.empty_like(t) for t in tensors]
+        nxt = getattr(settings, "next_viewpoint_cam", None)      # same Gaussians, next view of an accumulation step
+        if nxt is not None:
+            ncam = camera_struct(nxt, settings.supersampling)
+            r.hint_next_view(ncam, _settings_march(settings, ncam, rows=getattr(settings, "next_rows", None)))
         r.backward(*tensors, cam, march, rgb, dl, tuple(grads))
         g_pos, g_scale, g_quat, g_dens, g_sh, g_sg, g_sharp, g_axis = grads
         if settings.num_sph_gauss == 0 or tensors[6].numel() == 0:       # render_optix.py:190-197

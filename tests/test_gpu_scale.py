@@ -214,3 +214,80 @@ def test_two_depth_forward_is_bit_identical(kind, budget):
     finally:
         two_depth(r, 48, 16)
         del r
+
+
+@pytest.mark.parametrize("kind", ["tiny", "unbounded"])
+def test_lists_made_ahead_change_nothing(kind):
+    """Tile lists of an announced view, made on the context's own stream beside the backward of the view before:
+    the announced forward gives the image it gives without the announcement bit for bit, the accumulated
+    gradients agree to the order of the atomic additions, and a wrong announcement is harmless."""
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device: there is no CPU path")
+    from raygaussx_b200 import dist as rdist
+    from raygaussx_b200 import render_optix as ro
+    dev = torch.device("cuda")
+    if kind == "unbounded":
+        sc = scenes.unbounded_scene(n=200_000, n_cameras=3, width=314, height=207)
+    else:
+        sc = scenes.tiny_scene(n=512, width=40, height=24, log_scale_mean=-2.5, dynamic_sampling=True, dt_step=0.005)
+    tens = [t.to(dev).contiguous() for t in sc.tensors()]
+    r = ro.Renderer(dev)
+    cams = []
+    for cam in sc.cameras[:3]:
+        cam.to(dev)
+        cams.append(ro.camera_struct(cam))
+    if len(cams) == 1:                       # one camera: the blocks of a step are then row ranges of it
+        views, world = [cams[0]] * 3, 2      # rank 0 of 2: views 0 and half of view 1
+    else:
+        views, world = cams, 1
+    rays = views[0].width * views[0].height
+    g = torch.Generator(device="cpu").manual_seed(5)
+    targets = [torch.rand(rays, 3, generator=g).to(dev) for _ in views]
+    march_of = lambda cam, rows, flags: march(ro, sc, cam, flags=flags, rows=rows)
+    n = tens[0].shape[0]
+    plain, ahead = rdist.GradBuffer(n, 16, dev), rdist.GradBuffer(n, 16, dev)
+    blocks = rdist.shard_rows(len(views), views[0].height, 0, world)
+    assert len(blocks) >= 2
+    rdist.accumulation_step(r, tens, views, targets, march_of, plain, rank=0, world=world, lists_ahead=False)
+    assert r.lists_made_ahead() == 0
+    rdist.accumulation_step(r, tens, views, targets, march_of, ahead, rank=0, world=world, lists_ahead=True)
+    torch.cuda.synchronize()
+    assert r.lists_made_ahead() == len(blocks) - 1
+    for name in rdist.GRAD_FIELDS:
+        a, b = plain.views[name], ahead.views[name]
+        assert torch.isfinite(b).all() and a.abs().sum() > 0
+        assert ((a - b).abs().max() / a.abs().max()).item() < 1e-4, name
+
+    # forward of the announced view: bit-identical; recording and replay as without the announcement
+    first, second = blocks[0], blocks[1]
+    c0, c1 = views[first.view], views[second.view]
+    m0 = march_of(c0, (first.row_begin, first.row_end), _lib.FLAG_SAVE_HITS)
+    m1 = march_of(c1, (second.row_begin, second.row_end), _lib.FLAG_SAVE_HITS)
+    r.build(*tens[:4])
+    want = torch.zeros(rays, 3, device=dev)
+    r.forward(*tens, c1, m1, out=want)
+    r.build(*tens[:4])
+    rgb0 = torch.zeros(rays, 3, device=dev)
+    r.forward(*tens, c0, m0, out=rgb0)
+    dl = torch.sign(rgb0 - targets[0]) / (3 * rays)
+    grads = [torch.zeros_like(t) for t in tens]
+    made = r.lists_made_ahead()
+    r.hint_next_view(c1, m1)
+    r.backward(*tens, c0, m0, rgb0, dl, tuple(grads))
+    assert r.lists_made_ahead() == made + 1
+    got = torch.zeros(rays, 3, device=dev)
+    r.forward(*tens, c1, m1, out=got)
+    assert torch.equal(got, want)
+
+    # an announcement that does not come true: the next forward makes its own lists
+    r.hint_next_view(c1, m1)
+    r.backward(*tens, c1, m1, got, dl, tuple(grads))      # (c1's lists are current: nothing to make)
+    assert r.lists_made_ahead() == made + 1
+    r.hint_next_view(c1, m1)
+    r.forward(*tens, c0, m0, out=rgb0)
+    r.backward(*tens, c0, m0, rgb0, dl, tuple(grads))      # makes c1's lists ...
+    assert r.lists_made_ahead() == made + 2
+    other = torch.zeros(rays, 3, device=dev)
+    r.forward(*tens, c0, m0, out=other)                    # ... but c0 is rendered again
+    assert torch.equal(other, rgb0)
+    r.hint_next_view(None, None)
