@@ -141,6 +141,11 @@ __global__ void __launch_bounds__(128) finalize_kernel(FinalizeLaunch f) {
         r2.x += a2.x; r2.y += a2.y; r2.z += a2.z; r2.w += a2.w;
         r3.x += a3.x;
     }
+    // A Gaussian no ray met (most of a large scene, in any one view) has nothing to add: the gradient tensors were
+    // cleared by the launcher unless they accumulate, and are written for the others only.
+    if (r0.x == 0.f && r0.y == 0.f && r0.z == 0.f && r0.w == 0.f && r1.x == 0.f && r1.y == 0.f && r1.z == 0.f &&
+        r1.w == 0.f && r2.x == 0.f && r2.y == 0.f && r2.z == 0.f && r2.w == 0.f && r3.x == 0.f)
+        return;
     // The march left the moments of the loss gradient in the Gaussian's whitened frame y = M (x - p),
     // M = S^-1 R^T / k (rows as in emit_global).  With N = S^-1 R^T = k M:
     //   dL/dp     = N^T k mu                      = k sum_a col_a mu_a / s_a
@@ -179,7 +184,7 @@ __global__ void __launch_bounds__(128) finalize_kernel(FinalizeLaunch f) {
     const float dquat[4] = {dq.x, dq.y, dq.z, dq.w};
     const bool touched = r0.x != 0.f || r0.y != 0.f || r0.z != 0.f || r0.w != 0.f || r1.x != 0.f || r1.y != 0.f ||
                          r1.z != 0.f || r1.w != 0.f || r2.x != 0.f;
-    if (!touched) {          // a Gaussian no ray met: exact zeros even where hk, s or q are degenerate
+    if (!touched) {          // only colour or density gradients arrived: exact zeros even where hk, s or q are degenerate
         dpos[0] = dpos[1] = dpos[2] = 0.f;
         dscale[0] = dscale[1] = dscale[2] = 0.f;
     }
@@ -193,14 +198,7 @@ __global__ void __launch_bounds__(128) finalize_kernel(FinalizeLaunch f) {
     put(f.gr.densities + i, ddens, acc);
 
     const bool zero = drgb[0] == 0.f && drgb[1] == 0.f && drgb[2] == 0.f;   // utils/sh_utils.cu:226-228
-    if (zero) {
-        if (!acc) {
-            for (int k = 0; k < 3 * K; ++k) f.gr.color_features[(size_t)i * 3 * K + k] = 0.f;
-            for (int k = 0; k < 3 * G; ++k) f.gr.sg_features[(size_t)i * 3 * G + k] = 0.f;
-            for (int k = 0; k < G; ++k) f.gr.sharpness[(size_t)i * G + k] = 0.f;
-            for (int k = 0; k < 3 * G; ++k) f.gr.lobe_axis[(size_t)i * 3 * G + k] = 0.f;
-        }
-    } else {
+    if (!zero) {                // (else the colour gradients stay as cleared, or as accumulated so far)
         float3 v = make_float3(f.sc.positions[3 * i] - f.eye[0], f.sc.positions[3 * i + 1] - f.eye[1],
                                f.sc.positions[3 * i + 2] - f.eye[2]);
         float sum2 = dot3(v, v);
@@ -273,6 +271,18 @@ cudaError_t launch_colors(const ColorLaunch& c, cudaStream_t s) {
 
 cudaError_t launch_finalize(const FinalizeLaunch& f, cudaStream_t s) {
     if (f.sc.n == 0) return cudaSuccess;
+    if (!(f.flags & RGX_FLAG_ACCUMULATE)) {       // the kernel writes the rows of the Gaussians some ray met, nothing else
+        const size_t n = (size_t)f.sc.n, K = (size_t)f.sc.sh_coeffs, G = (size_t)f.sc.num_lobes;
+        struct { float* p; size_t count; } clear[] = {
+            {f.gr.positions, 3 * n}, {f.gr.scales, 3 * n}, {f.gr.quaternions, 4 * n}, {f.gr.densities, n},
+            {f.gr.color_features, 3 * K * n}, {f.gr.sg_features, 3 * G * n}, {f.gr.sharpness, G * n},
+            {f.gr.lobe_axis, 3 * G * n}};
+        for (auto& c : clear) {
+            if (!c.p || c.count == 0) continue;
+            cudaError_t e = cudaMemsetAsync(c.p, 0, c.count * sizeof(float), s);
+            if (e != cudaSuccess) return e;
+        }
+    }
     finalize_kernel<<<(f.sc.n + 127) / 128, 128, 0, s>>>(f);
     return cudaGetLastError();
 }

@@ -312,7 +312,7 @@ def test_a_failed_allocation_leaves_a_usable_context(ro):
     again, _, _ = r.forward(*tens, cs, march)
     assert torch.equal(want, again)
     # 3. a recording that cannot be allocated is not an error: the forward renders without it, the backward searches
-    fail_in(2)                                            # counter, per-ray heads, then the recording itself
+    fail_in(3)                                            # counter, per-ray heads, tile order, then the recording itself
     rgb, _, _ = r.forward(*tens, cs, ro._settings_march(settings_for(ro, sc, cam), cs, flags=_lib.FLAG_SAVE_HITS))
     fail_in(-1)
     assert torch.equal(rgb, want)
