@@ -332,6 +332,14 @@ def main():
     mufu_fwd = (1.0 * E + 70.0 * Sh) * frac_view
     fp32_peak = 2.0 * 128 * n_sm * sm_max_mhz * 1e6
     mufu_peak = 16.0 * n_sm * sm_max_mhz * 1e6
+    # the same two ceilings measured on this device (register-chain kernels of the library, a few milliseconds)
+    import ctypes as C
+    fma_tf, ex2_g = C.c_float(), C.c_float()
+    issue_src = "derived"
+    if _lib.lib().rgx_measure_peaks(local, C.byref(fma_tf), C.byref(ex2_g)) == 0 and fma_tf.value > 0 and ex2_g.value > 0:
+        fp32_peak_derived, mufu_peak_derived = fp32_peak, mufu_peak
+        fp32_peak, mufu_peak = fma_tf.value * 1e12, ex2_g.value * 1e9
+        issue_src = "measured"
     roofline = {"kernel": "march_forward_lists_kernel<false,true> (forward march, recording for the backward)",
                 "bound": "hbm", "achieved": achieved, "peak": hbm_peak,
                 "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_src, "traffic": traffic,
@@ -343,9 +351,11 @@ def main():
                              "achieved": alg_bwd / (bwd_ms * 1e-3) / 1e9,
                              "frac": alg_bwd / (bwd_ms * 1e-3) / 1e9 / hbm_peak},
                 "fp32_frac": f_fwd / (fwd_ms * 1e-3) / fp32_peak, "mufu_frac": mufu_fwd / (fwd_ms * 1e-3) / mufu_peak,
+                "fp32_peak_tflops": fp32_peak / 1e12, "ex2_peak_gops": mufu_peak / 1e9, "issue_peaks": issue_src,
                 "note": "the march kernels are bound by instruction issue (62-69 % of issue slots used, ncu), not by "
-                        "HBM: fp32_frac and mufu_frac are useful flops and ex2 per second over the derived peaks "
-                        "(2*128*SMs*f, 16*SMs*f)",
+                        "HBM: fp32_frac and mufu_frac are useful flops and ex2 per second over the fp32 FMA and ex2 "
+                        "rates (measured by rgx_measure_peaks; derived 2*128*SMs*f and 16*SMs*f if that failed); "
+                        "the backward's time includes the next view's tile lists made beside it on a second stream",
                 "counters_per_view": {k: cn[k] for k in ("rays", "slabs", "slabs_hit", "closest_queries", "hits",
                                                          "pairs_inside", "overflow_slabs", "prim_tests",
                                                          "candidates")}}

@@ -247,6 +247,12 @@ RGX_API int rgx_read_two_depth(rgx_ctx* ctx, long long out[4]);
  * read, and the number of (tile, Gaussian) pairs of the latest one. */
 RGX_API int rgx_read_binning(rgx_ctx* ctx, float* ms, int* runs, long long* last_pairs);
 
+/* Measured issue-rate peaks of a device (no counterpart in the reference): fp32 FMA throughput in TFLOP/s
+ * (an FMA counted as two operations) and ex2.approx throughput in 10^9 per second, with every SM busy on
+ * independent register chains; a few milliseconds, synchronises.  The ceilings the march kernels (bound by
+ * instruction issue, not by memory) are compared with. */
+RGX_API int rgx_measure_peaks(int device, float* fma_tflops, float* ex2_gops);
+
 /* Forward render without any allocation (no counterpart in the reference, which
  * allocates freely through cupy).  For callers that cannot call cudaMalloc when
  * they need a frame -- a viewer thread beside a trainer whose caching allocator

@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "librgx.so")
-SOURCES = ["api.cu", "build.cu", "color.cu", "march.cu", "march_lists.cu", "binning.cu", "static_forward.cu", "knn.cu"]
+SOURCES = ["api.cu", "build.cu", "color.cu", "march.cu", "march_lists.cu", "binning.cu", "static_forward.cu", "knn.cu", "peaks.cu"]
 HEADERS = ["rgx_internal.cuh", "device_math.cuh", "march_common.cuh", os.path.join("..", "..", "include", "rgx.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-fmad=false",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
