@@ -322,22 +322,36 @@ __device__ __forceinline__ void clip_scene(const SceneBox& b, const Ray& r, floa
 
 // Evaluate `count` staged Gaussians at this lane's sample: sums of sigma*g and of
 // (payload)*g, payload being rgb*sigma in the forward (cuda_train/forward/gaussians_aabb.cu:166-178).
+// Along a ray the whitened squared distance is a parabola in the sample position, q(tau) = q_min +
+// |de|^2 (tau - tau*)^2 about the closest approach tau* (a sum of two non-negative terms: no cancellation), so a
+// staged record is (tau*, (1 - q_min)/|de|^2, -hk |de|^2, -hk q_min) and (payload, sigma): the truncation
+// test q < 1 is d^2 < (1 - q_min)/|de|^2 and the exponent one fused multiply-add of d^2.
 template <bool COUNT>
 __device__ __forceinline__ void eval_forward(const WarpStage& ws, int count, float tau, float& s, float& cr,
                                              float& cg, float& cb, Tally& tl) {
 #pragma unroll 2
     for (int j = 0; j < count; ++j) {
-        float4 A = ws.recA[j], B = ws.recB[j], C = ws.recC[j];
-        float yx = fmaf(tau, B.x, A.x), yy = fmaf(tau, B.y, A.y), yz = fmaf(tau, B.z, A.z);
-        float q = fmaf(yx, yx, fmaf(yy, yy, __fmul_rn(yz, yz)));
-        bool in = q < 1.0f;
-        float e = in ? ex2_approx(__fmul_rn(-A.w, q)) : 0.0f;
-        s = fmaf(B.w, e, s);
+        const float4 A = ws.recA[j], C = ws.recB[j];
+        const float d = __fadd_rn(tau, -A.x);
+        const float d2 = __fmul_rn(d, d);
+        const bool in = d2 < A.y;
+        const float e = in ? ex2_approx(fmaf(A.z, d2, A.w)) : 0.0f;
+        s = fmaf(C.w, e, s);
         cr = fmaf(C.x, e, cr);
         cg = fmaf(C.y, e, cg);
         cb = fmaf(C.z, e, cb);
         if (COUNT) tl.v[C_PAIRS] += __popc(__ballot_sync(kFull, in));
     }
+}
+
+// The record of eval_forward for a hit with whitened ray origin Oe and direction de, sample positions counted
+// from tbuffer; hk is the exponent scale of ex2 (response = ex2(-hk q)).
+__device__ __forceinline__ float4 parabola_record(float3 Oe, float3 de, float tbuffer, float hk) {
+    const float a = dot3(de, de);
+    const float tstar = __fdiv_rn(-dot3(Oe, de), a);
+    const float3 P = make_float3(fmaf(tstar, de.x, Oe.x), fmaf(tstar, de.y, Oe.y), fmaf(tstar, de.z, Oe.z));
+    const float qmin = dot3(P, P);
+    return make_float4(__fadd_rn(tstar, -tbuffer), __fdiv_rn(1.0f - qmin, a), __fmul_rn(-hk, a), __fmul_rn(-hk, qmin));
 }
 
 __device__ __forceinline__ void flush_tally(const MarchLaunch& L, const Tally& tl, int lane) {
@@ -446,12 +460,9 @@ __device__ __forceinline__ int slab_sums(const MarchLaunch& L, const rgx_march& 
                 int* list = *hit_list;
                 if (list && nhit + rank < hit_cap) list[nhit + rank] = j;
             }
-            float4 c = __ldg(&L.g.rgba[j]);
-            ws.recA[slot] = make_float4(fmaf(tbuffer, t.de.x, t.Oe.x), fmaf(tbuffer, t.de.y, t.Oe.y),
-                                        fmaf(tbuffer, t.de.z, t.Oe.z), __ldg(&L.g.hk[j]));
-            ws.recB[slot] = make_float4(t.de.x, t.de.y, t.de.z, c.w);
-            ws.recC[slot] = BWD ? make_float4(fmaf(dl.x, c.x, fmaf(dl.y, c.y, __fmul_rn(dl.z, c.z))), 0.f, 0.f, 0.f)
-                                : make_float4(c.x, c.y, c.z, 0.f);
+            const float4 c = __ldg(&L.g.rgba[j]);       // (rgb sigma, sigma)
+            ws.recA[slot] = parabola_record(t.Oe, t.de, tbuffer, __ldg(&L.g.hk[j]));
+            ws.recB[slot] = BWD ? make_float4(fmaf(dl.x, c.x, fmaf(dl.y, c.y, __fmul_rn(dl.z, c.z))), 0.f, 0.f, c.w) : c;
         }
         if (COUNT) {
             unsigned long long hsh = take ? mix64(((unsigned long long)ray_id << 40) ^

@@ -403,6 +403,8 @@ struct ReplayStage {        // per warp: one group of up to 32 hits
     float4 a[kFan];         // whitened ray point at the reference parameter, hk
     float4 b[kFan];         // whitened direction, tbuffer - reference parameter
     float4 c[kFan];         // chat_i, sigma, first and last sample (as int bits)
+    float4 d[kFan];         // the response along the ray as a parabola about the closest approach (march_common.cuh,
+                            // eval_forward): -hk q_min, -hk |de|^2, (1 - q_min)/|de|^2, tbuffer - closest approach
     int slot[kFan];
     int upto[kFan];         // inclusive prefix of the number of runs
     int slab[kFan];         // which slab of the batch the hit belongs to
@@ -456,7 +458,8 @@ __device__ __forceinline__ void replay_batch(const MarchLaunch& L, const Ray& r,
             const float inv_a = __fdividef(1.0f, dot3(de, de));
             const float tca = __fmul_rn(-dot3(Oe, de), inv_a);
             const float3 P = make_float3(fmaf(tca, de.x, Oe.x), fmaf(tca, de.y, Oe.y), fmaf(tca, de.z, Oe.z));
-            const float hw = __fsqrt_rn(__fmul_rn(fmaxf(1.0f - dot3(P, P), 0.f), inv_a));
+            const float qmin = dot3(P, P);
+            const float hw = __fsqrt_rn(__fmul_rn(fmaxf(1.0f - qmin, 0.f), inv_a));
             // samples (s + 1/2) dt inside it, one more on each side against rounding; the test q < 1 decides
             const float x_lo = fmaf(__fadd_rn(__fadd_rn(tca, -hw), -tbuffer), inv_dt, -0.5f);
             const float x_hi = fmaf(__fadd_rn(__fadd_rn(tca, hw), -tbuffer), inv_dt, -0.5f);
@@ -467,6 +470,9 @@ __device__ __forceinline__ void replay_batch(const MarchLaunch& L, const Ray& r,
             sp.a[lane] = make_float4(fmaf(tcr, de.x, Oe.x), fmaf(tcr, de.y, Oe.y), fmaf(tcr, de.z, Oe.z), hk);
             sp.b[lane] = make_float4(de.x, de.y, de.z, __fadd_rn(tbuffer, -tcr));
             sp.c[lane] = make_float4(ci, c.w, __int_as_float(s_lo), __int_as_float(s_hi));
+            const float a = dot3(de, de);
+            sp.d[lane] = make_float4(__fmul_rn(-hk, qmin), __fmul_rn(-hk, a), __fmul_rn(1.0f - qmin, inv_a),
+                                     __fadd_rn(tbuffer, -tca));
             sp.slot[lane] = j;
             if (!SINGLE) sp.slab[lane] = k;
             nitem = s_hi >= s_lo ? (s_hi - s_lo + kRun) / kRun : 0;
@@ -487,12 +493,11 @@ __device__ __forceinline__ void replay_batch(const MarchLaunch& L, const Ray& r,
             const bool active = i < total;
             int h = 0;
             float sb = 0.f, n0 = 0.f, n1 = 0.f, n2 = 0.f;
-            float4 A = make_float4(0.f, 0.f, 0.f, 0.f), B = A, C = A;
             if (active) {
 #pragma unroll
                 for (int step = 16; step > 0; step >>= 1)
                     if (sp.upto[h + step - 1] <= i) h += step;          // first hit whose runs end after i
-                A = sp.a[h]; B = sp.b[h]; C = sp.c[h];
+                const float4 C = sp.c[h], D = sp.d[h];
                 const int k = SINGLE ? 0 : sp.slab[h];
                 const float dt = SINGLE ? dt1 : bt.dt[k];
                 const float* sbeta = bt.beta[k];
@@ -500,24 +505,26 @@ __device__ __forceinline__ void replay_batch(const MarchLaunch& L, const Ray& r,
                 const int s_hi = __float_as_int(C.w);
                 const int nrun = (s_hi - __float_as_int(C.z) + kRun) / kRun;
                 const int s0 = __float_as_int(C.z) + kRun * (i - (sp.upto[h] - nrun));
+                // sample position counted from the closest approach (d: the response) and from the reference
+                // point of the moments (tc); both advance by dt
+                const float x0 = __fmul_rn((float)s0 + 0.5f, dt);
+                float d = __fadd_rn(x0, D.w), tc = __fadd_rn(x0, sp.b[h].w);
 #pragma unroll
                 for (int q4 = 0; q4 < kRun; ++q4) {
                     const int s = s0 + q4;
-                    if (s <= s_hi) {
-                        const float tc = __fadd_rn(__fmul_rn((float)s + 0.5f, dt), B.w);
-                        const float yx = fmaf(tc, B.x, A.x), yy = fmaf(tc, B.y, A.y), yz = fmaf(tc, B.z, A.z);
-                        const float q = fmaf(yx, yx, fmaf(yy, yy, __fmul_rn(yz, yz)));
-                        if (q < 1.0f) {
-                            const float ex = ex2_approx(__fmul_rn(-A.w, q));
-                            const float be = sbeta[s];
-                            const float ga = __fmul_rn(ex, fmaf(C.x, be, sgamma[s]));   // g * (alpha + beta*(chat_i - chat_s))
-                            const float g1 = __fmul_rn(ga, tc);
-                            sb = fmaf(ex, be, sb);
-                            n0 = __fadd_rn(n0, ga);
-                            n1 = __fadd_rn(n1, g1);
-                            n2 = fmaf(g1, tc, n2);
-                        }
+                    const float d2 = __fmul_rn(d, d);
+                    if (s <= s_hi && d2 < D.z) {
+                        const float ex = ex2_approx(fmaf(D.y, d2, D.x));
+                        const float be = sbeta[s];
+                        const float ga = __fmul_rn(ex, fmaf(C.x, be, sgamma[s]));   // g * (alpha + beta*(chat_i - chat_s))
+                        const float g1 = __fmul_rn(ga, tc);
+                        sb = fmaf(ex, be, sb);
+                        n0 = __fadd_rn(n0, ga);
+                        n1 = __fadd_rn(n1, g1);
+                        n2 = fmaf(g1, tc, n2);
                     }
+                    d = __fadd_rn(d, dt);
+                    tc = __fadd_rn(tc, dt);
                 }
             }
             // runs of one hit sit in neighbouring lanes (at most 32 / kRun of them): add them up so that
@@ -535,7 +542,7 @@ __device__ __forceinline__ void replay_batch(const MarchLaunch& L, const Ray& r,
             const int seg_prev = __shfl_up_sync(kFull, seg, 1);
             const bool first = lane == 0 || seg_prev != seg;
             if (active && first && (sb != 0.f || n0 != 0.f || n1 != 0.f || n2 != 0.f))
-                emit_global(L, dl, sp.slot[h], expand_gradient(C.y, A, B, sb, n0, n1, n2));
+                emit_global(L, dl, sp.slot[h], expand_gradient(sp.c[h].y, sp.a[h], sp.b[h], sb, n0, n1, n2));
         }
         __syncwarp();                      // the next group reuses the staging arrays
     }
