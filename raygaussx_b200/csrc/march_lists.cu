@@ -200,7 +200,7 @@ __device__ __forceinline__ bool ray_pixel(const MarchLaunch& L, int tile_x, int 
 // The second phase (L.hz_phase == 2) has the complete lists of the flagged tiles and takes those rays up where
 // they stopped: same slabs, same hits in the same order, same image.
 template <bool COUNT, bool SAVE, bool HZ = false>
-__global__ void __launch_bounds__(kThreads, COUNT ? 1 : 3) march_forward_lists_kernel(const __grid_constant__ MarchLaunch L) {
+__global__ void __launch_bounds__(kThreads, COUNT ? 1 : 4) march_forward_lists_kernel(const __grid_constant__ MarchLaunch L) {
     __shared__ ListShared sh;
     __shared__ TapeState tape_state[SAVE ? kWarps : 1];
     constexpr bool save = SAVE;
