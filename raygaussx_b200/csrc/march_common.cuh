@@ -15,6 +15,12 @@ constexpr int kStack = 192;
 constexpr int kStage = 64;
 constexpr unsigned kFull = 0xffffffffu;
 constexpr int kTile = 8;   // CTA = 8x8 pixels; warp w marches column w of the tile
+// Unrolling of the evaluation loop over staged hits (recording forward of the 3 M-Gaussian view: 1: 13.1 ms,
+// 2: 11.9, 3: 11.9, 4: 11.8, 8: 11.8 -- but slabs with a handful of hits then run in the remainder loop).
+#ifndef RGX_EVAL_UNROLL
+#define RGX_EVAL_UNROLL 4
+#endif
+constexpr int kEvalUnroll = RGX_EVAL_UNROLL;
 constexpr int kMaxSlabs = 1 << 22;   // hard bound on slab iterations per ray
 
 struct WarpStage {      // staged hit records of one warp
@@ -329,7 +335,7 @@ __device__ __forceinline__ void clip_scene(const SceneBox& b, const Ray& r, floa
 template <bool COUNT>
 __device__ __forceinline__ void eval_forward(const WarpStage& ws, int count, float tau, float& s, float& cr,
                                              float& cg, float& cb, Tally& tl) {
-#pragma unroll 2
+#pragma unroll kEvalUnroll
     for (int j = 0; j < count; ++j) {
         const float4 A = ws.recA[j], C = ws.recB[j];
         const float d = __fadd_rn(tau, -A.x);
