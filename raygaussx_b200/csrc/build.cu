@@ -171,6 +171,17 @@ __global__ void __launch_bounds__(256) gather_kernel(BuildLaunch b) {
             g2.y = W.x * iz; g2.z = W.y * iz; g2.w = W.z * iz;
             hk = log2f(ratio);
             gaussian_aabb(p, s, q, dens, b.sigma_threshold, lo, hi);
+            // The boxes of the hierarchy and of the tile lists must contain the ellipsoid the per-ray test uses,
+            // with room for the rounding of both tests: that ellipsoid is stretched by |q|^2 when the quaternion
+            // is not a unit one (the box formula normalises it, the whitening map does not), and a ray's slab test
+            // is good to a few ulp of its distance from the eye.  (The scene box, which clips the rays as in the
+            // reference, is made from the unpadded boxes: bounds_kernel.)
+            const float qn = q.x * q.x + q.y * q.y + q.z * q.z + q.w * q.w;
+            const float grow = fmaxf(qn, 1.0f) * 1.001f - 1.0f;
+            const float3 h = make_float3(0.5f * (hi.x - lo.x), 0.5f * (hi.y - lo.y), 0.5f * (hi.z - lo.z));
+            const float reach = 4e-6f * (fmaxf(fabsf(p.x), fmaxf(fabsf(p.y), fabsf(p.z))) + 1.0f);
+            lo = make_float3(lo.x - (grow * h.x + reach), lo.y - (grow * h.y + reach), lo.z - (grow * h.z + reach));
+            hi = make_float3(hi.x + (grow * h.x + reach), hi.y + (grow * h.y + reach), hi.z + (grow * h.z + reach));
         }
     }
     b.g0[j] = g0; b.g1[j] = g1; b.g2[j] = g2;

@@ -79,7 +79,7 @@ __device__ __forceinline__ bool test_pending(const MarchLaunch& L, const Ray& r,
                                              int& npend, int lane, Tally& tl, LeafFn&& leaf) {
     const bool valid = lane < npend;
     const int j = valid ? pend[lane] : 0;
-    LeafTest t = test_gaussian(L, r, j, valid, tmin, tmax, tl, COUNT);
+    LeafTest t = test_gaussian(L, r, j, valid, tmin, tmax, tl, COUNT, false);
     const bool go = leaf(t, j);
     const int moved = (lane + kFan < npend) ? pend[lane + kFan] : 0;
     __syncwarp();
@@ -685,7 +685,7 @@ __global__ void __launch_bounds__(kThreads) march_backward_lists_kernel(const __
                                    for (int base = 0; base < nhit; base += kFan) {
                                        const bool valid = base + lane < nhit;
                                        const int j = valid ? hits[base + lane] : 0;
-                                       LeafTest t = test_gaussian(L, r, j, valid, p.tmin, p.tmax, tl, false);
+                                       LeafTest t = test_gaussian(L, r, j, valid, p.tmin, p.tmax, tl, false, false);
                                        if (!leaf(t, j)) return;
                                    }
                                }, emit);
