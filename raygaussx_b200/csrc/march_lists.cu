@@ -400,9 +400,9 @@ constexpr int kRun = 4;     // samples per work item of the replay (2: 12.9 ms, 
 constexpr int kBatch = 8;   // slabs of a ray whose hits are worked off together
 
 struct ReplayStage {        // per warp: one group of up to 32 hits
-    float4 a[kFan];         // whitened ray point at the reference parameter, hk
-    float4 b[kFan];         // whitened direction, tbuffer - reference parameter
-    float4 c[kFan];         // chat_i, sigma, first and last sample (as int bits)
+    float4 a[kFan];         // whitened ray point at the reference parameter of the moments, sigma
+    float4 b[kFan];         // whitened direction, -
+    float4 c[kFan];         // chat_i, tbuffer - reference parameter, first and last sample (as int bits)
     float4 d[kFan];         // the response along the ray as a parabola about the closest approach (march_common.cuh,
                             // eval_forward): -hk q_min, -hk |de|^2, (1 - q_min)/|de|^2, tbuffer - closest approach
     int slot[kFan];
@@ -412,8 +412,7 @@ struct ReplayStage {        // per warp: one group of up to 32 hits
 
 template <int NB>
 struct ReplayBatchT {       // per warp: up to NB consecutive slabs of the ray
-    float beta[NB][kSlab];
-    float gamma[NB][kSlab];
+    float2 bg[NB][kSlab];    // per sample: beta, gamma (slab_back_terms)
     float tbuffer[NB];
     float dt[NB];
     long long hits[NB];      // where the slab's hit list starts on the tape
@@ -467,9 +466,9 @@ __device__ __forceinline__ void replay_batch(const MarchLaunch& L, const Ray& r,
             const int s_hi = (int)fmaxf(fminf(floorf(x_hi) + 1.0f, (float)(kSlab - 1)), -1.f);
             // moments about the closest approach clamped to the slab, so that they stay small
             const float tcr = fminf(fmaxf(tca, tbuffer), tend);
-            sp.a[lane] = make_float4(fmaf(tcr, de.x, Oe.x), fmaf(tcr, de.y, Oe.y), fmaf(tcr, de.z, Oe.z), hk);
-            sp.b[lane] = make_float4(de.x, de.y, de.z, __fadd_rn(tbuffer, -tcr));
-            sp.c[lane] = make_float4(ci, c.w, __int_as_float(s_lo), __int_as_float(s_hi));
+            sp.a[lane] = make_float4(fmaf(tcr, de.x, Oe.x), fmaf(tcr, de.y, Oe.y), fmaf(tcr, de.z, Oe.z), c.w);
+            sp.b[lane] = make_float4(de.x, de.y, de.z, 0.f);
+            sp.c[lane] = make_float4(ci, __fadd_rn(tbuffer, -tcr), __int_as_float(s_lo), __int_as_float(s_hi));
             const float a = dot3(de, de);
             sp.d[lane] = make_float4(__fmul_rn(-hk, qmin), __fmul_rn(-hk, a), __fmul_rn(1.0f - qmin, inv_a),
                                      __fadd_rn(tbuffer, -tca));
@@ -500,23 +499,23 @@ __device__ __forceinline__ void replay_batch(const MarchLaunch& L, const Ray& r,
                 const float4 C = sp.c[h], D = sp.d[h];
                 const int k = SINGLE ? 0 : sp.slab[h];
                 const float dt = SINGLE ? dt1 : bt.dt[k];
-                const float* sbeta = bt.beta[k];
-                const float* sgamma = bt.gamma[k];
+                const float2* sbg = bt.bg[k];
                 const int s_hi = __float_as_int(C.w);
                 const int nrun = (s_hi - __float_as_int(C.z) + kRun) / kRun;
                 const int s0 = __float_as_int(C.z) + kRun * (i - (sp.upto[h] - nrun));
                 // sample position counted from the closest approach (d: the response) and from the reference
                 // point of the moments (tc); both advance by dt
                 const float x0 = __fmul_rn((float)s0 + 0.5f, dt);
-                float d = __fadd_rn(x0, D.w), tc = __fadd_rn(x0, sp.b[h].w);
+                float d = __fadd_rn(x0, D.w), tc = __fadd_rn(x0, C.y);
 #pragma unroll
                 for (int q4 = 0; q4 < kRun; ++q4) {
                     const int s = s0 + q4;
                     const float d2 = __fmul_rn(d, d);
                     if (s <= s_hi && d2 < D.z) {
                         const float ex = ex2_approx(fmaf(D.y, d2, D.x));
-                        const float be = sbeta[s];
-                        const float ga = __fmul_rn(ex, fmaf(C.x, be, sgamma[s]));   // g * (alpha + beta*(chat_i - chat_s))
+                        const float2 bg = sbg[s];
+                        const float be = bg.x;
+                        const float ga = __fmul_rn(ex, fmaf(C.x, be, bg.y));   // g * (alpha + beta*(chat_i - chat_s))
                         const float g1 = __fmul_rn(ga, tc);
                         sb = fmaf(ex, be, sb);
                         n0 = __fadd_rn(n0, ga);
@@ -541,8 +540,10 @@ __device__ __forceinline__ void replay_batch(const MarchLaunch& L, const Ray& r,
             }
             const int seg_prev = __shfl_up_sync(kFull, seg, 1);
             const bool first = lane == 0 || seg_prev != seg;
-            if (active && first && (sb != 0.f || n0 != 0.f || n1 != 0.f || n2 != 0.f))
-                emit_global(L, dl, sp.slot[h], expand_gradient(sp.c[h].y, sp.a[h], sp.b[h], sb, n0, n1, n2));
+            if (active && first && (sb != 0.f || n0 != 0.f || n1 != 0.f || n2 != 0.f)) {
+                const float4 A = sp.a[h];
+                emit_global(L, dl, sp.slot[h], expand_gradient(A.w, A, sp.b[h], sb, n0, n1, n2));
+            }
         }
         __syncwarp();                      // the next group reuses the staging arrays
     }
@@ -596,8 +597,7 @@ __global__ void __launch_bounds__(kThreads) march_backward_replay_kernel(const _
             const SlabBackTerms terms = slab_back_terms(sums.x, dc, p.dt, T, D, eps, lane);
             D = __fadd_rn(D, -terms.d_total);
             T = slab_exit_T(terms.tr, eps);
-            bt.beta[nslab][lane] = terms.beta;
-            bt.gamma[nslab][lane] = terms.gamma;
+            bt.bg[nslab][lane] = make_float2(terms.beta, terms.gamma);
             nhits += nhit;
             if (lane == 0) { bt.tbuffer[nslab] = tbuffer; bt.dt[nslab] = p.dt; bt.hits[nslab] = hits_at; bt.upto[nslab] = nhits; }
             ++nslab;
