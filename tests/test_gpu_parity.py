@@ -336,11 +336,16 @@ def test_autograd_row_ranges_add_up_to_the_whole_view(ro):
     g = torch.Generator().manual_seed(4)
     weight = torch.randn(h * w, 3, generator=g).to(dev)
 
-    def run(row_sets):
+    def run(row_sets, announce=False):
         leaves = [t.clone().requires_grad_(True) for t in sc.tensors()[:5]]
         image = torch.zeros(h * w, 3, device=dev)
-        for rows in row_sets:
-            st = settings_for(ro, sc, cam, rows=rows)
+        for i, rows in enumerate(row_sets):
+            extra = {}
+            if announce:      # same Gaussians throughout: build once, prepare each next range during the backward
+                extra["reuse_acceleration_structure"] = i > 0
+                if i + 1 < len(row_sets):
+                    extra.update(next_viewpoint_cam=cam, next_rows=row_sets[i + 1])
+            st = settings_for(ro, sc, cam, rows=rows, **extra)
             out = ro.RenderOptixFunction.apply(*leaves, *sc.tensors()[5:], st)
             lo, hi = (0, h * w) if rows is None else (rows[0] * w, rows[1] * w)
             (out[lo:hi] * weight[lo:hi]).sum().backward()
@@ -351,6 +356,12 @@ def test_autograd_row_ranges_add_up_to_the_whole_view(ro):
     parts_img, parts = run([(0, 5), (5, h)])
     assert torch.equal(whole_img, parts_img)
     for a, b in zip(whole, parts):
+        assert rel_max(a.cpu(), b.cpu()) < 1e-5
+    made = ro.get_renderer().lists_made_ahead()
+    ahead_img, ahead = run([(0, 5), (5, 9), (9, h)], announce=True)
+    assert ro.get_renderer().lists_made_ahead() == made + 2
+    assert torch.equal(whole_img, ahead_img)
+    for a, b in zip(whole, ahead):
         assert rel_max(a.cpu(), b.cpu()) < 1e-5
 
 
