@@ -249,6 +249,7 @@ def main():
         params = [t.clone().requires_grad_(True) for t in scene_dev_tensors[:5]] + list(scene_dev_tensors[5:])
         my_blocks = shard_rows(args.views, args.height, rank, world)
         loss_host = torch.zeros(1).pin_memory()
+        copy_stream = torch.cuda.Stream()
 
         def e2e_step(amortised=False):
             """amortised: the caller vouches that the Gaussians do not change inside the accumulation step (build
@@ -256,9 +257,22 @@ def main():
             for p in params[:5]:
                 p.grad = None
             total = torch.zeros((), device=dev)
+            # H2D of every block's target rows from pinned memory, on a copy stream beside the kernels (what a
+            # data loader does); a block waits for its own copy only
+            copy_stream.wait_stream(torch.cuda.current_stream())
+            staged = []
+            with torch.cuda.stream(copy_stream):
+                for b in my_blocks:
+                    lo, hi = b.row_begin * args.width, b.row_end * args.width
+                    t = targets_host[b.view][lo:hi].to(dev, non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record(copy_stream)
+                    staged.append((t, ev))
             for i, b in enumerate(my_blocks):                                    # this rank's rows of each of its views
                 lo, hi = b.row_begin * args.width, b.row_end * args.width
-                tgt = targets_host[b.view][lo:hi].to(dev, non_blocking=True)     # H2D of these rows' target
+                tgt, ev = staged[i]
+                torch.cuda.current_stream().wait_event(ev)
+                tgt.record_stream(torch.cuda.current_stream())
                 extra = {}
                 if amortised:
                     extra["reuse_acceleration_structure"] = i > 0
