@@ -107,3 +107,83 @@ def test_all_reduce_joins_the_ranks_gloo():
     out = mgr.dict()
     mp.spawn(_gloo_worker, args=(world, _free_port(), out), nprocs=world, join=True)
     assert out[0] == out[1] == [4.0, 4.0, 4.0]      # every view's rows were covered exactly once
+
+
+class _RecordingRenderer:
+    """Stands in for the CUDA renderer: writes a colour that depends on (view, row), adds the loss gradient's sum
+    per row range to the first gradient tensor, and keeps the order of calls."""
+
+    def __init__(self):
+        self.calls = []
+
+    def build(self, *a):
+        self.calls.append(("build",))
+
+    def forward(self, *args):
+        cam, march = args[-2], args[-1]
+        self.calls.append(("forward", cam.view, march["rows"]))
+        rgb = torch.zeros(cam.width * cam.height, 3)
+        lo, hi = march["rows"]
+        rgb[lo * cam.width:hi * cam.width] = 0.25 + cam.view
+        return rgb, None, None
+
+    def hint_next_view(self, cam, march):
+        self.calls.append(("hint", cam.view, march["rows"]))
+
+    def backward(self, *args):
+        cam, march, rgb, dl, grads = args[-5:]
+        self.calls.append(("backward", cam.view, march["rows"]))
+        lo, hi = march["rows"]
+        grads[0][cam.view, 0] += dl[lo * cam.width:hi * cam.width].sum()
+
+
+class _Cam:
+    def __init__(self, view, width, height):
+        self.view, self.width, self.height = view, width, height
+
+
+def _step_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.distributed.init_process_group("gloo", rank=rank, world_size=world)
+    n_views, w, h = 3, 4, 6
+    cams = [_Cam(v, w, h) for v in range(n_views)]
+    targets = [torch.zeros(w * h, 3) for _ in cams]
+    tensors = [torch.zeros(5, 3)] * 8
+    march_of = lambda cam, rows, flags: {"rows": rows, "flags": flags}
+    res = {}
+    for ahead in (False, True):
+        r = _RecordingRenderer()
+        gb = rdist.GradBuffer(5, 4, "cpu")
+        rdist.accumulation_step(r, tensors, cams, targets, march_of, gb, rank=rank, world=world, lists_ahead=ahead)
+        res[ahead] = (r.calls, gb.views["positions"][:n_views, 0].tolist())
+    out[rank] = res
+    torch.distributed.destroy_process_group()
+
+
+def test_accumulation_step_announces_each_next_block_gloo():
+    world = 2
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_step_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    n_views, w, h = 3, 4, 6
+    for rank in range(world):
+        blocks = rdist.shard_rows(n_views, h, rank, world)
+        plain, _ = out[rank][False]
+        ahead, _ = out[rank][True]
+        assert [c for c in plain if c[0] == "hint"] == []
+        want = [("build",)]
+        for i, b in enumerate(blocks):
+            rows = (b.row_begin, b.row_end)
+            want.append(("forward", b.view, rows))
+            if i + 1 < len(blocks):       # the next block is announced before this one's backward
+                nb = blocks[i + 1]
+                want.append(("hint", nb.view, (nb.row_begin, nb.row_end)))
+            want.append(("backward", b.view, rows))
+        assert ahead == want
+        assert [c for c in ahead if c[0] != "hint"] == plain
+    # the all-reduced gradient is the whole step's, whichever way it was cut, with or without announcements:
+    # sign(colour - 0) / (3 R n_views), three channels, all R rays of a view
+    for ahead in (False, True):
+        g0, g1 = out[0][ahead][1], out[1][ahead][1]
+        assert g0 == g1
+        assert g0 == pytest.approx([1.0 / n_views] * n_views, rel=1e-6)
