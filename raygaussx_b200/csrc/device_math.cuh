@@ -63,6 +63,12 @@ __device__ __forceinline__ void gaussian_aabb(float3 c, float3 s, float4 q, floa
     hi = make_float3(c.x + hx, c.y + hy, c.z + hz);
 }
 
+__device__ __forceinline__ float sqrt_approx(float x) {
+    float y;
+    asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

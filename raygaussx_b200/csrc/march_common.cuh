@@ -108,6 +108,8 @@ __device__ __forceinline__ void whiten_ray(const Ray& r, float4 g0, float4 g1, f
 }
 
 // Interval of the ray inside the truncation ellipsoid
+// (square root and the division for the first root are the approximate instructions, good to 2 ulp: the roots
+// only decide whether and where the interval meets a slab; forward 10.2 -> 10.0 ms)
 // (cuda_train/forward/gaussians_aabb.cu:43-91 with M = S^-1 R^T / k folded into g0..g2).
 __device__ __forceinline__ bool ellipsoid_interval(const Ray& r, float4 g0, float4 g1, float4 g2, float3& Oe,
                                                    float3& de, float& r1, float& r2) {
@@ -120,9 +122,9 @@ __device__ __forceinline__ bool ellipsoid_interval(const Ray& r, float4 g0, floa
     float3 P = make_float3(fmaf(bia, de.x, Oe.x), fmaf(bia, de.y, Oe.y), fmaf(bia, de.z, Oe.z));
     float disc = 1.0f - dot3(P, P);
     if (!(disc > 1e-7f)) return false;
-    float sd = __fsqrt_rn(__fmul_rn(disc, a));
+    float sd = sqrt_approx(__fmul_rn(disc, a));
     float q = b + copysignf(sd, b);
-    r1 = __fdiv_rn(c, q);
+    r1 = __fdividef(c, q);
     r2 = __fmul_rn(q, inv_a);
     return true;
 }

@@ -454,8 +454,11 @@ __device__ __forceinline__ void replay_batch(const MarchLaunch& L, const Ray& r,
             const float4 c = __ldg(&L.g.rgba[j]);
             const float ci = __fdividef(fmaf(dl.x, c.x, fmaf(dl.y, c.y, __fmul_rn(dl.z, c.z))), c.w);
             // closest approach and half width of the stretch inside the ellipsoid |Oe + t de| < 1
-            const float inv_a = __fdividef(1.0f, dot3(de, de));
-            const float tca = __fmul_rn(-dot3(Oe, de), inv_a);
+            const float aa = dot3(de, de);
+            const float inv_a = __fdividef(1.0f, aa);
+            // correctly rounded: the response is evaluated as a parabola about this point, and what the point is
+            // off the true closest approach comes back as an unmodelled linear term 2 |de|^2 (tau - tau*) error
+            const float tca = __fdiv_rn(-dot3(Oe, de), aa);
             const float3 P = make_float3(fmaf(tca, de.x, Oe.x), fmaf(tca, de.y, Oe.y), fmaf(tca, de.z, Oe.z));
             const float qmin = dot3(P, P);
             const float hw = __fsqrt_rn(__fmul_rn(fmaxf(1.0f - qmin, 0.f), inv_a));
@@ -469,8 +472,7 @@ __device__ __forceinline__ void replay_batch(const MarchLaunch& L, const Ray& r,
             sp.a[lane] = make_float4(fmaf(tcr, de.x, Oe.x), fmaf(tcr, de.y, Oe.y), fmaf(tcr, de.z, Oe.z), c.w);
             sp.b[lane] = make_float4(de.x, de.y, de.z, 0.f);
             sp.c[lane] = make_float4(ci, __fadd_rn(tbuffer, -tcr), __int_as_float(s_lo), __int_as_float(s_hi));
-            const float a = dot3(de, de);
-            sp.d[lane] = make_float4(__fmul_rn(-hk, qmin), __fmul_rn(-hk, a), __fmul_rn(1.0f - qmin, inv_a),
+            sp.d[lane] = make_float4(__fmul_rn(-hk, qmin), __fmul_rn(-hk, aa), __fmul_rn(1.0f - qmin, inv_a),
                                      __fadd_rn(tbuffer, -tca));
             sp.slot[lane] = j;
             if (!SINGLE) sp.slab[lane] = k;

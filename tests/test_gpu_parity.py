@@ -133,10 +133,11 @@ def test_backward_from_recorded_hits_equals_backward_by_search(ro, name):
     rgb2, _, _ = r.forward(*tens, cs, ro._settings_march(st, cs, flags=_lib.FLAG_SAVE_HITS))
     assert torch.equal(rgb, rgb2)
     replayed = backward(ro, r, sc, tens, cs, rgb2, dl)                # reads the recorded hits
-    # same hits and same per-sample sums; the replay adds each Gaussian's moments sample by sample in one lane,
-    # the search adds them across lanes: rounding only
+    # same hits and same per-sample sums; the replay adds each Gaussian's moments sample by sample in one lane and
+    # evaluates the response as a parabola about the closest approach, the search adds them across lanes and
+    # evaluates it from the whitened offset: rounding only (each is held to 1e-3 of the oracle's gradients)
     for a, b in zip(searched[:5], replayed[:5]):
-        assert rel_max(a.cpu(), b.cpu()) < 1e-4
+        assert rel_max(a.cpu(), b.cpu()) < 2e-4
     # a recording for another view must not be used: render a shifted camera without recording, then check
     g = load_golden(name)
     for nm, gr in zip(GRAD_NAMES, replayed):
