@@ -364,7 +364,7 @@ __device__ __forceinline__ float4 parabola_record(float3 Oe, float3 de, float tb
     const float tstar = __fdiv_rn(-dot3(Oe, de), a);
     const float3 P = make_float3(fmaf(tstar, de.x, Oe.x), fmaf(tstar, de.y, Oe.y), fmaf(tstar, de.z, Oe.z));
     const float qmin = dot3(P, P);
-    return make_float4(__fadd_rn(tstar, -tbuffer), __fdiv_rn(1.0f - qmin, a), __fmul_rn(-hk, a), __fmul_rn(-hk, qmin));
+    return make_float4(__fadd_rn(tstar, -tbuffer), __fdividef(1.0f - qmin, a), __fmul_rn(-hk, a), __fmul_rn(-hk, qmin));
 }
 
 __device__ __forceinline__ void flush_tally(const MarchLaunch& L, const Tally& tl, int lane) {

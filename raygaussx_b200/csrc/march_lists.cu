@@ -461,7 +461,7 @@ __device__ __forceinline__ void replay_batch(const MarchLaunch& L, const Ray& r,
             const float tca = __fdiv_rn(-dot3(Oe, de), aa);
             const float3 P = make_float3(fmaf(tca, de.x, Oe.x), fmaf(tca, de.y, Oe.y), fmaf(tca, de.z, Oe.z));
             const float qmin = dot3(P, P);
-            const float hw = __fsqrt_rn(__fmul_rn(fmaxf(1.0f - qmin, 0.f), inv_a));
+            const float hw = sqrt_approx(__fmul_rn(fmaxf(1.0f - qmin, 0.f), inv_a));      // only sizes the window of samples
             // samples (s + 1/2) dt inside it, one more on each side against rounding; the test q < 1 decides
             const float x_lo = fmaf(__fadd_rn(__fadd_rn(tca, -hw), -tbuffer), inv_dt, -0.5f);
             const float x_hi = fmaf(__fadd_rn(__fadd_rn(tca, hw), -tbuffer), inv_dt, -0.5f);
