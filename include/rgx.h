@@ -9,9 +9,17 @@
  * Conventions
  *   - every pointer named in a struct or argument list is a DEVICE pointer to
  *     contiguous fp32 (or int32) data owned by the caller, unless stated;
+ *   - rgx_scene.quaternions must start on a 16-byte boundary, and so must
+ *     rgx_scene.color_features and rgx_grads.color_features when sh_coeffs is 16
+ *     (the kernels move them 16 bytes at a time); anything else is refused with
+ *     RGX_E_INVALID before a kernel is launched.  Whole allocations of cudaMalloc
+ *     or of a framework's allocator satisfy this; a row slice of one may not;
  *   - every call enqueues its work on the given CUDA stream and returns without
- *     synchronising; no call performs a device->host copy unless stated;
+ *     synchronising, and performs no device->host copy, unless its comment says
+ *     otherwise (rgx_forward and rgx_backward do say otherwise: see there);
  *   - return value 0 is success, negative values are RGX_E_*; nothing throws;
+ *   - every call makes its device current while it runs and puts the caller's
+ *     current device back before it returns;
  *   - a context belongs to one device and one host thread at a time;
  *   - the context owns its workspace (device memory grown on demand in
  *     rgx_build / rgx_forward / rgx_backward, freed in rgx_destroy).
@@ -122,9 +130,6 @@ typedef struct rgx_counters {
     uint64_t ellipsoid_tests;/* exact ray/ellipsoid tests */
     uint64_t stack_overflows;/* traversal-stack overflows (results invalid if non-zero) */
     uint64_t hits_hash;     /* order-independent hash of every (ray, slab, Gaussian) hit triple */
-    uint64_t windows;       /* unused (kept so that the struct keeps its size) */
-    uint64_t window_retries;/* unused */
-    uint64_t fallback_windows;/* unused */
     uint64_t candidates;    /* tile-list march: list entries looked at (32 per opened block of a tile's list) */
     /* tile-list forward march, counting variant: warp-cycles spent per phase (clock64 differences summed over
      * warps).  cycles_search contains cycles_wait, which contains cycles_window and most of cycles_eval. */
@@ -135,7 +140,6 @@ typedef struct rgx_counters {
     uint64_t cycles_composite;/* compositing of a slab */
     uint64_t cycles_wait;     /* exact tests of 32 candidates and what follows from their hits */
     uint64_t cycles_total;    /* whole ray */
-    uint64_t reserved;
 } rgx_counters;
 
 /* Replaces: ox.DeviceContext / module / pipeline creation (optix_utils.py:154-210). */
@@ -163,7 +167,12 @@ RGX_API int rgx_build(rgx_ctx* ctx, const rgx_scene* scene, float sigma_threshol
 /* Replaces: compute_cupy_rgb + launch_pipeline_forward (render_optix.py:121-131;
  * device code cuda_train/forward/gaussians_aabb.cu, utils/sh_utils.cu:122-216).
  * rgb [R,3] is required; alpha [R] (1 - final transmittance) and depth [R]
- * (expected depth, cuda_gui/gaussians_aabb.cu:189-202) may be NULL.  R = width*height. */
+ * (expected depth, cuda_gui/gaussians_aabb.cu:189-202) may be NULL.  R = width*height.
+ * Host synchronisation: the first forward (or backward) of a view -- a camera and row range for which the
+ * context holds no tile lists yet -- waits once on `stream` for the number of (tile, Gaussian) pairs of the
+ * view (8 bytes device->host), which sizes the sort; a forward-only view that takes the two-depth path
+ * (rgx_debug_two_depth) waits up to three times.  A view whose lists were made ahead (rgx_hint_next_view) or
+ * are still cached does not wait.  RGX_FLAG_PER_RAY_SEARCH and RGX_FLAG_BRUTE_FORCE never wait. */
 RGX_API int rgx_forward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, const rgx_march* march,
                 float* rgb, float* alpha, float* depth, rgx_stream stream);
 
@@ -179,7 +188,13 @@ RGX_API int rgx_forward_frame(rgx_ctx* ctx, const rgx_scene* scene, const rgx_ca
 /* Replaces: launch_pipeline_backward + reduce_temp_grads + compute_cupy_sh_grad
  * (render_optix.py:166-185; device code cuda_train/backward/gaussians_aabb.cu,
  * utils/sh_utils.cu:218-412).  rgb is the forward's output for the same camera,
- * dL_drgb [R,3] the incoming gradient; rays outside [row_begin,row_end) are not read. */
+ * dL_drgb [R,3] the incoming gradient; rays outside [row_begin,row_end) are not read.
+ * The geometry (positions, scales, quaternions, densities) is NOT read from `scene` here but from the
+ * context's latest rgx_build: call rgx_backward before any rgx_build with other values, or build again from
+ * the forward's tensors first (a recording made before that build is then ignored and the rays are searched
+ * again).  `scene` supplies the count, the colour tensors and the shapes of the gradients.
+ * Host synchronisation: as rgx_forward, when the view's lists have to be made; and, when the lists of an
+ * announced next view are made beside it, one wait on a stream of the context's own (not on `stream`). */
 RGX_API int rgx_backward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, const rgx_march* march,
                  const float* rgb, const float* dL_drgb, const rgx_grads* grads, rgx_stream stream);
 
@@ -258,7 +273,9 @@ RGX_API int rgx_measure_peaks(int device, float* fma_tflops, float* ex2_gops);
  * they need a frame -- a viewer thread beside a trainer whose caching allocator
  * owns the device memory, a plug-in in a process that forbids allocations after
  * start-up, a latency path that cannot afford an allocation's implicit device
- * synchronisation.  Does what rgx_build + rgx_forward do (same kernels, same
+ * synchronisation.  (The CUDA runtime loads a kernel's code when the kernel is first launched, which may
+ * allocate inside the driver: make one warm-up call during start-up, before the phase in which nothing may
+ * allocate.)  Does what rgx_build + rgx_forward do (same kernels, same
  * results) with all scratch in a fixed 8 MiB array inside the library image, so it
  * needs no context and calls neither cudaMalloc nor cudaFree nor any allocating
  * library routine.  Limit: scene->n <= 32768, else RGX_E_TOO_LARGE;
@@ -268,6 +285,12 @@ RGX_API int rgx_measure_peaks(int device, float* fma_tflops, float* ex2_gops);
  * race; serialise them (same stream, or an event between them). */
 RGX_API int rgx_forward_static(int device, const rgx_scene* scene, const rgx_camera* cam, const rgx_march* march,
                                float sigma_threshold, float* rgb, float* alpha, float* depth, rgx_stream stream);
+
+/* How many kernels of this library the process has launched so far, over all contexts and devices (the
+ * library's own kernels; the radix-sort kernels of CUB that it calls are not counted).  No counterpart in
+ * the reference.  Instrumentation for benchmarks: the difference across a timed region is the number of
+ * launches inside it. */
+RGX_API unsigned long long rgx_kernel_launches(void);
 
 /* Bytes of device memory currently held by the context's workspace. */
 RGX_API size_t rgx_workspace_bytes(const rgx_ctx* ctx);

@@ -230,6 +230,8 @@ class MarchOutput:
     margin: torch.Tensor            # per ray: smallest relative distance of any evaluated predicate to flipping
     counters: dict = field(default_factory=dict)
     grads: Optional[dict] = None    # explicit backward: pos, scale, quat, density, rgb (per Gaussian)
+    overflow: Optional[torch.Tensor] = None   # per ray: some slab had more hits than max_prim_slice (which hits
+                                              # survive is then up to the traversal order: no parity defined)
 
 
 def _trace_closest(valid, root1, root2, tmin, tmax):
@@ -297,6 +299,7 @@ def _march_chunk(o, d, P, S, Q, dens, rgb_g, bb_min, bb_max, mp, delta=None, c_f
     C = torch.zeros(B, 3, dtype=F64)
     depth = torch.zeros(B, dtype=F64)
     margin = torch.full((B,), inf, dtype=F64)
+    ovf_ray = torch.zeros(B, dtype=torch.bool)
     cnt = dict(S=0, S_h=0, Q_c=0, P=0, E_in=0, OVF=0)
 
     with torch.no_grad():
@@ -342,6 +345,7 @@ def _march_chunk(o, d, P, S, Q, dens, rgb_g, bb_min, bb_max, mp, delta=None, c_f
             p0 = hit.sum(dim=1)
             cnt["S"] += int(idx.numel())
             cnt["OVF"] += int((p0 > mp.max_prim_slice).sum())
+            ovf_ray[idx[p0 > mp.max_prim_slice]] = True
             gap = torch.where(ok[idx], (hi - lo).abs() / slab[:, None], torch.full_like(lo, inf))
             gap = torch.cat([gap, torch.full_like(slab, inf)[:, None]], dim=1).min(dim=1).values
             margin[idx] = torch.minimum(margin[idx], gap)
@@ -447,7 +451,7 @@ def _march_chunk(o, d, P, S, Q, dens, rgb_g, bb_min, bb_max, mp, delta=None, c_f
             tbuf[h] = tb + slab                                                              # :324
 
     rgb = C + T[:, None] * bg[None, :]                                                       # :326-330
-    out = MarchOutput(rgb=rgb, alpha=1.0 - T, depth=depth, margin=margin, counters=cnt)
+    out = MarchOutput(rgb=rgb, alpha=1.0 - T, depth=depth, margin=margin, counters=cnt, overflow=ovf_ray)
     if want_grad:
         out.grads = dict(pos=g_pos, scale=g_scale, quat=quat_grad_from_columns(Q, g_U, g_V, g_W), density=g_dens,
                          rgb=g_rgb)
@@ -478,6 +482,22 @@ def _prefilter(o, dirs, P, rad, dens, sig_t):
         return near.any(dim=1) & (dens > sig_t)
 
 
+def _cone_cull(o, dirs, P, rad):
+    """Conservative cull for a whole set of rays from one origin: keep the Gaussians whose bounding sphere
+    reaches into the cone around the mean direction that contains every ray.  Like :func:`_prefilter` it only
+    saves memory and time on large scenes (the per-chunk filter then works on what is left)."""
+    with torch.no_grad():
+        axis = dirs.mean(dim=0)
+        axis = axis / axis.norm()
+        half = torch.acos((dirs @ axis).min().clamp(-1.0, 1.0)) + 1e-6
+        v = P - o[None, :]
+        dist = v.norm(dim=1)
+        inside = dist <= rad                                          # the origin lies in the sphere
+        ang = torch.acos(((v @ axis) / dist.clamp_min(1e-300)).clamp(-1.0, 1.0))
+        spread = torch.asin((rad / dist.clamp_min(1e-300)).clamp(max=1.0))
+        return inside | (ang <= half + spread + 1e-9)
+
+
 def march(positions, scales, quaternions, densities, rgb_g, cam: CameraParams, mp, ray_ids=None, delta=None,
           chunk=64, diff=False):
     """Forward (and, with ``delta = dL/dC [R,3]``, explicit backward) of the march
@@ -503,6 +523,7 @@ def march(positions, scales, quaternions, densities, rgb_g, cam: CameraParams, m
     alpha = torch.zeros(n_r, dtype=F64)
     depth = torch.zeros(n_r, dtype=F64)
     margin = torch.zeros(n_r, dtype=F64)
+    overflow = torch.zeros(n_r, dtype=torch.bool)
     total = dict(S=0, S_h=0, Q_c=0, P=0, E_in=0, OVF=0)
     grads = None
     if delta is not None:
@@ -512,23 +533,31 @@ def march(positions, scales, quaternions, densities, rgb_g, cam: CameraParams, m
         grads = dict(pos=torch.zeros(N, 3, dtype=F64), scale=torch.zeros(N, 3, dtype=F64),
                      quat=torch.zeros(N, 4, dtype=F64), density=torch.zeros(N, dtype=F64),
                      rgb=torch.zeros(N, 3, dtype=F64))
+    cone = None
+    if N > 100_000 and n_r > 0:
+        cone = _cone_cull(o, dirs, P.detach(), rad).nonzero(as_tuple=True)[0]
     for s in range(0, n_r, chunk):
         sl = slice(s, min(n_r, s + chunk))
         dch = dirs[sl]
-        keep = _prefilter(o, dch, P.detach(), rad, dens.detach(), sig_t)
-        ids = keep.nonzero(as_tuple=True)[0]
+        if cone is None:
+            keep = _prefilter(o, dch, P.detach(), rad, dens.detach(), sig_t)
+            ids = keep.nonzero(as_tuple=True)[0]
+        else:
+            keep = _prefilter(o, dch, P.detach()[cone], rad[cone], dens.detach()[cone], sig_t)
+            ids = cone[keep]
         out = _march_chunk(o, dch, P[ids], S[ids], Q[ids], dens[ids], rgbg[ids], bb_min, bb_max, mp,
                            delta=None if delta is None else delta[sl],
                            c_final=None if delta is None else fwd.rgb[sl], diff=diff)
         rgb.append(out.rgb)
         alpha[sl], depth[sl], margin[sl] = out.alpha.detach(), out.depth.detach(), out.margin
+        overflow[sl] = out.overflow
         for kx in total:
             total[kx] += out.counters[kx]
         if grads is not None:
             for kx in grads:
                 grads[kx].index_add_(0, ids, out.grads[kx])
     return MarchOutput(rgb=torch.cat(rgb, dim=0) if rgb else torch.zeros(0, 3, dtype=F64), alpha=alpha, depth=depth,
-                       margin=margin, counters=total, grads=grads)
+                       margin=margin, counters=total, grads=grads, overflow=overflow)
 
 
 # --------------------------------------------------------------------------- operator

@@ -43,10 +43,9 @@ class Grads(C.Structure):
 class Counters(C.Structure):
     _fields_ = [(k, C.c_uint64) for k in ("rays", "slabs", "slabs_hit", "closest_queries", "hits", "pairs_inside",
                                           "overflow_slabs", "node_tests", "prim_tests", "ellipsoid_tests",
-                                          "stack_overflows", "hits_hash", "windows", "window_retries",
-                                          "fallback_windows", "candidates", "cycles_window", "cycles_seek",
+                                          "stack_overflows", "hits_hash", "candidates", "cycles_window", "cycles_seek",
                                           "cycles_search", "cycles_eval", "cycles_composite", "cycles_wait",
-                                          "cycles_total", "reserved")]
+                                          "cycles_total")]
 
     def as_dict(self):
         return {k: int(getattr(self, k)) for k, _ in self._fields_}
@@ -77,6 +76,7 @@ SYMBOLS = {
     "rgx_reset_counters": (C.c_int, [C.c_void_p, C.c_void_p]),
     "rgx_read_counters": (C.c_int, [C.c_void_p, C.POINTER(Counters), C.c_void_p]),
     "rgx_workspace_bytes": (C.c_size_t, [C.c_void_p]),
+    "rgx_kernel_launches": (C.c_ulonglong, []),
     "rgx_forward_static": (C.c_int, [C.c_int, C.POINTER(Scene), C.POINTER(Camera), C.POINTER(March), C.c_float, _fp, _fp,
                                      _fp, C.c_void_p]),
     "rgx_set_profiling": (C.c_int, [C.c_void_p, C.c_int]),

@@ -1,5 +1,6 @@
 // C ABI of librgx.so: context, workspace and the entry points of include/rgx.h.
 #include "rgx_internal.cuh"
+#include <atomic>
 #include <cstdio>
 #include <cstring>
 #include <new>
@@ -84,6 +85,7 @@ struct rgx_ctx {
     unsigned long long rgba_serial = 0, tape_rgba_serial = 0;   // which evaluation of the per-view colours is in rgba / was recorded with
     unsigned long long tape_build_id = 0;
     rgx_camera tape_cam{};
+    rgx_march tape_march{};            // the parameters that shape the slabs of the recording
     int tape_row_begin = 0, tape_row_end = 0;
     int* tape_tile_order = nullptr; int tape_order_cap = 0;   // order of the recording forward's CTAs, kept for the replay
     // lists of the view announced by rgx_hint_next_view, made on a stream of the context's own while the backward replays
@@ -100,6 +102,11 @@ struct rgx_ctx {
     std::vector<Timed> timed;       // recorded, not yet read
     std::vector<Timed> spare;       // event pairs ready for reuse
 };
+
+namespace rgx {
+static std::atomic<unsigned long long> g_launches{0};
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+}  // namespace rgx
 
 namespace {
 
@@ -246,19 +253,28 @@ int ensure_workspace(rgx_ctx* ctx, int n_pad, int boxes) {
     return RGX_OK;
 }
 
-int check_scene(rgx_ctx* ctx, const rgx_scene* sc, bool need_color) {
+// need_geometry: positions / scales / quaternions / densities are read by the call (rgx_gaussian_colors reads
+// positions only).  Pointers that kernels load 16 bytes at a time must be 16-byte aligned (include/rgx.h).
+int check_scene(rgx_ctx* ctx, const rgx_scene* sc, bool need_color, bool need_geometry = true) {
     if (!ctx) return RGX_E_INVALID;
-    if (ctx->alloc_failed) { cudaSetDevice(ctx->device); release_workspace(ctx); }
+    if (ctx->alloc_failed) release_workspace(ctx);      // the caller has made the context's device current
     if (!sc) return fail(ctx, RGX_E_INVALID, "scene is null");
     if (sc->n < 0) return fail(ctx, RGX_E_INVALID, "negative Gaussian count");
     if (sc->n > (1 << 30)) return fail(ctx, RGX_E_TOO_LARGE, "more than 2^30 Gaussians");
-    if (sc->n > 0 && (!sc->positions || !sc->scales || !sc->quaternions || !sc->densities))
-        return fail(ctx, RGX_E_INVALID, "null geometry tensor");
+    if (sc->n > 0 && !sc->positions) return fail(ctx, RGX_E_INVALID, "null positions");
+    if (need_geometry) {
+        if (sc->n > 0 && (!sc->scales || !sc->quaternions || !sc->densities))
+            return fail(ctx, RGX_E_INVALID, "null geometry tensor");
+        if (sc->n > 0 && !aligned16(sc->quaternions))
+            return fail(ctx, RGX_E_INVALID, "quaternions must be 16-byte aligned");
+    }
     if (need_color) {
         int k = sc->sh_coeffs;
         if (k != 1 && k != 4 && k != 9 && k != 16) return fail(ctx, RGX_E_INVALID, "sh_coeffs must be 1, 4, 9 or 16");
         if (sc->num_lobes < 0 || sc->num_lobes > kMaxLobes) return fail(ctx, RGX_E_INVALID, "num_lobes out of range");
         if (sc->n > 0 && !sc->color_features) return fail(ctx, RGX_E_INVALID, "null color_features");
+        if (sc->n > 0 && k == 16 && !aligned16(sc->color_features))
+            return fail(ctx, RGX_E_INVALID, "color_features must be 16-byte aligned when sh_coeffs is 16");
         if (sc->n > 0 && sc->num_lobes > 0 && (!sc->sg_features || !sc->sharpness || !sc->lobe_axis))
             return fail(ctx, RGX_E_INVALID, "null spherical-Gaussian tensor");
     }
@@ -338,7 +354,7 @@ int rgx_create(int device, rgx_ctx** out) {
 
 void rgx_destroy(rgx_ctx* ctx) {
     if (!ctx) return;
-    cudaSetDevice(ctx->device);
+    DeviceGuard guard(ctx->device);
     release_workspace(ctx);
     if (ctx->bin_total_host) cudaFreeHost(ctx->bin_total_host);
     if (ctx->tape_used_host) cudaFreeHost(ctx->tape_used_host);
@@ -358,12 +374,13 @@ size_t rgx_workspace_bytes(const rgx_ctx* ctx) { return ctx ? ctx->bytes : 0; }
 
 int rgx_build(rgx_ctx* ctx, const rgx_scene* scene, float sigma_threshold, int morton_bits, int curve,
               rgx_stream stream) {
+    if (!ctx) return RGX_E_INVALID;
+    DeviceGuard guard(ctx->device);
     int rc = check_scene(ctx, scene, false);
     if (rc) return rc;
     if (morton_bits != 10 && morton_bits != 20) return fail(ctx, RGX_E_INVALID, "key_bits must be 10 or 20");
     if (curve != RGX_CURVE_MORTON && curve != RGX_CURVE_HILBERT) return fail(ctx, RGX_E_INVALID, "unknown curve");
     if (!(sigma_threshold > 0.f)) return fail(ctx, RGX_E_INVALID, "sigma_threshold must be positive");
-    cudaSetDevice(ctx->device);
     cudaStream_t s = (cudaStream_t)stream;
     const int n = scene->n;
     const int n_pad = ((n + kFan - 1) / kFan) * kFan;
@@ -462,6 +479,7 @@ static int emit_setup(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, B
         RGB_(tile_first, c); RGB_(tile_last, c); RGB_(tile_cnt, c); RGB_(tile_pcnt, c); RGB_(tile_pbegin, c);
         RGB_(tile_dir, c); RGB_(tile_iota, c); RGB_(tile_cnt_sorted, c); RGB_(tile_order, c); RGB_(tile_unrecorded, c);
         ctx->bin_tiles_cap = (int)c;
+        ctx->tape_valid = false;       // tile_unrecorded belongs to the recording and has just lost its contents
     }
     // first view of a context: room for eight tiles per Gaussian; a view that needs more runs the emission twice
     if (ctx->bin_pair_cap == 0 && (e = grow_pairs(ctx, (size_t)ctx->n_pad * 8)) != cudaSuccess)
@@ -750,11 +768,12 @@ static int prepare_march(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera*
 
 static int forward_impl(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, const rgx_march* march, float* rgb,
                         float* alpha, float* depth, uchar4* frame, rgx_stream stream) {
+    if (!ctx) return RGX_E_INVALID;
+    DeviceGuard guard(ctx->device);
     MarchLaunch L{};
     int rc = prepare_march(ctx, scene, cam, march, L);
     if (rc) return rc;
     if (!rgb && !frame) return fail(ctx, RGX_E_INVALID, "colour output is null");
-    cudaSetDevice(ctx->device);
     cudaStream_t s = (cudaStream_t)stream;
     join_side(ctx, s);
     if ((rc = run_colors(ctx, scene, cam->eye, s))) return rc;
@@ -837,6 +856,7 @@ static int forward_impl(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* 
         ctx->tape_rgba_serial = ctx->rgba_serial;
         ctx->tape_build_id = ctx->build_id;
         ctx->tape_cam = *cam;
+        ctx->tape_march = *march;
         ctx->tape_row_begin = march->row_begin; ctx->tape_row_end = march->row_end;
     }
     return RGX_OK;
@@ -857,6 +877,8 @@ int rgx_forward_frame(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* ca
 
 int rgx_backward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, const rgx_march* march,
                  const float* rgb, const float* dL_drgb, const rgx_grads* grads, rgx_stream stream) {
+    if (!ctx) return RGX_E_INVALID;
+    DeviceGuard guard(ctx->device);
     MarchLaunch L{};
     int rc = prepare_march(ctx, scene, cam, march, L);
     if (rc) return rc;
@@ -864,17 +886,23 @@ int rgx_backward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, co
     if (scene->n > 0 && (!grads->positions || !grads->scales || !grads->quaternions || !grads->densities ||
                          !grads->color_features))
         return fail(ctx, RGX_E_INVALID, "null gradient tensor");
+    if (scene->n > 0 && scene->sh_coeffs == 16 && !aligned16(grads->color_features))
+        return fail(ctx, RGX_E_INVALID, "the color_features gradient must be 16-byte aligned when sh_coeffs is 16");
     if (scene->n > 0 && scene->num_lobes > 0 && (!grads->sg_features || !grads->sharpness || !grads->lobe_axis))
         return fail(ctx, RGX_E_INVALID, "null spherical-Gaussian gradient tensor");
     if (scene->n == 0) return RGX_OK;
-    cudaSetDevice(ctx->device);
     cudaStream_t s = (cudaStream_t)stream;
     join_side(ctx, s);
     // a backward that replays the recording of this very view finds the forward's per-view colours still in place
-    const bool replays = ctx->tape_valid && ctx->tape_build_id == ctx->build_id &&
-                         ctx->tape_row_begin == march->row_begin && ctx->tape_row_end == march->row_end &&
-                         std::memcmp(&ctx->tape_cam, cam, sizeof(rgx_camera)) == 0 &&
-                         !(march->flags & (RGX_FLAG_BRUTE_FORCE | RGX_FLAG_PER_RAY_SEARCH));
+    // the recording is this view's: same build, camera, rows and the march parameters that shape the slabs
+    const bool tape_matches = ctx->tape_valid && ctx->tape_build_id == ctx->build_id &&
+                              ctx->tape_row_begin == march->row_begin && ctx->tape_row_end == march->row_end &&
+                              std::memcmp(&ctx->tape_cam, cam, sizeof(rgx_camera)) == 0 &&
+                              ctx->tape_march.dt_step == march->dt_step &&
+                              ctx->tape_march.dynamic_sampling == march->dynamic_sampling &&
+                              ctx->tape_march.max_prim_slice == march->max_prim_slice &&
+                              ctx->tape_march.transmittance_eps == march->transmittance_eps;
+    const bool replays = tape_matches && !(march->flags & (RGX_FLAG_BRUTE_FORCE | RGX_FLAG_PER_RAY_SEARCH));
     if (!(replays && ctx->rgba_serial == ctx->tape_rgba_serial) && (rc = run_colors(ctx, scene, cam->eye, s))) return rc;
     cudaError_t e = cudaMemsetAsync(ctx->grad_rows, 0, sizeof(float4) * 4 * (size_t)ctx->n_pad * (size_t)ctx->grad_copies, s);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "backward memset");
@@ -882,9 +910,7 @@ int rgx_backward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, co
         if ((rc = ensure_lists(ctx, cam, march, s))) return rc;
         L.lists = ctx->lists;
     }
-    if (L.lists.ent_id && ctx->tape_valid && ctx->tape_build_id == ctx->build_id &&
-        ctx->tape_row_begin == march->row_begin && ctx->tape_row_end == march->row_end &&
-        std::memcmp(&ctx->tape_cam, cam, sizeof(rgx_camera)) == 0) {
+    if (L.lists.ent_id && tape_matches) {
         L.tape = ctx->tape; L.tape_used = ctx->tape_used; L.tape_cap = ctx->tape_cap; L.ray_head = ctx->ray_head;
         L.tile_unrecorded = ctx->tile_unrecorded;
         L.replay_order = ctx->tape_tile_order;
@@ -933,11 +959,14 @@ int rgx_hint_next_view(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* mar
 
 int rgx_lists_made_ahead(const rgx_ctx* ctx) { return ctx ? ctx->prefetched : 0; }
 
+unsigned long long rgx_kernel_launches(void) { return rgx::g_launches.load(std::memory_order_relaxed); }
+
 int rgx_gaussian_colors(rgx_ctx* ctx, const rgx_scene* scene, const float eye[3], float* rgb_out, rgx_stream stream) {
-    int rc = check_scene(ctx, scene, true);
+    if (!ctx) return RGX_E_INVALID;
+    DeviceGuard guard(ctx->device);
+    int rc = check_scene(ctx, scene, true, false);
     if (rc) return rc;
     if (!eye || (!rgb_out && scene->n > 0)) return fail(ctx, RGX_E_INVALID, "null argument");
-    cudaSetDevice(ctx->device);
     ColorLaunch c{};
     c.sc = *scene;
     std::memcpy(c.eye, eye, sizeof(c.eye));
@@ -950,9 +979,9 @@ int rgx_gaussian_colors(rgx_ctx* ctx, const rgx_scene* scene, const float eye[3]
 
 int rgx_scene_box(rgx_ctx* ctx, float bb_min[3], float bb_max[3], rgx_stream stream) {
     if (!ctx || !bb_min || !bb_max) return RGX_E_INVALID;
-    if (ctx->alloc_failed) { cudaSetDevice(ctx->device); release_workspace(ctx); }
+    DeviceGuard guard(ctx->device);
+    if (ctx->alloc_failed) release_workspace(ctx);
     if (!ctx->built) return fail(ctx, RGX_E_NOT_BUILT, "rgx_build has not been called");
-    cudaSetDevice(ctx->device);
     SceneBox h;
     cudaError_t e = cudaMemcpyAsync(&h, ctx->box, sizeof(h), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
@@ -996,7 +1025,7 @@ int rgx_set_profiling(rgx_ctx* ctx, int enable) {
 int rgx_read_kernel_times(rgx_ctx* ctx, float* forward_ms, int* forward_launches, float* backward_ms,
                           int* backward_launches) {
     if (!ctx || !forward_ms || !forward_launches || !backward_ms || !backward_launches) return RGX_E_INVALID;
-    cudaSetDevice(ctx->device);
+    DeviceGuard guard(ctx->device);
     float sum[3] = {0.f, 0.f, 0.f};
     int cnt[3] = {0, 0, 0};
     for (auto& t : ctx->timed) {
@@ -1029,7 +1058,7 @@ int rgx_read_binning(rgx_ctx* ctx, float* ms, int* runs, long long* last_pairs) 
 
 int rgx_reset_counters(rgx_ctx* ctx, rgx_stream stream) {
     if (!ctx) return RGX_E_INVALID;
-    cudaSetDevice(ctx->device);
+    DeviceGuard guard(ctx->device);
     int rc = ensure_workspace(ctx, ctx->cap_n_pad, ctx->cap_boxes);
     if (rc) return rc;
     cudaError_t e = cudaMemsetAsync(ctx->counters, 0, sizeof(DeviceCounters), (cudaStream_t)stream);
@@ -1038,7 +1067,7 @@ int rgx_reset_counters(rgx_ctx* ctx, rgx_stream stream) {
 
 int rgx_read_counters(rgx_ctx* ctx, rgx_counters* out, rgx_stream stream) {
     if (!ctx || !out) return RGX_E_INVALID;
-    cudaSetDevice(ctx->device);
+    DeviceGuard guard(ctx->device);
     int rc = ensure_workspace(ctx, ctx->cap_n_pad, ctx->cap_boxes);
     if (rc) return rc;
     static_assert(sizeof(rgx_counters) == sizeof(DeviceCounters), "counter layouts must match");

@@ -586,9 +586,9 @@ cudaError_t launch_bin_emit(const BinLaunch& b, cudaStream_t s) {
     cudaError_t e;
     // total_dev: [0] pairs, [1] length of the list of large Gaussians, [2] next of them to take
     if ((e = cudaMemsetAsync(b.total_dev, 0, 4 * sizeof(unsigned long long), s)) != cudaSuccess) return e;
-    bin_tile_dirs_kernel<<<(ntiles + tb - 1) / tb, tb, 0, s>>>(b, ntiles);
-    bin_emit_kernel<<<(b.n_pad + kEmitThreads - 1) / kEmitThreads, kEmitThreads, 0, s>>>(b);
-    bin_emit_big_kernel<<<b.big_grid, kBigWarps * 32, 0, s>>>(b);
+    note_launch(), bin_tile_dirs_kernel<<<(ntiles + tb - 1) / tb, tb, 0, s>>>(b, ntiles);
+    note_launch(), bin_emit_kernel<<<(b.n_pad + kEmitThreads - 1) / kEmitThreads, kEmitThreads, 0, s>>>(b);
+    note_launch(), bin_emit_big_kernel<<<b.big_grid, kBigWarps * 32, 0, s>>>(b);
     return cudaGetLastError();
 }
 
@@ -607,9 +607,9 @@ cudaError_t launch_bin_fill(const BinLaunch& b, int total, cudaStream_t s) {
         e = cub::DeviceRadixSort::SortPairs(b.cub_temp, temp, b.keys_in, b.keys_out, b.vals_in, b.vals_out, (int64_t)total, 0,
                                             kl.tile_bits + kl.near_bits + kl.id_bits, s);
         if (e != cudaSuccess) return e;
-        bin_ranges_kernel<<<(total + tb - 1) / tb, tb, 0, s>>>(b, total, kl.near_bits + kl.id_bits);
+        note_launch(), bin_ranges_kernel<<<(total + tb - 1) / tb, tb, 0, s>>>(b, total, kl.near_bits + kl.id_bits);
     }
-    bin_tile_counts_kernel<<<(ntiles + tb - 1) / tb, tb, 0, s>>>(b, ntiles);
+    note_launch(), bin_tile_counts_kernel<<<(ntiles + tb - 1) / tb, tb, 0, s>>>(b, ntiles);
     temp = b.cub_bytes;
     if ((e = cub::DeviceScan::ExclusiveSum(b.cub_temp, temp, b.tile_pcnt, b.tile_pbegin, ntiles + 1, s)) != cudaSuccess) return e;
     // CTAs take the tiles with the longest lists first: the march ends with short tiles, not with one long one
@@ -617,10 +617,10 @@ cudaError_t launch_bin_fill(const BinLaunch& b, int total, cudaStream_t s) {
     if ((e = cub::DeviceRadixSort::SortPairsDescending(b.cub_temp, temp, b.tile_cnt, b.tile_cnt_sorted, b.tile_iota, b.tile_order,
                                                        ntiles, 0, 32, s)) != cudaSuccess) return e;
     const size_t n_entries = (((size_t)total + 32u * (size_t)ntiles + 31) / 32) * 32;   // upper bound of the padded layout
-    bin_fill_kernel<<<(unsigned)((n_entries + tb - 1) / tb), tb, 0, s>>>(b, n_entries);
-    if (total > 0) bin_scatter_kernel<<<(total + tb - 1) / tb, tb, 0, s>>>(b, total, kl);
+    note_launch(), bin_fill_kernel<<<(unsigned)((n_entries + tb - 1) / tb), tb, 0, s>>>(b, n_entries);
+    if (total > 0) note_launch(), bin_scatter_kernel<<<(total + tb - 1) / tb, tb, 0, s>>>(b, total, kl);
     const size_t n_blocks = (n_entries + 31) / 32;
-    bin_blocks_kernel<<<(unsigned)((n_blocks + 7) / 8), 256, 0, s>>>(b, n_blocks);
+    note_launch(), bin_blocks_kernel<<<(unsigned)((n_blocks + 7) / 8), 256, 0, s>>>(b, n_blocks);
     return cudaGetLastError();
 }
 
@@ -628,7 +628,7 @@ cudaError_t launch_bin_fill(const BinLaunch& b, int total, cudaStream_t s) {
 cudaError_t launch_bin_hist(const BinLaunch& b, int total, unsigned int* hist, cudaStream_t s) {
     const KeyLayout kl = key_layout(b.tiles_x * ((b.cam.height + b.tile - 1) / b.tile), b.n_pad);
     if (kl.near_bits < kHistBits) return cudaErrorInvalidValue;
-    if (total > 0) bin_hist_kernel<<<592, 256, 0, s>>>(b.keys_in, total, kl.id_bits + kl.near_bits - kHistBits, hist);
+    if (total > 0) note_launch(), bin_hist_kernel<<<592, 256, 0, s>>>(b.keys_in, total, kl.id_bits + kl.near_bits - kHistBits, hist);
     return cudaGetLastError();
 }
 
@@ -648,8 +648,8 @@ cudaError_t launch_bin_select(const BinLaunch& b, int total, int mode, unsigned 
     const KeyLayout kl = key_layout(b.tiles_x * ((b.cam.height + b.tile - 1) / b.tile), b.n_pad);
     if (total <= 0) return cudaSuccess;
     const int blocks = (int)(((long long)total + 2047) / 2048);
-    if (mode == 0) bin_select_kernel<0><<<blocks, 256, 0, s>>>(b.keys_in, b.vals_in, total, kl, cut, tile_flag, out_k, out_v, counter, tile_more);
-    else bin_select_kernel<1><<<blocks, 256, 0, s>>>(b.keys_in, b.vals_in, total, kl, cut, tile_flag, out_k, out_v, counter, tile_more);
+    if (mode == 0) note_launch(), bin_select_kernel<0><<<blocks, 256, 0, s>>>(b.keys_in, b.vals_in, total, kl, cut, tile_flag, out_k, out_v, counter, tile_more);
+    else note_launch(), bin_select_kernel<1><<<blocks, 256, 0, s>>>(b.keys_in, b.vals_in, total, kl, cut, tile_flag, out_k, out_v, counter, tile_more);
     return cudaGetLastError();
 }
 

@@ -248,21 +248,21 @@ size_t build_cub_temp_bytes(int n_pad) {
 cudaError_t launch_build(const BuildLaunch& b, cudaStream_t s) {
     const int n = b.sc.n;
     const int tb = 256;
-    init_bounds_kernel<<<1, 32, 0, s>>>(b.bounds);
-    bounds_kernel<<<(n + tb - 1) / tb, tb, 0, s>>>(b);
-    morton_kernel<<<(n + tb - 1) / tb, tb, 0, s>>>(b);
+    note_launch(), init_bounds_kernel<<<1, 32, 0, s>>>(b.bounds);
+    note_launch(), bounds_kernel<<<(n + tb - 1) / tb, tb, 0, s>>>(b);
+    note_launch(), morton_kernel<<<(n + tb - 1) / tb, tb, 0, s>>>(b);
     size_t temp = b.cub_temp_bytes;
     cudaError_t e = cub::DeviceRadixSort::SortPairs(b.cub_temp, temp, b.keys_in, b.keys_out, b.vals_in, b.vals_out, n,
                                                     0, 3 * b.morton_bits, s);
     if (e != cudaSuccess) return e;
-    gather_kernel<<<(b.n_pad + tb - 1) / tb, tb, 0, s>>>(b);
+    note_launch(), gather_kernel<<<(b.n_pad + tb - 1) / tb, tb, 0, s>>>(b);
     int total = b.offset[b.num_levels - 1] + ((b.count[b.num_levels - 1] + kFan - 1) / kFan) * kFan;
     int upper = total - b.offset[1];
-    fill_inverted_kernel<<<(upper + tb - 1) / tb, tb, 0, s>>>(b.bx, b.by, b.bz, b.offset[1], total);
+    note_launch(), fill_inverted_kernel<<<(upper + tb - 1) / tb, tb, 0, s>>>(b.bx, b.by, b.bz, b.offset[1], total);
     e = cudaMemsetAsync(b.refit_counters, 0, sizeof(unsigned int) * (size_t)total, s);
     if (e != cudaSuccess) return e;
     int warps = b.count[1];
-    refit_kernel<<<(warps + 7) / 8, 256, 0, s>>>(b);
+    note_launch(), refit_kernel<<<(warps + 7) / 8, 256, 0, s>>>(b);
     return cudaGetLastError();
 }
 

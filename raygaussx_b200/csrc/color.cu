@@ -265,7 +265,7 @@ __global__ void __launch_bounds__(128) finalize_kernel(FinalizeLaunch f) {
 cudaError_t launch_colors(const ColorLaunch& c, cudaStream_t s) {
     int slots = c.perm ? ((c.sc.n + 31) / 32) * 32 : c.sc.n;
     if (slots == 0) return cudaSuccess;
-    colors_kernel<<<(slots + 127) / 128, 128, 0, s>>>(c);
+    note_launch(), colors_kernel<<<(slots + 127) / 128, 128, 0, s>>>(c);
     return cudaGetLastError();
 }
 
@@ -283,7 +283,7 @@ cudaError_t launch_finalize(const FinalizeLaunch& f, cudaStream_t s) {
             if (e != cudaSuccess) return e;
         }
     }
-    finalize_kernel<<<(f.sc.n + 127) / 128, 128, 0, s>>>(f);
+    note_launch(), finalize_kernel<<<(f.sc.n + 127) / 128, 128, 0, s>>>(f);
     return cudaGetLastError();
 }
 

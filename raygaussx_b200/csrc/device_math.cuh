@@ -16,16 +16,20 @@ __device__ __forceinline__ float3 cross3(float3 a, float3 b) {
 
 // Columns (U, V, W) of the rotation given by the un-normalised quaternion formula
 // the reference uses for intersection and marching
-// (cuda_train/forward/gaussians_aabb.cu:7-17); q = (r, i, j, k) = (w, x, y, z).
+// (cuda_train/forward/gaussians_aabb.cu:7-17); q = (w, x, y, z) with vector part v = (x, y, z).
+// Written as R = I - (tr(S) I - S) + A with the symmetric part S = 2 v v^T and the antisymmetric part
+// A = 2 w [v]_x, which for a unit quaternion is the usual rotation and for any other the same
+// polynomial the reference evaluates.
 __device__ __forceinline__ void quat_to_columns(float4 q, float3& U, float3& V, float3& W) {
-    const float r = q.x, i = q.y, j = q.z, k = q.w;
-    const float ii = i + i, jj = j + j, kk = k + k;
-    const float ri = r * ii, rj = r * jj, rk = r * kk;
-    const float ii2 = i * ii, jj2 = j * jj, kk2 = k * kk;
-    const float ij = i * jj, ik = i * kk, jk = j * kk;
-    U = make_float3(1.f - (jj2 + kk2), ij + rk, ik - rj);
-    V = make_float3(ij - rk, 1.f - (ii2 + kk2), jk + ri);
-    W = make_float3(ik + rj, jk - ri, 1.f - (ii2 + jj2));
+    const float w = q.x;
+    const float3 v = make_float3(q.y, q.z, q.w);
+    const float3 v2 = make_float3(v.x + v.x, v.y + v.y, v.z + v.z);
+    const float3 diag = make_float3(v.x * v2.x, v.y * v2.y, v.z * v2.z);       // S_xx, S_yy, S_zz
+    const float3 off = make_float3(v.y * v2.z, v.x * v2.z, v.x * v2.y);        // S_yz, S_xz, S_xy
+    const float3 anti = make_float3(w * v2.x, w * v2.y, w * v2.z);             // A_zy, A_xz, A_yx
+    U = make_float3(1.f - (diag.y + diag.z), off.z + anti.z, off.y - anti.y);
+    V = make_float3(off.z - anti.z, 1.f - (diag.x + diag.z), off.x + anti.x);
+    W = make_float3(off.y + anti.y, off.x - anti.x, 1.f - (diag.x + diag.y));
 }
 
 // Gradient of the same formula w.r.t. q given the gradients of the three columns

@@ -191,7 +191,8 @@ extern "C" RGX_API int rgx_knn_mean_dist2(int device, const float* points, int n
     if (n < 0 || (n > 0 && (!points || !mean_dist2))) return RGX_E_INVALID;
     if (n > (1 << 30)) return RGX_E_TOO_LARGE;
     if (n == 0) return RGX_OK;
-    if (cudaSetDevice(device) != cudaSuccess) return RGX_E_CUDA;
+    DeviceGuard guard(device);
+    if (!guard.ok) { (void)cudaGetLastError(); return RGX_E_CUDA; }
     cudaStream_t s = (cudaStream_t)stream;
     const int n_pad = ((n + 1023) / 1024) * 1024;
     const int n_boxes = n_pad / 32, n_upper = n_boxes / 32;
@@ -206,14 +207,14 @@ extern "C" RGX_API int rgx_knn_mean_dist2(int device, const float* points, int n
     e = grab(up_hi, n_upper, e); e = grab(temp, temp_bytes, e);
     if (e == cudaSuccess) {
         const int tb = 256;
-        knn_init_kernel<<<1, 32, 0, s>>>(bounds);
-        knn_bounds_kernel<<<(n + tb - 1) / tb, tb, 0, s>>>(points, n, bounds);
-        knn_keys_kernel<<<(n + tb - 1) / tb, tb, 0, s>>>(points, n, bounds, keys_in, vals_in);
+        note_launch(), knn_init_kernel<<<1, 32, 0, s>>>(bounds);
+        note_launch(), knn_bounds_kernel<<<(n + tb - 1) / tb, tb, 0, s>>>(points, n, bounds);
+        note_launch(), knn_keys_kernel<<<(n + tb - 1) / tb, tb, 0, s>>>(points, n, bounds, keys_in, vals_in);
         e = cub::DeviceRadixSort::SortPairs(temp, temp_bytes, keys_in, keys_out, vals_in, vals_out, n, 0, 30, s);
         if (e == cudaSuccess) {
-            knn_gather_kernel<<<(n_pad + tb - 1) / tb, tb, 0, s>>>(points, n, n_pad, vals_out, sorted, box_lo, box_hi);
-            knn_upper_kernel<<<(n_upper * 32 + tb - 1) / tb, tb, 0, s>>>(box_lo, box_hi, n_boxes, up_lo, up_hi);
-            knn_query_kernel<<<(n_boxes * 32 + tb - 1) / tb, tb, 0, s>>>(sorted, vals_out, n, n_boxes, n_upper, box_lo, box_hi,
+            note_launch(), knn_gather_kernel<<<(n_pad + tb - 1) / tb, tb, 0, s>>>(points, n, n_pad, vals_out, sorted, box_lo, box_hi);
+            note_launch(), knn_upper_kernel<<<(n_upper * 32 + tb - 1) / tb, tb, 0, s>>>(box_lo, box_hi, n_boxes, up_lo, up_hi);
+            note_launch(), knn_query_kernel<<<(n_boxes * 32 + tb - 1) / tb, tb, 0, s>>>(sorted, vals_out, n, n_boxes, n_upper, box_lo, box_hi,
                                                                       up_lo, up_hi, mean_dist2);
             e = cudaGetLastError();
         }

@@ -19,8 +19,8 @@
 
 // This file holds the per-ray variant: every query searches the hierarchy (or,
 // for validation, every Gaussian) on its own.  It is the general path -- it makes
-// no assumption about neighbouring rays -- and the one the tiled kernels fall
-// back to when a tile's shared candidate list does not fit.
+// no assumption about neighbouring rays and needs no per-view lists -- selected by
+// RGX_FLAG_PER_RAY_SEARCH / RGX_FLAG_BRUTE_FORCE and used by rgx_forward_static.
 
 namespace rgx {
 
@@ -167,10 +167,10 @@ cudaError_t launch_march_forward_per_ray(const MarchLaunch& m, cudaStream_t s) {
     int grid = grid_for(m);
     if (grid == 0) return cudaSuccess;
     bool count = (m.m.flags & RGX_FLAG_COUNT_WORK) != 0, brute = (m.m.flags & RGX_FLAG_BRUTE_FORCE) != 0;
-    if (count && brute) march_forward_kernel<true, true><<<grid, kWarps * 32, 0, s>>>(m);
-    else if (count) march_forward_kernel<true, false><<<grid, kWarps * 32, 0, s>>>(m);
-    else if (brute) march_forward_kernel<false, true><<<grid, kWarps * 32, 0, s>>>(m);
-    else march_forward_kernel<false, false><<<grid, kWarps * 32, 0, s>>>(m);
+    if (count && brute) note_launch(), march_forward_kernel<true, true><<<grid, kWarps * 32, 0, s>>>(m);
+    else if (count) note_launch(), march_forward_kernel<true, false><<<grid, kWarps * 32, 0, s>>>(m);
+    else if (brute) note_launch(), march_forward_kernel<false, true><<<grid, kWarps * 32, 0, s>>>(m);
+    else note_launch(), march_forward_kernel<false, false><<<grid, kWarps * 32, 0, s>>>(m);
     return cudaGetLastError();
 }
 
@@ -178,8 +178,8 @@ cudaError_t launch_march_backward_per_ray(const MarchLaunch& m, cudaStream_t s) 
     int grid = grid_for(m);
     if (grid == 0) return cudaSuccess;
     bool brute = (m.m.flags & RGX_FLAG_BRUTE_FORCE) != 0;
-    if (brute) march_backward_kernel<true><<<grid, kWarps * 32, 0, s>>>(m);
-    else march_backward_kernel<false><<<grid, kWarps * 32, 0, s>>>(m);
+    if (brute) note_launch(), march_backward_kernel<true><<<grid, kWarps * 32, 0, s>>>(m);
+    else note_launch(), march_backward_kernel<false><<<grid, kWarps * 32, 0, s>>>(m);
     return cudaGetLastError();
 }
 

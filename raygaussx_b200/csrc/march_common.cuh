@@ -14,7 +14,7 @@ constexpr int kWarps = 8;
 constexpr int kStack = 192;
 constexpr int kStage = 64;
 constexpr unsigned kFull = 0xffffffffu;
-constexpr int kTile = 8;   // CTA = 8x8 pixels; warp w marches column w of the tile
+constexpr int kTile = 8;   // per-ray variant (march.cu): a CTA marches 8x8 pixels, warp w takes column w
 // Unrolling of the evaluation loop over staged hits (recording forward of the 3 M-Gaussian view: 1: 13.1 ms,
 // 2: 11.9, 3: 11.9, 4: 11.8, 8: 11.8 -- but slabs with a handful of hits then run in the remainder loop).
 #ifndef RGX_EVAL_UNROLL

@@ -716,13 +716,13 @@ cudaError_t launch_march_forward(const MarchLaunch& m, cudaStream_t s) {
     if (grid <= 0) return cudaSuccess;
     const bool count = (m.m.flags & RGX_FLAG_COUNT_WORK) != 0, save = m.tape != nullptr;
     if (m.hz_phase != 0) {
-        march_forward_lists_kernel<false, false, true><<<grid, kThreads, 0, s>>>(m);
+        note_launch(), march_forward_lists_kernel<false, false, true><<<grid, kThreads, 0, s>>>(m);
         return cudaGetLastError();
     }
-    if (count && save) march_forward_lists_kernel<true, true><<<grid, kThreads, 0, s>>>(m);
-    else if (count) march_forward_lists_kernel<true, false><<<grid, kThreads, 0, s>>>(m);
-    else if (save) march_forward_lists_kernel<false, true><<<grid, kThreads, 0, s>>>(m);
-    else march_forward_lists_kernel<false, false><<<grid, kThreads, 0, s>>>(m);
+    if (count && save) note_launch(), march_forward_lists_kernel<true, true><<<grid, kThreads, 0, s>>>(m);
+    else if (count) note_launch(), march_forward_lists_kernel<true, false><<<grid, kThreads, 0, s>>>(m);
+    else if (save) note_launch(), march_forward_lists_kernel<false, true><<<grid, kThreads, 0, s>>>(m);
+    else note_launch(), march_forward_lists_kernel<false, false><<<grid, kThreads, 0, s>>>(m);
     return cudaGetLastError();
 }
 
@@ -730,7 +730,7 @@ cudaError_t launch_march_backward_search(const MarchLaunch& m, cudaStream_t s) {
     if (!use_lists(m)) return launch_march_backward_per_ray(m, s);
     const int grid = m.lists.tiles_x * m.lists.tiles_y;
     if (grid <= 0) return cudaSuccess;
-    march_backward_lists_kernel<<<grid, kThreads, 0, s>>>(m);   // a CTA whose tile was recorded completely returns at once
+    note_launch(), march_backward_lists_kernel<<<grid, kThreads, 0, s>>>(m);   // a CTA whose tile was recorded completely returns at once
     return cudaGetLastError();
 }
 
@@ -738,8 +738,8 @@ cudaError_t launch_march_backward_replay(const MarchLaunch& m, cudaStream_t s) {
     if (!use_lists(m) || !m.tape) return cudaSuccess;
     const int grid = m.lists.tiles_x * m.lists.tiles_y;
     if (grid <= 0) return cudaSuccess;
-    if (m.replay_batched) march_backward_replay_kernel<kBatch><<<grid, kThreads, 0, s>>>(m);
-    else march_backward_replay_kernel<1><<<grid, kThreads, 0, s>>>(m);
+    if (m.replay_batched) note_launch(), march_backward_replay_kernel<kBatch><<<grid, kThreads, 0, s>>>(m);
+    else note_launch(), march_backward_replay_kernel<1><<<grid, kThreads, 0, s>>>(m);
     return cudaGetLastError();
 }
 

@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 
 #include "../../include/rgx.h"
+#include "rgx_internal.cuh"
 
 namespace {
 
@@ -55,7 +56,8 @@ extern "C" int rgx_measure_peaks(int device, float* fma_tflops, float* ex2_gops)
     *ex2_gops = 0.f;
     int count = 0, sms = 0;
     if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) return RGX_E_CUDA;
-    if (cudaSetDevice(device) != cudaSuccess ||
+    rgx::DeviceGuard guard(device);
+    if (!guard.ok ||
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
         return RGX_E_CUDA;
     float* sink = nullptr;
@@ -71,13 +73,13 @@ extern "C" int rgx_measure_peaks(int device, float* fma_tflops, float* ex2_gops)
         bool ok = true;
         for (int rep = 0; rep < 2 && ok; ++rep) {           // the first repetition warms up
             cudaEventRecord(e0, s);
-            fma_chain_kernel<<<grid, kThreads, 0, s>>>(0.999f, 1e-4f, fma_iters, sink);
+            rgx::note_launch(), fma_chain_kernel<<<grid, kThreads, 0, s>>>(0.999f, 1e-4f, fma_iters, sink);
             cudaEventRecord(e1, s);
             ok = cudaStreamSynchronize(s) == cudaSuccess && cudaEventElapsedTime(&ms_fma, e0, e1) == cudaSuccess;
         }
         for (int rep = 0; rep < 2 && ok; ++rep) {
             cudaEventRecord(e0, s);
-            ex2_chain_kernel<<<grid, kThreads, 0, s>>>(ex2_iters, sink);
+            rgx::note_launch(), ex2_chain_kernel<<<grid, kThreads, 0, s>>>(ex2_iters, sink);
             cudaEventRecord(e1, s);
             ok = cudaStreamSynchronize(s) == cudaSuccess && cudaEventElapsedTime(&ms_ex2, e0, e1) == cudaSuccess;
         }

@@ -13,6 +13,22 @@ constexpr int kSlab = 32;         // samples per slab  (BUFFER_SIZE, cuda_train/
 constexpr int kChunk = 16;        // samples per chunk (CHUNK_SIZE, :3)
 constexpr int kMaxLobes = 8;
 
+// Pointers that kernels read or write 16 bytes at a time (float4) must start on a 16-byte boundary.
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Makes `device` current for the duration of an entry point and puts the caller's device back afterwards.
+struct DeviceGuard {
+    int prev = -1, dev;
+    bool ok;
+    explicit DeviceGuard(int device) : dev(device) {
+        if (cudaGetDevice(&prev) != cudaSuccess) { prev = -1; (void)cudaGetLastError(); }
+        ok = prev == device || cudaSetDevice(device) == cudaSuccess;
+    }
+    ~DeviceGuard() { if (prev >= 0 && prev != dev) cudaSetDevice(prev); }
+    DeviceGuard(const DeviceGuard&) = delete;
+    DeviceGuard& operator=(const DeviceGuard&) = delete;
+};
+
 // Hierarchy over the Morton-sorted Gaussians.  Level 0 holds one box per Gaussian,
 // node j of level l+1 bounds boxes [32j, 32j+32) of level l.  All levels live in
 // one set of arrays; every level is padded to a multiple of 32 entries with
@@ -43,11 +59,11 @@ struct SortedGaussians {
 };
 
 struct DeviceCounters {   // mirrors rgx_counters
-    unsigned long long v[24];
+    unsigned long long v[20];
 };
 enum { C_RAYS, C_SLABS, C_SLABS_HIT, C_CLOSEST, C_HITS, C_PAIRS, C_OVF, C_NODE_TESTS, C_PRIM_TESTS, C_ELL_TESTS,
-       C_STACK_OVF, C_HASH, C_WINDOWS, C_RETRIES, C_FALLBACKS, C_CANDS, C_CYC_WINDOW, C_CYC_SEEK, C_CYC_SEARCH,
-       C_CYC_EVAL, C_CYC_COMP, C_CYC_WAIT, C_CYC_TOTAL, C_RESERVED, C_NUM };
+       C_STACK_OVF, C_HASH, C_CANDS, C_CYC_WINDOW, C_CYC_SEEK, C_CYC_SEARCH,
+       C_CYC_EVAL, C_CYC_COMP, C_CYC_WAIT, C_CYC_TOTAL, C_NUM };
 
 struct SceneBox {         // written by the build, read by the march kernels
     float lo[3];
@@ -167,6 +183,9 @@ struct BuildLaunch {
     int count[kMaxLevels];
     void* cub_temp; size_t cub_temp_bytes;
 };
+
+// Counts the kernels of this library that were launched by this process (rgx_kernel_launches).
+void note_launch();
 
 // host launchers (each returns the cudaError_t of its last launch)
 cudaError_t launch_build(const BuildLaunch& b, cudaStream_t s);

@@ -105,6 +105,8 @@ extern "C" RGX_API int rgx_forward_static(int device, const rgx_scene* scene, co
         return RGX_E_INVALID;
     if (n > 0 && scene->num_lobes > 0 && (!scene->sg_features || !scene->sharpness || !scene->lobe_axis))
         return RGX_E_INVALID;
+    // loaded 16 bytes at a time by the kernels
+    if (n > 0 && (!aligned16(scene->quaternions) || (k == 16 && !aligned16(scene->color_features)))) return RGX_E_INVALID;
     if (cam->width <= 0 || cam->height <= 0 || (long long)cam->width * cam->height > (1ll << 30)) return RGX_E_INVALID;
     if (!(march->dt_step > 0.f) || march->max_prim_slice <= 0 || !(march->transmittance_eps >= 0.f) ||
         march->row_begin < 0 || march->row_end > cam->height || march->row_begin > march->row_end ||
@@ -112,7 +114,8 @@ extern "C" RGX_API int rgx_forward_static(int device, const rgx_scene* scene, co
         return RGX_E_INVALID;
     if (march->flags & RGX_FLAG_COUNT_WORK) return RGX_E_INVALID;   // counters live in a context's workspace
 
-    if (cudaSetDevice(device) != cudaSuccess) return RGX_E_CUDA;
+    DeviceGuard guard(device);       // the caller's current device is put back on return
+    if (!guard.ok) { (void)cudaGetLastError(); return RGX_E_CUDA; }
     unsigned char* base = nullptr;
     int rc = scratch_for(device, &base);
     if (rc != RGX_OK) return rc;

@@ -86,7 +86,10 @@ def _as_input(t: torch.Tensor, name: str) -> torch.Tensor:
         raise ValueError(f"{name} must be a CUDA tensor (there is no CPU path)")
     if t.dtype != torch.float32:
         raise ValueError(f"{name} must be float32, got {t.dtype}")
-    return t.detach().contiguous()
+    t = t.detach().contiguous()
+    if t.data_ptr() % 16:            # a row slice of a larger buffer: the kernels load 16 bytes at a time (rgx.h)
+        t = t.clone()
+    return t
 
 
 def camera_struct(cam, supersampling=(1, 1)) -> _Camera:
@@ -130,6 +133,8 @@ class Renderer:
             raise _lib.RgxError(rc, "rgx_create failed")
         self._ctx = h
         self._n_built = -1
+        self._build_serial = 0       # counts the builds of this context
+        self._built_from = None      # the four geometry tensors of the latest build, kept alive (see geometry_is_built)
 
     def __del__(self):
         try:
@@ -186,6 +191,20 @@ class Renderer:
         _lib.check(self._ctx, self._lib.rgx_build(self._ctx, C.byref(sc), float(sigma_threshold), int(morton_bits),
                                                   int(curve), self._stream()))
         self._n_built = positions.shape[0]
+        self._build_serial += 1
+        tensors = (positions, scales, quaternions, densities)
+        self._built_from = (tensors, tuple((t.data_ptr(), t._version, tuple(t.shape)) for t in tensors))
+
+    def geometry_is_built(self, positions, scales, quaternions, densities) -> bool:
+        """True when the latest build was made from these very tensors and none of them has been written to
+        since: same storage, same shape, same version counter.  The build keeps its tensors alive, so an equal
+        address cannot belong to a new tensor that merely landed in recycled memory.  (Tensors recomputed from
+        unchanged parameters -- ``exp`` of the log-scales, say -- are new tensors and count as changed; writes
+        through ``tensor.data`` bypass the version counter here as they do for autograd.)"""
+        if self._built_from is None:
+            return False
+        return self._built_from[1] == tuple((t.data_ptr(), t._version, tuple(t.shape))
+                                            for t in (positions, scales, quaternions, densities))
 
     def forward(self, positions, scales, quaternions, densities, color_features, sg_features, sharpness, lobe_axis,
                 cam: _Camera, march: _March, want_alpha=False, want_depth=False, out=None):
@@ -306,14 +325,17 @@ class RenderOptixFunction(torch.autograd.Function):
         cam = camera_struct(settings.viewpoint_cam, settings.supersampling)
         # The reference rebuilds its acceleration structure in every forward
         # (scripts/train.py:117 passes update=False; update=True refits).  Same here,
-        # unless the caller vouches that the geometry is unchanged.
-        if not getattr(settings, "reuse_acceleration_structure", False) or r._n_built != tensors[0].shape[0]:
+        # unless the geometry tensors are the very ones of the latest build, untouched
+        # since, or the caller vouches that their values are unchanged.
+        vouched = getattr(settings, "reuse_acceleration_structure", False) and r._n_built == tensors[0].shape[0]
+        if not (vouched or r.geometry_is_built(*tensors[:4])):
             r.build(*tensors[:4], sigma_threshold=SIGMA_THRESHOLD,
                     morton_bits=getattr(settings, "morton_bits", 10))
         # keep what the rays met, so that the backward of this view does not have to search again
         march = _settings_march(settings, cam, flags=_lib.FLAG_SAVE_HITS, rows=getattr(settings, "rows", None))
         rgb, _, _ = r.forward(*tensors, cam, march)
         ctx.settings = settings
+        ctx.build_serial = r._build_serial
         ctx.save_for_backward(*tensors, rgb)
         return rgb
 
@@ -327,6 +349,11 @@ class RenderOptixFunction(torch.autograd.Function):
         flags = _lib.FLAG_EXACT_SH_GRAD if getattr(settings, "exact_sh_grad", False) else 0
         march = _settings_march(settings, cam, flags=flags, rows=getattr(settings, "rows", None))
         grads = [torch.empty_like(t) for t in tensors]
+        if r._build_serial != ctx.build_serial:
+            # another build came between this view's forward and its backward (a second model, an evaluation copy,
+            # a finite-difference probe): the backward reads the geometry of the latest build, so build again from
+            # the tensors this forward saw.  The forward's recording belonged to the old build: the rays are searched.
+            r.build(*tensors[:4], sigma_threshold=SIGMA_THRESHOLD, morton_bits=getattr(settings, "morton_bits", 10))
         nxt = getattr(settings, "next_viewpoint_cam", None)      # same Gaussians, next view of an accumulation step
         if nxt is not None:
             ncam = camera_struct(nxt, settings.supersampling)

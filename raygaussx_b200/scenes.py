@@ -68,6 +68,34 @@ class SimpleCamera:
         return self
 
 
+def crop_camera(cam, x0, y0, width, height):
+    """A camera whose ``width`` x ``height`` image is the window of ``cam``'s image that starts at pixel
+    ``(x0, y0)``: same eye and axes, the field of view narrowed and the principal point moved so that ray
+    ``(x, y)`` of the crop is ray ``(x0 + x, y0 + y)`` of ``cam`` (the camera model of
+    cuda_train/forward/gaussians_aabb.cu:95-110 expresses this exactly; the rays agree to fp32 rounding)."""
+    import copy
+    c = copy.copy(cam)
+    w_full, h_full = cam.image_width, cam.image_height
+    c.FoVx = 2.0 * math.atan(math.tan(cam.FoVx / 2) * width / w_full)
+    c.FoVy = 2.0 * math.atan(math.tan(cam.FoVy / 2) * height / h_full)
+    c.Px = (cam.Px * w_full - x0) / width
+    c.Py = (cam.Py * h_full - y0) / height
+    c.image_width, c.image_height = int(width), int(height)
+    if hasattr(c, "_rgx_camera"):
+        del c._rgx_camera
+    return c
+
+
+def lowres_camera(cam, width, height):
+    """``cam`` with a coarser image: same eye, axes, field of view and principal point, ``width`` x ``height`` rays."""
+    import copy
+    c = copy.copy(cam)
+    c.image_width, c.image_height = int(width), int(height)
+    if hasattr(c, "_rgx_camera"):
+        del c._rgx_camera
+    return c
+
+
 @dataclass
 class Scene:
     positions: torch.Tensor

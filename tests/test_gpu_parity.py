@@ -2,10 +2,13 @@
 
 Every call goes through the C ABI of librgx.so (ctypes), the same way the autograd
 entry point does.  Tolerances: max abs error 1e-4 on RGB and alpha, relative error
-1e-3 on gradients (max |a-b| / max |a| per tensor), identical hit sets between the
-tiled, per-ray and exhaustive searches.  Colour comparisons skip rays whose discrete
-decisions sit within 3e-5 (relative) of flipping in the float64 oracle; the number of
-skipped rays is asserted to stay small.
+1e-3 on gradients (max |a-b| / max |a| per tensor, plus an entry-by-entry relative
+check on the entries above a thousandth of the tensor's largest), identical hit sets
+between the tiled, per-ray and exhaustive searches.  Rays whose discrete decisions
+(truncation, termination, slab overlap) sit within 3e-5 (relative) of flipping in the
+float64 oracle may legitimately decide otherwise in fp32: they are held to a loose
+bound of 1e-3 -- one flipped truncation moves a pixel by about sigma_t dt -- instead
+of 1e-4, and their share is asserted case by case.
 """
 import numpy as np
 import pytest
@@ -19,6 +22,12 @@ pytestmark = pytest.mark.gpu
 RGB_TOL = 1e-4
 GRAD_TOL = 1e-3
 MARGIN = 3e-5
+LOOSE_RGB_TOL = 1e-3
+# share of rays outside the margin, per golden case (a property of the committed vectors)
+STEADY_SHARE = {"config1": 0.9465, "small_static": 0.8906, "small_dynamic_white": 0.9648, "small_lobes_deg2": 0.9028,
+                "small_deg0": 0.8819, "small_deg1_cap": 0.7986}
+ELEMENT_FLOOR = 1e-3      # entries above this fraction of the tensor's largest are compared one by one
+ELEMENT_TOL = 2e-2        # ... to this relative error at worst, and to 5e-3 at the 99th percentile
 
 
 @pytest.fixture(scope="module")
@@ -28,6 +37,18 @@ def ro():
     from raygaussx_b200 import render_optix
     _lib.lib()      # fails loudly if librgx.so is missing
     return render_optix
+
+
+def elementwise(ref, got):
+    """(worst, 99th percentile) relative error over the entries of ``ref`` above ELEMENT_FLOOR of its largest:
+    what max-normalised errors cannot see -- a small entry that is entirely wrong."""
+    ref = np.asarray(ref, dtype=np.float64).reshape(-1)
+    got = np.asarray(got, dtype=np.float64).reshape(-1)
+    big = np.abs(ref) > ELEMENT_FLOOR * np.abs(ref).max()
+    if not big.any():
+        return 0.0, 0.0
+    rel = np.abs(got[big] - ref[big]) / np.abs(ref[big])
+    return float(rel.max()), float(np.quantile(rel, 0.99))
 
 
 def settings_for(ro, sc, cam, **kw):
@@ -66,9 +87,11 @@ def test_forward_and_backward_match_golden(ro, name):
     assert input_checksum(sc) == pytest.approx(float(g["input_sum"]), rel=1e-12)
     r, tens, cs, rgb, alpha, depth = render(ro, sc)
     steady = g["oracle_margin"] > MARGIN
-    assert steady.mean() > 0.78
+    assert steady.mean() == pytest.approx(STEADY_SHARE[name], abs=2e-3)
     err = np.abs(rgb.cpu().numpy().astype(np.float64) - g["oracle_rgb"]).max(axis=1)
     assert err[steady].max() <= RGB_TOL
+    assert err[~steady].max() <= LOOSE_RGB_TOL          # marginal rays: bounded, not dropped
+    assert np.abs(alpha.cpu().numpy() - g["oracle_alpha"])[~steady].max() <= LOOSE_RGB_TOL
     assert np.abs(alpha.cpu().numpy() - g["oracle_alpha"])[steady].max() <= RGB_TOL
     assert np.abs(depth.cpu().numpy() - g["oracle_depth"])[steady].max() <= 5e-4
     # against the reference's own device code (fp32): same tolerance
@@ -78,6 +101,8 @@ def test_forward_and_backward_match_golden(ro, name):
         if "oracle_grad_" + nm in g.files:
             assert rel_max(g["oracle_grad_" + nm], gr.cpu()) <= GRAD_TOL, nm
             assert rel_max(g["ref_grad_" + nm], gr.cpu()) <= GRAD_TOL, nm
+            worst, p99 = elementwise(g["oracle_grad_" + nm], gr.cpu())
+            assert worst <= ELEMENT_TOL and p99 <= 5e-3, (nm, worst, p99)
 
 
 @pytest.mark.parametrize("name", ["small_static", "small_dynamic_white", "config1"])
@@ -392,3 +417,101 @@ def test_partly_recorded_forward_mixes_replay_and_search(ro, cap):
         assert rel_max(a.cpu(), b.cpu()) < 1e-4
     _lib.check(r._ctx, r._lib.rgx_debug_cap_recording(r._ctx, C.c_longlong(-1)))
     del r
+
+
+@pytest.mark.parametrize("name", ["config1", "small_lobes_deg2", "small_deg0"])
+def test_gaussian_colours_match_the_reference_kernel(ro, name):
+    """rgx_gaussian_colors against the reference's forward_sh (utils/sh_utils.cu:122-216, run on the CPU for the
+    golden file) and the float64 restatement: SH degrees 0, 2 and 3, with and without lobes."""
+    g = load_golden(name)
+    sc = make_scene(name)
+    dev = torch.device("cuda")
+    t = [x.to(dev).contiguous() for x in sc.tensors()]
+    r = ro.get_renderer()
+    r.build(*t[:4])
+    eye = sc.cameras[0].camera_center.cpu().tolist()
+    got = r.gaussian_colors(t[0], t[4], t[5], t[6], t[7], eye).cpu().numpy()
+    assert got.shape == (sc.n, 3)
+    assert np.abs(got - g["ref_gaussian_rgb"]).max() <= 2e-6
+    assert np.abs(got.astype(np.float64) - g["oracle_gaussian_rgb"]).max() <= 2e-6
+
+
+@pytest.mark.parametrize("name", ["config1", "small_static"])
+def test_scene_box_matches_the_reference_reductions(ro, name):
+    """rgx_scene_box against the min/max reductions over the per-Gaussian boxes of optix_utils.py:36-109
+    (restated in fp32 numpy beside the reference build, and in float64 by the oracle); Gaussians at or below
+    the density threshold take part with a zero-size box, as in the reference."""
+    from oracle import oracle, ref_shim
+    sc = make_scene(name)
+    sc.densities[::5] = 0.05
+    sc.positions[7] = torch.tensor([3.0, -2.5, 4.0])        # a sub-threshold Gaussian far outside still stretches the box
+    sc.densities[7] = 0.01
+    dev = torch.device("cuda")
+    t = [x.to(dev).contiguous() for x in sc.tensors()]
+    r = ro.get_renderer()
+    r.build(*t[:4])
+    lo, hi = r.scene_box()
+    _, ref_lo, ref_hi = ref_shim.ellipsoids_bbox(sc.quaternions.numpy(), sc.positions.numpy(), sc.scales.numpy(),
+                                                 sc.densities.numpy())
+    assert np.abs(lo - ref_lo).max() <= 1e-6 and np.abs(hi - ref_hi).max() <= 1e-6
+    _, _, o_lo, o_hi = oracle.ellipsoid_aabbs(sc.positions.double(), sc.scales.double(), sc.quaternions.double(),
+                                              sc.densities.double(), 0.1)
+    assert np.abs(lo - o_lo.numpy()).max() <= 1e-6 and np.abs(hi - o_hi.numpy()).max() <= 1e-6
+    assert hi[2] == pytest.approx(4.0, abs=1e-6)
+
+
+def test_backward_after_a_build_of_other_geometry(ro):
+    """forward(A), then another model of the same size is built and rendered, then backward(A): the gradients
+    must be A's (the reference keeps its acceleration structure per call and reads the saved tensors).  The
+    autograd entry point notices the foreign build and builds again from the tensors its forward saw."""
+    name = "small_static"
+    g = load_golden(name)
+    sc = make_scene(name)
+    dev = torch.device("cuda")
+    sc.to(dev)
+    leaves = [t.clone().requires_grad_(True) for t in sc.tensors()[:5]]
+    st = settings_for(ro, sc, sc.cameras[0])
+    out = ro.RenderOptixFunction.apply(*leaves, *sc.tensors()[5:], st)
+    other = scenes.tiny_scene(n=sc.n, width=16, height=16, log_scale_mean=-2.2, seed=123)   # same count, other values
+    other.to(dev)
+    with torch.no_grad():
+        ro.RenderOptixFunction.apply(*other.tensors(), settings_for(ro, other, other.cameras[0]))
+    (out * torch.from_numpy(g["dl"]).to(dev, torch.float32)).sum().backward()
+    for nm, leaf in zip(GRAD_NAMES, leaves):
+        assert rel_max(g["oracle_grad_" + nm], leaf.grad.cpu()) <= GRAD_TOL, nm
+
+
+def test_misaligned_inputs(ro):
+    """A row slice of a larger buffer starts off the 16-byte boundary the kernels need for quaternions and
+    16-coefficient colour rows: the C ABI refuses it (no launch, no fault), the autograd entry point copies it."""
+    name = "small_static"
+    g = load_golden(name)
+    sc = make_scene(name)
+    dev = torch.device("cuda")
+    sc.to(dev)
+    padded_q = torch.cat([torch.zeros(1, 4, device=dev), sc.quaternions])[1:]            # 16 bytes in: still aligned
+    odd_q = torch.cat([torch.zeros(1, device=dev), sc.quaternions.reshape(-1)])[1:].view(-1, 4)   # 4 bytes in
+    odd_sh = torch.cat([torch.zeros(2, device=dev), sc.color_features.reshape(-1)])[2:].view_as(sc.color_features)
+    assert padded_q.data_ptr() % 16 == 0 and odd_q.data_ptr() % 16 == 4 and odd_sh.data_ptr() % 16 == 8
+    r = ro.get_renderer()
+    with pytest.raises(_lib.RgxError) as e:
+        r._n_built = -1
+        sc_struct = r._scene(sc.positions, sc.scales, odd_q, sc.densities)
+        _lib.check(r._ctx, r._lib.rgx_build(r._ctx, __import__("ctypes").byref(sc_struct), 0.1, 10, 1, r._stream()))
+    assert e.value.code == _lib.RGX_E_INVALID
+    r.build(sc.positions, sc.scales, sc.quaternions, sc.densities)
+    cs = ro.camera_struct(sc.cameras[0])
+    march = ro._settings_march(settings_for(ro, sc, sc.cameras[0]), cs)
+    with pytest.raises(_lib.RgxError) as e:
+        r.forward(sc.positions, sc.scales, sc.quaternions, sc.densities, odd_sh, *sc.tensors()[5:], cs, march)
+    assert e.value.code == _lib.RGX_E_INVALID
+    torch.cuda.synchronize()                                  # the context is intact: nothing faulted
+    tens = list(sc.tensors())
+    tens[2], tens[4] = odd_q, odd_sh
+    leaves = [t.detach().requires_grad_(True) for t in tens[:5]]
+    out = ro.RenderOptixFunction.apply(*leaves, *tens[5:], settings_for(ro, sc, sc.cameras[0]))
+    steady = g["oracle_margin"] > MARGIN
+    assert np.abs(out.detach().cpu().numpy() - g["oracle_rgb"]).max(axis=1)[steady].max() <= RGB_TOL
+    (out * torch.from_numpy(g["dl"]).to(dev, torch.float32)).sum().backward()
+    for nm, leaf in zip(GRAD_NAMES, leaves):
+        assert rel_max(g["oracle_grad_" + nm], leaf.grad.cpu()) <= GRAD_TOL, nm

@@ -14,10 +14,12 @@ the stated maximum are refused.
 """
 import ctypes as C
 
+import numpy as np
 import pytest
 import torch
 
 from raygaussx_b200 import _lib, scenes
+from tests.helpers import load_golden
 
 pytestmark = pytest.mark.gpu
 
@@ -76,10 +78,43 @@ def test_static_forward_matches_regular_forward_twice():
         assert (rgb - rgb_e).abs().max().item() <= RGB_TOL
         assert (alpha - alpha_e).abs().max().item() <= RGB_TOL
         assert (depth - depth_e).abs().max().item() <= 5e-4
+        if sc is prepared[0][0]:
+            # the first scene is the 4,096-Gaussian 64x64 configuration: also against the committed golden vectors
+            # (float64 oracle and the reference's own device code), not only against this library's other path
+            g = load_golden("config1")
+            steady = g["oracle_margin"] > 3e-5
+            got = rgb.cpu().numpy()
+            assert np.abs(got.astype(np.float64) - g["oracle_rgb"]).max(axis=1)[steady].max() <= RGB_TOL
+            assert np.abs(got - g["ref_rgb"]).max(axis=1)[steady].max() <= RGB_TOL
+            assert np.abs(alpha.cpu().numpy() - g["oracle_alpha"])[steady].max() <= RGB_TOL
     after = torch.cuda.mem_get_info(dev)[0]
     # torch's own tensors of the loop are freed back to its cache; the driver-level free memory may only
     # shrink by what torch itself newly reserved (a few MiB), never by a workspace
     assert before - after < 64 * 2 ** 20
+
+
+def test_static_forward_at_its_stated_maximum():
+    """Exactly 32,768 Gaussians: the fixed carve-up of the array is at its tightest (every sub-array full, the
+    hierarchy at its deepest for the limit).  Twice in a row against the regular entry points."""
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    from raygaussx_b200 import render_optix as ro
+    dev = torch.device("cuda", torch.cuda.current_device())
+    sc = scenes.tiny_scene(n=STATIC_MAX, width=32, height=24, log_scale_mean=-4.0, seed=77)
+    tens = [t.to(dev).contiguous() for t in sc.tensors()]
+    sc.cameras[0].to(dev)
+    cs = ro.camera_struct(sc.cameras[0])
+    r = ro.get_renderer(dev)
+    r.build(*tens[:4])
+    want, want_alpha, _ = r.forward(*tens, cs, _march(ro, sc, cs), want_alpha=True)
+    assert want_alpha.max().item() > 0.5            # the view is not empty
+    for _ in range(2):
+        rc, rgb, alpha, _ = _call_static(ro, sc, cs, _march(ro, sc, cs), tens)
+        torch.cuda.synchronize()
+        assert rc == _lib.RGX_OK
+        assert (rgb - want).abs().max().item() <= RGB_TOL
+        assert (alpha - want_alpha).abs().max().item() <= RGB_TOL
+    assert torch.cuda.current_device() == dev.index   # the caller's current device is left as it was
 
 
 def test_static_forward_refuses_what_it_cannot_hold():
