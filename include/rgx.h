@@ -231,7 +231,8 @@ RGX_API int rgx_read_kernel_times(rgx_ctx* ctx, float* forward_ms, int* forward_
  * SimpleKNN::knn; called from classes/point_cloud.py:252,592 to size the first Gaussians).
  * points [n,3] -> mean_dist2 [n]: the mean of the squared distances from each point to its three nearest
  * other points, exact (Morton sort, two levels of boxes of 32, one warp per 32 queries).  With fewer than
- * four points the missing neighbours count as FLT_MAX, as in the reference.  Needs no context; allocates
+ * four points the missing neighbours stay at FLT_MAX in the fp32 sum, as in the reference: one missing gives
+ * about FLT_MAX / 3, two or three overflow to +inf.  Needs no context; allocates
  * and frees its scratch (about 70 bytes per point) inside the call and synchronises the stream. */
 RGX_API int rgx_knn_mean_dist2(int device, const float* points, int n, float* mean_dist2, rgx_stream stream);
 

@@ -563,19 +563,27 @@ def march(positions, scales, quaternions, densities, rgb_g, cam: CameraParams, m
 # --------------------------------------------------------------------------- operator
 def knn_mean_dist2(points):
     """Mean of the squared distances from every point to its three nearest other points, by brute force in
-    float64 (what SimpleKNN::knn computes, submodules/simple-knn/simple_knn.cu: a point is excluded by its
-    index, so a duplicate counts with distance zero; missing neighbours count as FLT_MAX)."""
+    float64 (what SimpleKNN::knn computes, submodules/simple-knn/simple_knn.cu:146-185: a point is excluded by
+    its index, so a duplicate counts with distance zero).  With fewer than four points the missing neighbours
+    stay at FLT_MAX and the reference adds them up in fp32: one missing gives about FLT_MAX / 3, two or three
+    overflow to +inf.  Pinned to the reference's own output by tests/golden/knn.npz."""
     import numpy as np
     p = np.asarray(points, dtype=np.float64)
     n = p.shape[0]
     out = np.empty(n, dtype=np.float64)
-    flt_max = float(np.finfo(np.float32).max)
+    flt_max = np.finfo(np.float32).max
     for i in range(n):
         d = ((p - p[i]) ** 2).sum(axis=1)
         d = np.delete(d, i)
         best = np.sort(d)[:3].tolist()
-        best += [flt_max] * (3 - len(best))
-        out[i] = (best[0] + best[1] + best[2]) / 3.0
+        if len(best) == 3:
+            out[i] = (best[0] + best[1] + best[2]) / 3.0
+        else:                                  # the reference's fp32 sum with FLT_MAX for what is missing
+            with np.errstate(over="ignore"):
+                total = np.float32(0.0)
+                for b in [np.float32(x) for x in best] + [flt_max] * (3 - len(best)):
+                    total = np.float32(total + b)
+                out[i] = float(np.float32(total / np.float32(3.0)))
     return out
 
 

@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "librgx.so")
+# the in-tree build; RGX_LIBRARY names another build of the same library (a differently tuned one, say)
+LIB_PATH = os.environ.get("RGX_LIBRARY") or os.path.join(_HERE, "librgx.so")
 
 RGX_OK, RGX_E_INVALID, RGX_E_CUDA, RGX_E_NOT_BUILT, RGX_E_TOO_LARGE = 0, -1, -2, -3, -4
 CURVE_MORTON, CURVE_HILBERT = 0, 1

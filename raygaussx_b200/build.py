@@ -35,16 +35,19 @@ def needs_build():
     return any(os.path.getmtime(d) > t for d in deps if os.path.exists(d))
 
 
-def build(force=False, verbose=False, extra=()):
+def build(force=False, verbose=False, extra=(), out=None):
+    """Compile every .cu of the package into librgx.so (or ``out``).  Returns the library path.
+    ``extra`` and ``$RGX_NVCC_FLAGS`` are added to the compiler's flags (tuning macros)."""
     extra = tuple(extra) + tuple(os.environ.get("RGX_NVCC_FLAGS", "").split())
-    """Compile every .cu of the package into librgx.so.  Returns the library path."""
-    if not force and not needs_build():
+    lib = out or LIB
+    if not force and out is None and not needs_build():
         return LIB
     objs = []
-    os.makedirs(os.path.join(HERE, "build"), exist_ok=True)
+    objdir = os.path.join(HERE, "build") if out is None else os.path.join(os.path.dirname(os.path.abspath(out)), "obj_" + os.path.basename(out))
+    os.makedirs(objdir, exist_ok=True)
     procs = []
     for src in SOURCES:
-        obj = os.path.join(HERE, "build", src.replace(".cu", ".o"))
+        obj = os.path.join(objdir, src.replace(".cu", ".o"))
         cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-c", os.path.join(CSRC, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas")
@@ -60,10 +63,11 @@ def build(force=False, verbose=False, extra=()):
         failed |= p.returncode != 0
     if failed:
         raise RuntimeError("nvcc failed")
-    cmd = [_nvcc(), "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
+    cmd = [_nvcc(), "-shared", "-o", lib, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
     subprocess.run(cmd, check=True)
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    out_arg = [a.split("=", 1)[1] for a in sys.argv if a.startswith("--out=")]
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, out=out_arg[0] if out_arg else None))

@@ -22,6 +22,9 @@ constexpr int kTile = 8;   // per-ray variant (march.cu): a CTA marches 8x8 pixe
 #endif
 constexpr int kEvalUnroll = RGX_EVAL_UNROLL;
 constexpr int kMaxSlabs = 1 << 22;   // hard bound on slab iterations per ray
+#ifndef RGX_PACKED_FMA
+#define RGX_PACKED_FMA 1
+#endif
 
 struct WarpStage {      // staged hit records of one warp
     float4 recA[kStage];
@@ -339,9 +342,27 @@ __device__ __forceinline__ void clip_scene(const SceneBox& b, const Ray& r, floa
 // |de|^2 (tau - tau*)^2 about the closest approach tau* (a sum of two non-negative terms: no cancellation), so a
 // staged record is (tau*, (1 - q_min)/|de|^2, -hk |de|^2, -hk q_min) and (payload, sigma): the truncation
 // test q < 1 is d^2 < (1 - q_min)/|de|^2 and the exponent one fused multiply-add of d^2.
+// The four sums advance with two packed fp32x2 fused multiply-adds per hit (sm_100's FFMA2: two IEEE fp32 FMAs in
+// one instruction, same bits as two scalar ones): the loop is bound by instruction issue, not by the FMA pipe.
 template <bool COUNT>
 __device__ __forceinline__ void eval_forward(const WarpStage& ws, int count, float tau, float& s, float& cr,
                                              float& cg, float& cb, Tally& tl) {
+#if RGX_PACKED_FMA
+    float2 rg = make_float2(cr, cg), bs = make_float2(cb, s);
+#pragma unroll kEvalUnroll
+    for (int j = 0; j < count; ++j) {
+        const float4 A = ws.recA[j], C = ws.recB[j];
+        const float d = __fadd_rn(tau, -A.x);
+        const float d2 = __fmul_rn(d, d);
+        const bool in = d2 < A.y;
+        const float e = in ? ex2_approx(fmaf(A.z, d2, A.w)) : 0.0f;
+        const float2 ee = make_float2(e, e);
+        rg = __ffma2_rn(make_float2(C.x, C.y), ee, rg);
+        bs = __ffma2_rn(make_float2(C.z, C.w), ee, bs);
+        if (COUNT) tl.v[C_PAIRS] += __popc(__ballot_sync(kFull, in));
+    }
+    cr = rg.x; cg = rg.y; cb = bs.x; s = bs.y;
+#else
 #pragma unroll kEvalUnroll
     for (int j = 0; j < count; ++j) {
         const float4 A = ws.recA[j], C = ws.recB[j];
@@ -355,6 +376,7 @@ __device__ __forceinline__ void eval_forward(const WarpStage& ws, int count, flo
         cb = fmaf(C.z, e, cb);
         if (COUNT) tl.v[C_PAIRS] += __popc(__ballot_sync(kFull, in));
     }
+#endif
 }
 
 // The record of eval_forward for a hit with whitened ray origin Oe and direction de, sample positions counted

@@ -138,6 +138,7 @@ __device__ __forceinline__ void search_tile(const MarchLaunch& L, const Ray& r, 
     }
 }
 
+
 // Closest hit over [tmin,tmax] in a tile list, +inf on a miss.
 template <bool COUNT>
 __device__ __forceinline__ float closest_in_tile(const MarchLaunch& L, const Ray& r, float tmin, float tmax,

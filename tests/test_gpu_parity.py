@@ -27,7 +27,8 @@ LOOSE_RGB_TOL = 1e-3
 STEADY_SHARE = {"config1": 0.9465, "small_static": 0.8906, "small_dynamic_white": 0.9648, "small_lobes_deg2": 0.9028,
                 "small_deg0": 0.8819, "small_deg1_cap": 0.7986}
 ELEMENT_FLOOR = 1e-3      # entries above this fraction of the tensor's largest are compared one by one
-ELEMENT_TOL = 2e-2        # ... to this relative error at worst, and to 5e-3 at the 99th percentile
+ELEMENT_TOL = 1e-1        # ... to this relative error at worst (an entirely wrong entry is off by 1), and to 5e-3
+                          # at the 99th percentile; a flipped truncation on a marginal ray moves small entries by percents
 
 
 @pytest.fixture(scope="module")
