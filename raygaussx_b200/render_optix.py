@@ -44,13 +44,20 @@ class RenderOptixSettings:
     the render to those image rows (of the supersampled image): the other rays of the returned image are left
     unwritten and take no part in the backward -- how a view is shared between ranks.  ``next_viewpoint_cam``
     (with ``next_rows``) announces the view that will be rendered next with the same, unchanged Gaussians and
-    ``reuse_acceleration_structure`` set: the backward of this view then prepares it beside its own kernels."""
+    ``reuse_acceleration_structure`` set (or the very same, untouched parameter tensors, which the forward
+    recognises by itself): the backward of this view then prepares it beside its own kernels.
+    ``accumulate_leaf_grads``: when every differentiable input is a leaf tensor, the backward adds its gradients
+    straight into their ``.grad`` (allocated and zeroed on first use) and hands autograd nothing to accumulate --
+    one pass over the 59 floats per Gaussian less per view.  Off by default, because hooks registered on those
+    leaves (``register_hook``, ``register_post_accumulate_grad_hook``, DistributedDataParallel) do not see
+    gradients that bypass autograd's accumulation."""
 
     def __init__(self, context, update, gas, program_grps_fwd, pipeline_fwd, program_grps_bwd, pipeline_bwd, dt_step,
                  dynamic_sampling, viewpoint_cam, max_prim_slice, num_sph_gauss, iteration=0, jitter=False,
                  rnd_sample=0, supersampling=(1, 1), white_background=False, hit_prim_idx=None, *,
                  transmittance_eps=TRANSMITTANCE_EPSILON, exact_sh_grad=False, rows=None,
-                 next_viewpoint_cam=None, next_rows=None, reuse_acceleration_structure=False):
+                 next_viewpoint_cam=None, next_rows=None, reuse_acceleration_structure=False,
+                 accumulate_leaf_grads=False):
         self.context = context
         self.update = update
         self.gas = gas
@@ -75,6 +82,7 @@ class RenderOptixSettings:
         self.next_viewpoint_cam = next_viewpoint_cam
         self.next_rows = next_rows
         self.reuse_acceleration_structure = reuse_acceleration_structure   # the caller vouches: same geometry as the last build
+        self.accumulate_leaf_grads = accumulate_leaf_grads
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -336,6 +344,15 @@ class RenderOptixFunction(torch.autograd.Function):
         rgb, _, _ = r.forward(*tensors, cam, march)
         ctx.settings = settings
         ctx.build_serial = r._build_serial
+        ctx.leaves = None
+        if getattr(settings, "accumulate_leaf_grads", False):
+            given = (positions, scales, normalized_quaternions, densities, color_features, sph_gauss_features,
+                     bandwidth_sharpness, lobe_axis)
+            wanted = [g for g in given if g.requires_grad]
+            if all(g.requires_grad for g in given[:5]) and all(
+                    g.is_leaf and g.is_cuda and g.dtype == torch.float32 and g.is_contiguous()
+                    and g.data_ptr() % 16 == 0 for g in wanted):
+                ctx.leaves = given
         ctx.save_for_backward(*tensors, rgb)
         return rgb
 
@@ -348,7 +365,22 @@ class RenderOptixFunction(torch.autograd.Function):
         cam = camera_struct(settings.viewpoint_cam, settings.supersampling)
         flags = _lib.FLAG_EXACT_SH_GRAD if getattr(settings, "exact_sh_grad", False) else 0
         march = _settings_march(settings, cam, flags=flags, rows=getattr(settings, "rows", None))
-        grads = [torch.empty_like(t) for t in tensors]
+        leaves = ctx.leaves
+        if leaves is not None:
+            targets = [t for t in leaves if t.requires_grad]       # the first five, and the lobe tensors that ask
+            for t in targets:
+                if t.grad is None:
+                    t.grad = torch.zeros_like(t, memory_format=torch.contiguous_format)
+            if not all(t.grad.is_contiguous() and t.grad.dtype == torch.float32 and t.grad.data_ptr() % 16 == 0
+                       for t in targets):
+                leaves = None
+        if leaves is not None:
+            # lobe tensors that ask for no gradient still need somewhere for it to go
+            grads = [t.grad if t.requires_grad else torch.zeros_like(s) for t, s in zip(leaves, tensors)]
+            flags |= _lib.FLAG_ACCUMULATE
+            march = _settings_march(settings, cam, flags=flags, rows=getattr(settings, "rows", None))
+        else:
+            grads = [torch.empty_like(t) for t in tensors]
         if r._build_serial != ctx.build_serial:
             # another build came between this view's forward and its backward (a second model, an evaluation copy,
             # a finite-difference probe): the backward reads the geometry of the latest build, so build again from
@@ -359,6 +391,8 @@ class RenderOptixFunction(torch.autograd.Function):
             ncam = camera_struct(nxt, settings.supersampling)
             r.hint_next_view(ncam, _settings_march(settings, ncam, rows=getattr(settings, "next_rows", None)))
         r.backward(*tensors, cam, march, rgb, dl, tuple(grads))
+        if leaves is not None:            # already in the leaves' .grad: nothing for autograd to accumulate
+            return (None,) * 9
         g_pos, g_scale, g_quat, g_dens, g_sh, g_sg, g_sharp, g_axis = grads
         if settings.num_sph_gauss == 0 or tensors[6].numel() == 0:       # render_optix.py:190-197
             g_sg = g_sharp = g_axis = None

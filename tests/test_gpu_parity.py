@@ -516,3 +516,38 @@ def test_misaligned_inputs(ro):
     (out * torch.from_numpy(g["dl"]).to(dev, torch.float32)).sum().backward()
     for nm, leaf in zip(GRAD_NAMES, leaves):
         assert rel_max(g["oracle_grad_" + nm], leaf.grad.cpu()) <= GRAD_TOL, nm
+
+
+def test_automatic_reuse_and_in_place_gradient_accumulation(ro):
+    """The autograd entry point builds its acceleration structure again only when the geometry tensors are other
+    tensors than those of the latest build or were written to since; and with ``accumulate_leaf_grads`` the
+    gradients of several views land in the leaves' ``.grad`` with the values autograd's own accumulation gives."""
+    sc = make_scene("small_dynamic_white")
+    dev = torch.device("cuda")
+    sc.to(dev)
+    cam = sc.cameras[0]
+    h, w = cam.image_height, cam.image_width
+    weight = torch.randn(h * w, 3, generator=torch.Generator().manual_seed(5)).to(dev)
+    r = ro.get_renderer()
+
+    def run(in_place):
+        leaves = [t.clone().requires_grad_(True) for t in sc.tensors()[:5]]
+        builds = []
+        for i, rows in enumerate(((0, 6), (6, h), (0, h))):
+            st = settings_for(ro, sc, cam, rows=rows, accumulate_leaf_grads=in_place)
+            before = r._build_serial
+            out = ro.RenderOptixFunction.apply(*leaves, *sc.tensors()[5:], st)
+            builds.append(r._build_serial - before)
+            lo, hi = rows[0] * w, rows[1] * w
+            (out[lo:hi] * weight[lo:hi]).sum().backward()
+            if i == 1:
+                with torch.no_grad():
+                    leaves[1].mul_(1.0)          # an in-place write to the scales, values unchanged: must be noticed
+        return builds, [l.grad.clone() for l in leaves]
+
+    builds, want = run(False)
+    assert builds == [1, 0, 1], builds              # new tensors; untouched; written to
+    builds2, got = run(True)
+    assert builds2 == [1, 0, 1]
+    for a, b in zip(want, got):
+        assert rel_max(a.cpu(), b.cpu()) < 1e-5
