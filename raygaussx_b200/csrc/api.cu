@@ -705,7 +705,7 @@ static int forward_two_depth(rgx_ctx* ctx, const rgx_camera* cam, const rgx_marc
         cut = i;
     }
     if (cut < 0 || cum >= total) return plain();               // everything begins within the budget: one depth is enough
-    const float horizon = bin_hist_bucket_end(cut);
+    const float horizon = bin_hist_bucket_end(b, cut);
     const int count1 = (int)cum;
     if ((e = launch_bin_select(b, total, 0, (unsigned int)cut, nullptr, ctx->sel_keys, ctx->sel_vals, ctx->hz_scalars, ctx->tile_more, s)) != cudaSuccess)
         return cuda_fail(ctx, e, "pair selection");

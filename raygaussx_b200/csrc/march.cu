@@ -146,7 +146,7 @@ __global__ void __launch_bounds__(kWarps * 32) march_backward_kernel(const __gri
             SlabBackTerms bt = slab_back_terms(s, dc, p.dt, T, D, eps, lane);
             // pass 2: same search again; gradients of every hit Gaussian
             slab_gradients(L, L.m, r, p, tbuffer, tau, dl, bt.beta, bt.gamma, ws, prim_of[warp], lane, enumerate,
-                           [&](int j, const GaussGrad& g) { emit_global(L, dl, j, g); });
+                           [&](int j, const GaussGrad& g) { emit_global(L, dl, j, g, blockIdx.x); });
             // advance the ray state exactly as the forward does
             D = __fadd_rn(D, -bt.d_total);
             T = slab_exit_T(bt.tr, eps);

@@ -722,8 +722,9 @@ __device__ __forceinline__ void slab_gradients(const MarchLaunch& L, const rgx_m
 //   (mu.xyz, Y00) (Y11, Y22, Y01, Y02) (Y12, dsigma, drgb.xy) (drgb.z, -, -, -)
 // A Gaussian that fills the view is met by every ray, and additions to one address queue up in
 // the L2; CTAs therefore spread over `copies` sets of rows, which finalize_kernel adds up.
-__device__ __forceinline__ void emit_global(const MarchLaunch& L, float3 dl, int j, const GaussGrad& g) {
-    float4* row = L.grad_rows + 4 * ((size_t)(blockIdx.x & (unsigned)(L.grad_copies - 1)) * (size_t)L.g.n_pad + (size_t)j);
+// `spread`: what chooses the copy (the CTA's tile, so that the CTAs that share a tile -- and its Gaussians -- share rows).
+__device__ __forceinline__ void emit_global(const MarchLaunch& L, float3 dl, int j, const GaussGrad& g, unsigned spread) {
+    float4* row = L.grad_rows + 4 * ((size_t)(spread & (unsigned)(L.grad_copies - 1)) * (size_t)L.g.n_pad + (size_t)j);
     red_add_v4(row, g.mu.x, g.mu.y, g.mu.z, g.y00);
     red_add_v4(row + 1, g.y11, g.y22, g.y01, g.y02);
     red_add_v4(row + 2, g.y12, g.dsigma, __fmul_rn(dl.x, g.drgb_scale), __fmul_rn(dl.y, g.drgb_scale));

@@ -196,7 +196,7 @@ size_t binning_cub_temp_bytes(size_t pair_cap, int ntiles);
 cudaError_t launch_bin_emit(const BinLaunch& b, cudaStream_t s);
 cudaError_t launch_bin_fill(const BinLaunch& b, int total, cudaStream_t s);
 cudaError_t launch_bin_hist(const BinLaunch& b, int total, unsigned int* hist, cudaStream_t s);
-float bin_hist_bucket_end(int bucket);
+float bin_hist_bucket_end(const BinLaunch& b, int bucket);
 cudaError_t launch_bin_select(const BinLaunch& b, int total, int mode, unsigned int cut, const int* tile_flag, uint64_t* out_k,
                               uint32_t* out_v, unsigned long long* counter, int* tile_more, cudaStream_t s);
 cudaError_t launch_march_forward(const MarchLaunch& m, cudaStream_t s);
