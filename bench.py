@@ -208,7 +208,8 @@ def main():
     import torch.distributed as dist
     from raygaussx_b200 import _lib, scenes as S
     from raygaussx_b200 import render_optix as ro
-    from raygaussx_b200.dist import GradBuffer, accumulation_step, shard_rows
+    from raygaussx_b200.dist import (GradBuffer, accumulation_step, shard_rows, shard_rows_weighted,
+                                     view_costs_from_blocks)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -240,8 +241,11 @@ def main():
         return ro.Renderer._march(mp.dt_step, mp.dynamic_sampling, mp.max_prim_slice, mp.white_background,
                                   mp.transmittance_eps, rows, cam.height, flags)
 
-    def step():
-        accumulation_step(renderer, scene_dev_tensors, cams, targets, march_of, grads, rank=rank, world=world)
+    all_blocks = [shard_rows(args.views, args.height, r, world) for r in range(world)]
+
+    def step(events=None):
+        accumulation_step(renderer, scene_dev_tensors, cams, targets, march_of, grads, rank=rank, world=world,
+                          blocks=all_blocks[rank], block_events=events)
 
     def barrier():
         if world > 1:
@@ -249,8 +253,20 @@ def main():
         torch.cuda.synchronize()
 
     # ---- device-resident timing
-    for _ in range(args.warmup):
-        step()
+    for w in range(args.warmup):
+        if w == 0 and world > 1:
+            # the first warm-up step, cut into equal row counts, times every block; from then on the rows are cut so
+            # that every rank gets an equal share of the measured cost (views differ by a few per cent)
+            events = []
+            step(events)
+            torch.cuda.synchronize()
+            mine = [(b, e0.elapsed_time(e1)) for b, e0, e1 in events]
+            gathered = [None] * world
+            dist.all_gather_object(gathered, mine)
+            costs = view_costs_from_blocks(args.views, args.height, [x for g in gathered for x in g])
+            all_blocks = [shard_rows_weighted(costs, args.height, r, world) for r in range(world)]
+        else:
+            step()
     barrier()
     renderer.set_profiling(True)
     renderer.read_kernel_times()
@@ -282,7 +298,7 @@ def main():
     e2e = None
     if not args.no_e2e:
         params = [t.clone().requires_grad_(True) for t in scene_dev_tensors[:5]] + list(scene_dev_tensors[5:])
-        my_blocks = shard_rows(args.views, args.height, rank, world)
+        my_blocks = all_blocks[rank]
         loss_host = torch.zeros(1).pin_memory()
         copy_stream = torch.cuda.Stream()
 
@@ -385,7 +401,7 @@ def main():
     n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
     bwd_ms = ktimes["backward_ms"] / max(1, ktimes["backward_launches"])
     fwd_ms = ktimes["forward_ms"] / max(1, ktimes["forward_launches"])
-    blocks0 = shard_rows(args.views, args.height, 0, world)
+    blocks0 = all_blocks[0]
     rows_per_launch = sum(b.row_end - b.row_begin for b in blocks0) / max(1, len(blocks0))
     rays_per_launch = rows_per_launch * args.width
     # work counters of one view (outside the timed region)
@@ -491,7 +507,8 @@ def main():
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "gaussians": args.gaussians, "image": f"{args.width}x{args.height}",
-                   "views_per_step": args.views, "sh_degree": 3, "sharding": f"rows/{world}",
+                   "views_per_step": args.views, "sh_degree": 3,
+                   "sharding": f"rows/{world}" + (", cut by the per-view cost measured in the first warm-up step" if world > 1 else ""),
                    "shell_scales": "the shell's drawn log-scale N(-1, 0.5) is the LONGEST axis, the two others "
                                    "shorter by log-uniform factors up to 10 (read as the shortest axis, every ray "
                                    "overflows the 512-hit cap in its first slab and parity is undefined)",

@@ -70,12 +70,32 @@ def test_full_size_backward_properties(big):
     for rows in ((0, 300), (300, 828)):
         r.backward(*tens, cs, march(ro, sc, cs, rows=rows, flags=_lib.FLAG_ACCUMULATE), rgb, dl, tuple(parts))
     torch.cuda.synchronize()
-    for a, b in zip(whole[:5], parts[:5]):
+    # Which of the two is right?  A reference with far less rounding: the image in 46 bands of 18 rows, each band's
+    # gradient accumulated on its own (a Gaussian then sums 46 times fewer fp32 terms per band) and the bands added
+    # up in float64.  Only the order and grouping of additions differ between the three.
+    ref64 = [torch.zeros_like(t, dtype=torch.float64) for t in tens[:5]]
+    for lo in range(0, cs.height, 18):
+        band = [torch.zeros_like(t) for t in tens]
+        r.backward(*tens, cs, march(ro, sc, cs, rows=(lo, min(lo + 18, cs.height))), rgb, dl, tuple(band))
+        for acc, g in zip(ref64, band[:5]):
+            acc += g.double()
+    torch.cuda.synchronize()
+    report = []
+    for nm, a, b, ref in zip(("positions", "scales", "quaternions", "densities", "color_features"), whole[:5], parts[:5], ref64):
         assert torch.isfinite(a).all()
         assert a.abs().sum() > 0
-        # Only the order of fp32 atomic additions differs; Gaussians that cover much of the image sum
-        # ~10^5 contributions of both signs, which bounds the agreement well above one ulp.
-        assert ((a - b).abs().max() / a.abs().max()).item() < 3e-3
+        scale = ref.abs().max()
+        ea, eb = ((a.double() - ref).abs().max() / scale).item(), ((b.double() - ref).abs().max() / scale).item()
+        ab = ((a - b).abs().max() / a.abs().max()).item()
+        report.append(f"{nm}: whole vs banded-fp64 {ea:.2e}, two parts vs banded-fp64 {eb:.2e}, whole vs two parts {ab:.2e}")
+    print("\n".join(report))
+    for nm, a, b, ref in zip(("positions", "scales", "quaternions", "densities", "color_features"), whole[:5], parts[:5], ref64):
+        scale = ref.abs().max()
+        # Gaussians that cover much of the image sum ~10^5 contributions of both signs in fp32 atomics; measured
+        # 3e-5 .. 7e-5 for all three comparisons, far inside the 1e-3 the gradients are held to
+        assert ((a.double() - ref).abs().max() / scale).item() < 3e-4, report
+        assert ((b.double() - ref).abs().max() / scale).item() < 3e-4, report
+        assert ((a - b).abs().max() / a.abs().max()).item() < 3e-4, report
 
 
 @pytest.mark.parametrize("cam_index", [0, 1, 2])
@@ -117,8 +137,9 @@ def test_tile_lists_find_every_hit_with_the_camera_inside_the_scene(cam_index):
     searched = [torch.zeros_like(t) for t in tens]
     r.backward(*tens, cs, march(ro, sc, cs), rgb, dl, tuple(searched))
     torch.cuda.synchronize()
-    for x, y in zip(replayed[:5], searched[:5]):
-        assert ((x - y).abs().max() / y.abs().max().clamp_min(1e-30)).item() < 2e-3
+    worst = max(((x - y).abs().max() / y.abs().max().clamp_min(1e-30)).item() for x, y in zip(replayed[:5], searched[:5]))
+    print(f"camera {cam_index}: replayed vs searched gradients, worst max-normalised difference {worst:.2e}")
+    assert worst < 1e-3
 
 
 @pytest.mark.parametrize("cam_index", [0, 1])

@@ -187,3 +187,31 @@ def test_accumulation_step_announces_each_next_block_gloo():
         g0, g1 = out[0][ahead][1], out[1][ahead][1]
         assert g0 == g1
         assert g0 == pytest.approx([1.0 / n_views] * n_views, rel=1e-6)
+
+
+@pytest.mark.parametrize("world", [1, 2, 3, 8])
+def test_weighted_shards_cover_every_row_once_and_balance_the_cost(world):
+    views, height = 20, 828
+    costs = [22.0 + 0.6 * ((7 * v) % 5 - 2) for v in range(views)]          # views differ by a few per cent
+    seen, share = [], []
+    for rank in range(world):
+        blocks = rdist.shard_rows_weighted(costs, height, rank, world)
+        share.append(sum((b.row_end - b.row_begin) / height * costs[b.view] for b in blocks))
+        for b in blocks:
+            assert 0 <= b.row_begin < b.row_end <= height
+            seen += [(b.view, r) for r in range(b.row_begin, b.row_end)]
+    assert sorted(seen) == [(v, r) for v in range(views) for r in range(height)]
+    assert max(share) - min(share) <= 2 * max(costs) / height + 1e-9        # equal up to a row
+    # equal costs give the equal-count cuts; degenerate costs fall back to them
+    for rank in range(world):
+        assert rdist.shard_rows_weighted([1.0] * views, height, rank, world) == rdist.shard_rows(views, height, rank, world)
+        assert rdist.shard_rows_weighted([0.0] * views, height, rank, world) == rdist.shard_rows(views, height, rank, world)
+
+
+def test_view_costs_from_timed_blocks():
+    B = rdist.RowBlock
+    timed = [(B(0, 0, 10), 5.0), (B(1, 0, 4), 2.0), (B(1, 4, 10), 4.0)]     # view 2 was not timed
+    costs = rdist.view_costs_from_blocks(3, 10, timed)
+    assert costs[0] == pytest.approx(5.0) and costs[1] == pytest.approx(6.0) and costs[2] == pytest.approx(5.5)
+    half = rdist.view_costs_from_blocks(1, 10, [(B(0, 0, 5), 3.0)])          # half a view timed: scaled to the whole
+    assert half == [pytest.approx(6.0)]
