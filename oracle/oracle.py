@@ -482,6 +482,29 @@ def _prefilter(o, dirs, P, rad, dens, sig_t):
         return near.any(dim=1) & (dens > sig_t)
 
 
+def _pierced(o, dirs, P, S, Q, dens, sig_t):
+    """Exact cull for a chunk: keep the Gaussians whose truncation ellipsoid the LINE of some ray of the chunk
+    pierces (the discriminant test of cuda_train/forward/gaussians_aabb.cu:57-73 in float64, with a little slack).
+    Bounding spheres say little about needles of 100:1; this leaves the few hundred Gaussians per ray that can
+    appear in a hit set at all, so that the dense sample x Gaussian tensors stay small."""
+    with torch.no_grad():
+        U, V, W = quat_to_columns(Q)
+        inv_s = 1.0 / S
+        Mrows = torch.stack([U * inv_s[:, 0:1], V * inv_s[:, 1:2], W * inv_s[:, 2:3]], dim=1)
+        k2 = 2.0 * torch.log((dens / sig_t).clamp_min(1e-300))
+        yO = torch.einsum("mkj,mj->mk", Mrows, o[None, :] - P)
+        keep = torch.zeros(P.shape[0], dtype=torch.bool)
+        A0 = (yO * yO).sum(dim=1)
+        for b in range(dirs.shape[0]):                      # ray by ray: [M, 3] temporaries only
+            yd = torch.einsum("mkj,j->mk", Mrows, dirs[b])
+            A1 = (yO * yd).sum(dim=1)
+            A2 = (yd * yd).sum(dim=1)
+            # |P|^2 / k^2 < 1 - 1e-7 is the reference's test; keep everything within a hair of it
+            p2 = (A0 - A1 * A1 / A2) / k2
+            keep |= (1.0 - p2) > 0.5e-7
+        return keep & (dens > sig_t)
+
+
 def _cone_cull(o, dirs, P, rad):
     """Conservative cull for a whole set of rays from one origin: keep the Gaussians whose bounding sphere
     reaches into the cone around the mean direction that contains every ray.  Like :func:`_prefilter` it only
@@ -545,6 +568,7 @@ def march(positions, scales, quaternions, densities, rgb_g, cam: CameraParams, m
         else:
             keep = _prefilter(o, dch, P.detach()[cone], rad[cone], dens.detach()[cone], sig_t)
             ids = cone[keep]
+            ids = ids[_pierced(o, dch, P.detach()[ids], S.detach()[ids], Q.detach()[ids], dens.detach()[ids], sig_t)]
         out = _march_chunk(o, dch, P[ids], S[ids], Q[ids], dens[ids], rgbg[ids], bb_min, bb_max, mp,
                            delta=None if delta is None else delta[sl],
                            c_final=None if delta is None else fwd.rgb[sl], diff=diff)
