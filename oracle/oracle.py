@@ -9,8 +9,10 @@ Gaussian and keeps those whose intersection test passes.
 Pinning: the reference ships no tests or golden vectors for this path.  The
 oracle is pinned instead against the reference's own device sources compiled for
 the CPU (``oracle/_ref``, see ``oracle/Makefile``; traversal replaced by an
-exhaustive loop): ``tests/test_oracle_vs_reference.py`` compares the two on
-seeded scenes, and ``tests/golden/`` holds outputs of that build.
+exhaustive loop): ``tests/test_oracle.py`` compares the two live on seeded scenes wherever that build is
+present, ``tests/golden/`` holds outputs of that build (small cases in full; a few hundred rays each of the
+300 k, 3 M and 7 M scenes), and ``tests/golden/knn.npz`` holds the output of the reference's own
+nearest-neighbour extension for :func:`knn_mean_dist2`.
 
 Each function cites the reference lines it follows:
 

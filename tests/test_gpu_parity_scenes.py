@@ -40,7 +40,7 @@ ELEM_P99 = 1e-2
 # smallest share of rays that must be outside the margin, per view (dense views evaluate ~10^5 predicates per ray)
 MIN_STEADY = {"object:whole": 0.80, "object:crop_centre": 0.55, "object:crop_rim": 0.75,
               "unbounded:whole": 0.60, "unbounded:crop_centre": 0.55, "unbounded:crop_sky": 0.55,
-              "stress:whole": 0.40, "stress:crop_centre": 0.30}
+              "stress:whole": 0.70, "stress:crop_centre": 0.70}
 
 VIEWS = [(s, v[0]) for s, (_, views) in SCENES.items() for v in views]
 _cache = {}
