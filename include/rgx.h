@@ -258,6 +258,19 @@ RGX_API int rgx_debug_cap_recording(rgx_ctx* ctx, long long ints);
 RGX_API int rgx_debug_two_depth(rgx_ctx* ctx, int min_pairs_per_ray, int budget_per_ray);
 RGX_API int rgx_read_two_depth(rgx_ctx* ctx, long long out[4]);
 
+/* Lists up to a horizon for recording forwards (no counterpart in the reference).  A forward with
+ * RGX_FLAG_SAVE_HITS -- a training view, whose rays end long before they have seen most of their tile's list --
+ * sorts and lays out only the (tile, Gaussian) pairs that begin nearest to the eye, about `budget_per_ray` per ray
+ * (default 6; views with fewer than 2^21 pairs, or whose budget covers half of them, get complete lists).  The march
+ * counts the rays that would have needed more; if there are any, the complete lists are made and the whole view is
+ * marched again (same image and recording as without the feature), and the budget is multiplied by four for the
+ * views to come.  Costs one more wait on the stream per new view (the histogram that picks the horizon) and one
+ * after the march (the count).  budget_per_ray = 0 switches the feature off, < 0 leaves it as it is.
+ * rgx_read_near_lists returns and clears (views whose lists stopped at a horizon, pairs emitted for them, pairs
+ * kept, views that had to be marched again). */
+RGX_API int rgx_debug_near_lists(rgx_ctx* ctx, int budget_per_ray);
+RGX_API int rgx_read_near_lists(rgx_ctx* ctx, long long out[4]);
+
 /* Per-view tile-list construction (binning + sort), timed like the march kernels while
  * profiling is enabled: summed milliseconds and number of constructions since the last
  * read, and the number of (tile, Gaussian) pairs of the latest one. */

@@ -10,6 +10,10 @@
 
 using namespace rgx;
 
+#ifndef RGX_NEAR_BUDGET
+#define RGX_NEAR_BUDGET 6
+#endif
+
 struct rgx_ctx {
     int device = 0;
     std::string error;
@@ -70,6 +74,11 @@ struct rgx_ctx {
     float binning_ms = 0.f; int binning_runs = 0;
     float kept_ms[2] = {0.f, 0.f}; int kept_n[2] = {0, 0};
     bool lists_valid = false;
+    // lists of a recording forward's view may hold only the pairs that begin before a horizon (lists_from_pairs)
+    bool lists_partial = false;
+    float lists_horizon = 0.f;
+    int near_budget_per_ray = RGX_NEAR_BUDGET;   // pairs per ray such lists keep; multiplied by four whenever a ray reached the horizon
+    long long near_stats[4] = {0, 0, 0, 0};   // views with such lists, pairs emitted, pairs kept, views marched again
     unsigned long long lists_build_id = 0;
     rgx_camera lists_cam{};
     int lists_row_begin = 0, lists_row_end = 0;
@@ -567,12 +576,84 @@ static void lists_now_valid(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march
     ctx->lists_row_begin = m->row_begin; ctx->lists_row_end = m->row_end;
     ctx->lists_build_id = ctx->build_id;
     ctx->lists_valid = true;
+    ctx->lists_partial = false;
     ctx->last_pairs = total;
 }
 
-// Makes ctx->lists valid for this camera and row range (no-op if they already are).
-static int ensure_lists(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, cudaStream_t s) {
-    if (lists_cached(ctx, cam, m)) return RGX_OK;
+static int two_depth_workspace(rgx_ctx* ctx, int ntiles) {
+    cudaError_t e = cudaSuccess;
+    if (!ctx->hz_hist) {
+        RGB_(hz_hist, 2048); RGB_(hz_scalars, 4);
+        if ((e = cudaMallocHost((void**)&ctx->hz_hist_host, 2048 * sizeof(unsigned int))) != cudaSuccess ||
+            (e = cudaMallocHost((void**)&ctx->hz_scalars_host, 4 * sizeof(unsigned long long))) != cudaSuccess)
+            return cuda_fail(ctx, e, "pinned histogram");
+    }
+    if (ctx->bin_pair_cap > ctx->sel_cap) {
+        RGB_(sel_keys, ctx->bin_pair_cap); RGB_(sel_vals, ctx->bin_pair_cap);
+        ctx->sel_cap = ctx->bin_pair_cap;
+    }
+    if (ntiles > ctx->hz_tiles_cap) {
+        RGB_(tile_more, (size_t)ntiles + 64); RGB_(tile_resume, (size_t)ntiles + 64);
+        ctx->hz_tiles_cap = ntiles + 64;
+    }
+    return RGX_OK;
+}
+
+// Turns the emitted pairs into ctx->lists.  near_only: the view belongs to a recording forward -- a training view,
+// whose rays end long before they have seen most of their tile's list (on the 3 M-Gaussian scene every ray ends within
+// the nearest eighth of the pairs).  Then only the pairs that begin before a horizon are sorted and laid out, about
+// near_budget_per_ray per ray: a histogram of the near distances picks the horizon (one more wait on `s`), the march
+// counts the rays that would have needed more (march_lists.cu, hz_phase 3), and forward_impl, should there be any,
+// makes the complete lists and marches the view again.  Sorting is the largest part of a view's list construction.
+static int lists_from_pairs(rgx_ctx* ctx, BinLaunch& b, int total, int ntiles, const rgx_camera* cam, const rgx_march* m,
+                            bool near_only, cudaStream_t s) {
+    cudaError_t e = cudaSuccess;
+    int rc;
+    const long long rays = (long long)cam->width * (m->row_end - m->row_begin);
+    const long long budget = (long long)ctx->near_budget_per_ray * rays;
+    if (near_only && total >= (1 << 21) && budget * 2 < (long long)total) {
+        if ((rc = two_depth_workspace(ctx, ntiles))) return rc;
+        if ((e = cudaMemsetAsync(ctx->hz_hist, 0, 2048 * sizeof(unsigned int), s)) != cudaSuccess ||
+            (e = cudaMemsetAsync(ctx->tile_more, 0, sizeof(int) * (size_t)ntiles, s)) != cudaSuccess ||
+            (e = cudaMemsetAsync(ctx->hz_scalars, 0, 4 * sizeof(unsigned long long), s)) != cudaSuccess ||
+            (e = launch_bin_hist(b, total, ctx->hz_hist, s)) != cudaSuccess ||
+            (e = cudaMemcpyAsync(ctx->hz_hist_host, ctx->hz_hist, 2048 * sizeof(unsigned int), cudaMemcpyDeviceToHost, s)) != cudaSuccess ||
+            (e = cudaStreamSynchronize(s)) != cudaSuccess)
+            return cuda_fail(ctx, e, "near-distance histogram");
+        long long cum = 0;
+        int cut = -1;
+        for (int i = 0; i < 2048; ++i) {
+            if (ctx->hz_hist_host[i] == 0) continue;
+            if (cut >= 0 && cum + ctx->hz_hist_host[i] > budget) break;
+            cum += ctx->hz_hist_host[i];
+            cut = i;
+        }
+        if (cut >= 0 && cum * 2 < (long long)total) {            // worth it: less than half of the pairs
+            if ((e = launch_bin_select(b, total, 0, (unsigned int)cut, nullptr, ctx->sel_keys, ctx->sel_vals, ctx->hz_scalars,
+                                       ctx->tile_more, s)) != cudaSuccess)
+                return cuda_fail(ctx, e, "pair selection");
+            uint64_t* all_keys = b.keys_in;
+            uint32_t* all_vals = b.vals_in;
+            rc = fill_lists(ctx, b, ctx->sel_keys, ctx->sel_vals, (int)cum, ntiles, s);
+            b.keys_in = all_keys; b.vals_in = all_vals;
+            if (rc) return rc;
+            lists_now_valid(ctx, cam, m, total);
+            ctx->lists_partial = true;
+            ctx->lists_horizon = bin_hist_bucket_end(b, cut);
+            ctx->near_stats[0] += 1; ctx->near_stats[1] += total; ctx->near_stats[2] += cum;
+            return RGX_OK;
+        }
+    }
+    if ((rc = fill_lists(ctx, b, ctx->bin_keys_in, ctx->bin_vals_in, total, ntiles, s))) return rc;
+    lists_now_valid(ctx, cam, m, total);
+    return RGX_OK;
+}
+
+// Makes ctx->lists valid for this camera and row range (no-op if they already are).  near_only: see lists_from_pairs;
+// complete lists are wanted otherwise, and cached lists that stop at a horizon are made again.
+static int ensure_lists(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, cudaStream_t s, bool near_only = false,
+                        bool near_cached_ok = false) {
+    if (lists_cached(ctx, cam, m) && (!ctx->lists_partial || near_only || near_cached_ok)) return RGX_OK;
     ctx->lists_valid = false;
     if (m->row_end <= m->row_begin || ctx->n == 0) return RGX_OK;   // nothing to march
     ScopedTimer timer(ctx, s, 2);
@@ -580,9 +661,7 @@ static int ensure_lists(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m,
     int total = 0, ntiles = 0;
     int rc = emit_pairs(ctx, cam, m, s, b, total, ntiles);
     if (rc) return rc;
-    if ((rc = fill_lists(ctx, b, ctx->bin_keys_in, ctx->bin_vals_in, total, ntiles, s))) return rc;
-    lists_now_valid(ctx, cam, m, total);
-    return RGX_OK;
+    return lists_from_pairs(ctx, b, total, ntiles, cam, m, near_only, s);
 }
 
 // Lists of the announced view, made on the context's own stream while the stream of the caller replays a
@@ -634,11 +713,10 @@ static void lists_ahead_end(rgx_ctx* ctx, ListsAhead& a) {
     int total = 0;
     {
         ScopedTimer timer(ctx, ctx->side, 2);
+        const bool near_only = (ctx->hint_march.flags & RGX_FLAG_SAVE_HITS) && !(ctx->hint_march.flags & RGX_FLAG_COUNT_WORK);
         if (emit_finish(ctx, a.b, ctx->side, total) == RGX_OK &&
-            fill_lists(ctx, a.b, ctx->bin_keys_in, ctx->bin_vals_in, total, a.ntiles, ctx->side) == RGX_OK) {
-            lists_now_valid(ctx, &ctx->hint_cam, &ctx->hint_march, total);
+            lists_from_pairs(ctx, a.b, total, a.ntiles, &ctx->hint_cam, &ctx->hint_march, near_only, ctx->side) == RGX_OK)
             ctx->prefetched++;
-        }
     }
     cudaEventRecord(ctx->ev_lists, ctx->side);
     ctx->lists_event_set = true;
@@ -667,20 +745,7 @@ static int forward_two_depth(rgx_ctx* ctx, const rgx_camera* cam, const rgx_marc
     };
     if ((long long)total < (long long)ctx->hz_min_pairs_per_ray * rays || total == 0) return plain();
     // workspace of the two-depth path
-    if (!ctx->hz_hist) {
-        RGB_(hz_hist, 2048); RGB_(hz_scalars, 4);
-        if ((e = cudaMallocHost((void**)&ctx->hz_hist_host, 2048 * sizeof(unsigned int))) != cudaSuccess ||
-            (e = cudaMallocHost((void**)&ctx->hz_scalars_host, 4 * sizeof(unsigned long long))) != cudaSuccess)
-            return cuda_fail(ctx, e, "pinned histogram");
-    }
-    if (ctx->bin_pair_cap > ctx->sel_cap) {
-        RGB_(sel_keys, ctx->bin_pair_cap); RGB_(sel_vals, ctx->bin_pair_cap);
-        ctx->sel_cap = ctx->bin_pair_cap;
-    }
-    if (ntiles > ctx->hz_tiles_cap) {
-        RGB_(tile_more, (size_t)ntiles + 64); RGB_(tile_resume, (size_t)ntiles + 64);
-        ctx->hz_tiles_cap = ntiles + 64;
-    }
+    if ((rc = two_depth_workspace(ctx, ntiles))) return rc;
     const long long all_rays = (long long)cam->width * cam->height;
     if (2 * all_rays > ctx->hz_state_cap) {
         RGB_(hz_state, (size_t)(2 * all_rays));
@@ -787,79 +852,111 @@ static int forward_impl(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* 
             bool handled = false;
             if ((rc = forward_two_depth(ctx, cam, march, L, s, handled))) return rc;
             if (handled) return RGX_OK;
-        } else if ((rc = ensure_lists(ctx, cam, march, s))) return rc;
+        } else {
+            const bool counts = (march->flags & RGX_FLAG_COUNT_WORK) != 0;
+            const bool near_only = (march->flags & RGX_FLAG_SAVE_HITS) && !counts && ctx->near_budget_per_ray > 0;
+            if ((rc = ensure_lists(ctx, cam, march, s, near_only, !counts))) return rc;
+        }
         L.lists = ctx->lists;
     }
-    cudaError_t e;
-    const bool record = (march->flags & RGX_FLAG_SAVE_HITS) && L.lists.ent_id != nullptr && ctx->n > 0;
-    if (march->flags & RGX_FLAG_SAVE_HITS) ctx->tape_valid = false;
-    if (record) {
-        const long long rays = (long long)cam->width * cam->height;
-        const long long rows_rays = (long long)cam->width * (march->row_end - march->row_begin);
-        if (!ctx->tape_used) {
-            if ((e = regrow(ctx, ctx->tape_used, 4)) != cudaSuccess) return cuda_fail(ctx, e, "tape");
-            if ((e = cudaMallocHost((void**)&ctx->tape_used_host, 4 * sizeof(unsigned long long))) != cudaSuccess)
+    const bool counting = (march->flags & RGX_FLAG_COUNT_WORK) != 0;
+    // one march of the view over the lists in L.lists (a lambda: a view whose lists stop at a horizon may need a second one)
+    auto march_once = [&]() -> int {
+        cudaError_t e;
+        const bool record = (march->flags & RGX_FLAG_SAVE_HITS) && L.lists.ent_id != nullptr && ctx->n > 0;
+        if (march->flags & RGX_FLAG_SAVE_HITS) ctx->tape_valid = false;
+        if (record) {
+            const long long rays = (long long)cam->width * cam->height;
+            const long long rows_rays = (long long)cam->width * (march->row_end - march->row_begin);
+            if (!ctx->tape_used) {
+                if ((e = regrow(ctx, ctx->tape_used, 4)) != cudaSuccess) return cuda_fail(ctx, e, "tape");
+                if ((e = cudaMallocHost((void**)&ctx->tape_used_host, 4 * sizeof(unsigned long long))) != cudaSuccess)
+                    return cuda_fail(ctx, e, "tape");
+                for (int i = 0; i < 4; ++i) ctx->tape_used_host[i] = 0;
+            }
+            if (rays > ctx->ray_head_cap) {
+                if ((e = regrow(ctx, ctx->ray_head, (size_t)rays)) != cudaSuccess) return cuda_fail(ctx, e, "tape");
+                ctx->ray_head_cap = rays;
+            }
+            const int ntiles = L.lists.tiles_x * L.lists.tiles_y;
+            if (ntiles > ctx->tape_order_cap) {
+                if ((e = regrow(ctx, ctx->tape_tile_order, (size_t)ntiles + 64)) != cudaSuccess) return cuda_fail(ctx, e, "tape");
+                ctx->tape_order_cap = ntiles + 64;
+            }
+            // room: 1024 ints per ray to begin with; what the previous recording asked for and half as much again when
+            // that came close to the end (the counter keeps counting past the end), within half of the free memory
+            long long want = rows_rays * 1024 + 4096;
+            const long long seen = (long long)*ctx->tape_used_host;
+            if (seen > (ctx->tape_cap / 8) * 7) want = want > seen + seen / 2 ? want : seen + seen / 2;
+            if (want > ctx->tape_cap) {
+                size_t free_b = 0, total_b = 0;
+                if (cudaMemGetInfo(&free_b, &total_b) == cudaSuccess) {
+                    const long long room = (long long)((free_b + (size_t)ctx->tape_cap * sizeof(int)) / 2 / sizeof(int));
+                    if (want > room) want = room;
+                }
+            }
+            if (want > ctx->tape_cap) {
+                if ((e = regrow(ctx, ctx->tape, (size_t)want)) != cudaSuccess) {
+                    // no memory for a larger tape: render without one, the backward searches again
+                    (void)cudaGetLastError();
+                    ctx->tape = nullptr;
+                    ctx->tape_cap = 0;
+                    ctx->alloc_failed = false;     // nothing else depends on this array
+                } else {
+                    ctx->tape_cap = want;
+                }
+            }
+            if ((e = cudaMemsetAsync(ctx->tape_used, 0, 4 * sizeof(unsigned long long), s)) != cudaSuccess ||
+                (e = cudaMemsetAsync(ctx->tile_unrecorded, 0, sizeof(int) * (size_t)ntiles, s)) != cudaSuccess ||
+                (e = cudaMemcpyAsync(ctx->tape_tile_order, L.lists.tile_order, sizeof(int) * (size_t)ntiles, cudaMemcpyDeviceToDevice, s)) != cudaSuccess)
                 return cuda_fail(ctx, e, "tape");
-            for (int i = 0; i < 4; ++i) ctx->tape_used_host[i] = 0;
-        }
-        if (rays > ctx->ray_head_cap) {
-            if ((e = regrow(ctx, ctx->ray_head, (size_t)rays)) != cudaSuccess) return cuda_fail(ctx, e, "tape");
-            ctx->ray_head_cap = rays;
-        }
-        const int ntiles = L.lists.tiles_x * L.lists.tiles_y;
-        if (ntiles > ctx->tape_order_cap) {
-            if ((e = regrow(ctx, ctx->tape_tile_order, (size_t)ntiles + 64)) != cudaSuccess) return cuda_fail(ctx, e, "tape");
-            ctx->tape_order_cap = ntiles + 64;
-        }
-        // room: 1024 ints per ray to begin with; what the previous recording asked for and half as much again when
-        // that came close to the end (the counter keeps counting past the end), within half of the free memory
-        long long want = rows_rays * 1024 + 4096;
-        const long long seen = (long long)*ctx->tape_used_host;
-        if (seen > (ctx->tape_cap / 8) * 7) want = want > seen + seen / 2 ? want : seen + seen / 2;
-        if (want > ctx->tape_cap) {
-            size_t free_b = 0, total_b = 0;
-            if (cudaMemGetInfo(&free_b, &total_b) == cudaSuccess) {
-                const long long room = (long long)((free_b + (size_t)ctx->tape_cap * sizeof(int)) / 2 / sizeof(int));
-                if (want > room) want = room;
+            if (ctx->tape) {
+                L.tape = ctx->tape; L.tape_used = ctx->tape_used; L.tape_cap = ctx->tape_cap; L.ray_head = ctx->ray_head;
+                L.tile_unrecorded = ctx->tile_unrecorded;
+                if (ctx->tape_limit >= 0 && ctx->tape_limit < L.tape_cap) L.tape_cap = ctx->tape_limit;
             }
         }
-        if (want > ctx->tape_cap) {
-            if ((e = regrow(ctx, ctx->tape, (size_t)want)) != cudaSuccess) {
-                // no memory for a larger tape: render without one, the backward searches again
-                (void)cudaGetLastError();
-                ctx->tape = nullptr;
-                ctx->tape_cap = 0;
-                ctx->alloc_failed = false;     // nothing else depends on this array
-            } else {
-                ctx->tape_cap = want;
-            }
+        const bool recorded = L.tape != nullptr;
+        {
+            ScopedTimer timer(ctx, s, 0);
+            e = launch_march_forward(L, s);
         }
-        if ((e = cudaMemsetAsync(ctx->tape_used, 0, 4 * sizeof(unsigned long long), s)) != cudaSuccess ||
-            (e = cudaMemsetAsync(ctx->tile_unrecorded, 0, sizeof(int) * (size_t)ntiles, s)) != cudaSuccess ||
-            (e = cudaMemcpyAsync(ctx->tape_tile_order, L.lists.tile_order, sizeof(int) * (size_t)ntiles, cudaMemcpyDeviceToDevice, s)) != cudaSuccess)
-            return cuda_fail(ctx, e, "tape");
-        if (ctx->tape) {
-            L.tape = ctx->tape; L.tape_used = ctx->tape_used; L.tape_cap = ctx->tape_cap; L.ray_head = ctx->ray_head;
-            L.tile_unrecorded = ctx->tile_unrecorded;
-            if (ctx->tape_limit >= 0 && ctx->tape_limit < L.tape_cap) L.tape_cap = ctx->tape_limit;
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "forward march");
+        if (recorded) {
+            cudaMemcpyAsync(ctx->tape_used_host, ctx->tape_used, 4 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, s);
+            ctx->tape_valid = true;
+            ctx->tape_rgba_serial = ctx->rgba_serial;
+            ctx->tape_build_id = ctx->build_id;
+            ctx->tape_cam = *cam;
+            ctx->tape_march = *march;
+            ctx->tape_row_begin = march->row_begin; ctx->tape_row_end = march->row_end;
         }
+        return RGX_OK;
+    };
+    for (int attempt = 0;; ++attempt) {
+        const bool near_lists = L.lists.ent_id != nullptr && ctx->lists_partial && !counting && attempt == 0;
+        L.hz_phase = 0;
+        if (near_lists) {
+            // the lists hold the pairs that begin before the horizon only: rays that would need more are counted
+            L.hz_phase = 3; L.horizon = ctx->lists_horizon; L.tile_more = ctx->tile_more;
+            L.hz_count = reinterpret_cast<unsigned int*>(ctx->hz_scalars + 1);
+            cudaError_t e0 = cudaMemsetAsync(ctx->hz_scalars + 1, 0, sizeof(unsigned long long), s);
+            if (e0 != cudaSuccess) return cuda_fail(ctx, e0, "horizon counter");
+        }
+        if ((rc = march_once())) return rc;
+        if (!near_lists) return RGX_OK;
+        cudaError_t e1 = cudaMemcpyAsync(ctx->hz_scalars_host + 1, ctx->hz_scalars + 1, sizeof(unsigned long long),
+                                         cudaMemcpyDeviceToHost, s);
+        if (e1 == cudaSuccess) e1 = cudaStreamSynchronize(s);
+        if (e1 != cudaSuccess) return cuda_fail(ctx, e1, "horizon read-back");
+        if ((ctx->hz_scalars_host[1] & 0xffffffffull) == 0ull) return RGX_OK;      // every ray ended before the horizon
+        // some ray reached the horizon: the complete lists, the whole view again, and deeper lists from now on
+        ctx->near_stats[3] += 1;
+        ctx->near_budget_per_ray = ctx->near_budget_per_ray < (1 << 18) ? ctx->near_budget_per_ray * 4 : ctx->near_budget_per_ray;
+        ctx->lists_valid = false;
+        if ((rc = ensure_lists(ctx, cam, march, s))) return rc;
+        L.lists = ctx->lists;
     }
-    const bool recorded = L.tape != nullptr;
-    {
-        ScopedTimer timer(ctx, s, 0);
-        e = launch_march_forward(L, s);
-    }
-    if (e != cudaSuccess) return cuda_fail(ctx, e, "forward march");
-    if (recorded) {
-        cudaMemcpyAsync(ctx->tape_used_host, ctx->tape_used, 4 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, s);
-        ctx->tape_valid = true;
-        ctx->tape_rgba_serial = ctx->rgba_serial;
-        ctx->tape_build_id = ctx->build_id;
-        ctx->tape_cam = *cam;
-        ctx->tape_march = *march;
-        ctx->tape_row_begin = march->row_begin; ctx->tape_row_end = march->row_end;
-    }
-    return RGX_OK;
 }
 
 int rgx_forward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, const rgx_march* march, float* rgb,
@@ -907,7 +1004,9 @@ int rgx_backward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, co
     cudaError_t e = cudaMemsetAsync(ctx->grad_rows, 0, sizeof(float4) * 4 * (size_t)ctx->n_pad * (size_t)ctx->grad_copies, s);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "backward memset");
     if (!(march->flags & (RGX_FLAG_BRUTE_FORCE | RGX_FLAG_PER_RAY_SEARCH))) {
-        if ((rc = ensure_lists(ctx, cam, march, s))) return rc;
+        // lists that stop at a horizon serve the backward of the view whose forward they were checked by (its rays
+        // are known to end before the horizon); any other backward gets complete lists
+        if ((rc = ensure_lists(ctx, cam, march, s, false, tape_matches))) return rc;
         L.lists = ctx->lists;
     }
     if (L.lists.ent_id && tape_matches) {
@@ -1001,6 +1100,19 @@ int rgx_debug_two_depth(rgx_ctx* ctx, int min_pairs_per_ray, int budget_per_ray)
     if (!ctx || budget_per_ray < 0) return RGX_E_INVALID;
     ctx->hz_min_pairs_per_ray = min_pairs_per_ray;
     if (budget_per_ray > 0) ctx->hz_budget_per_ray = budget_per_ray;
+    return RGX_OK;
+}
+
+int rgx_debug_near_lists(rgx_ctx* ctx, int budget_per_ray) {
+    if (!ctx) return RGX_E_INVALID;
+    if (budget_per_ray >= 0) ctx->near_budget_per_ray = budget_per_ray;
+    ctx->lists_valid = false;          // lists made under the old setting are not reused
+    return RGX_OK;
+}
+
+int rgx_read_near_lists(rgx_ctx* ctx, long long out[4]) {
+    if (!ctx || !out) return RGX_E_INVALID;
+    for (int i = 0; i < 4; ++i) { out[i] = ctx->near_stats[i]; ctx->near_stats[i] = 0; }
     return RGX_OK;
 }
 

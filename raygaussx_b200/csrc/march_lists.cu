@@ -213,6 +213,9 @@ __device__ __forceinline__ bool ray_pixel(const MarchLaunch& L, int tile_x, int 
 // pairs beyond (L.tile_more) -- puts its state aside (L.hz_state), flags its tile (L.tile_resume) and stops.
 // The second phase (L.hz_phase == 2) has the complete lists of the flagged tiles and takes those rays up where
 // they stopped: same slabs, same hits in the same order, same image.
+// L.hz_phase == 3 is the first phase without a second one, for recording forwards (training views, whose rays
+// are expected to end before the horizon): a ray that would need more is only counted, and the caller, if the
+// count is not zero, makes the complete lists and marches the whole view again.
 template <bool COUNT, bool SAVE, bool HZ = false>
 __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 4) march_forward_lists_kernel(const __grid_constant__ MarchLaunch L) {
     __shared__ ListShared sh;
@@ -267,7 +270,7 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 4) march_forward_lists_k
         bool hz_more = false, hz_susp = false;
         float4 hz_a = make_float4(0.f, 0.f, 0.f, 0.f);
         if (HZ) {
-            hz_more = L.hz_phase == 1 && L.tile_more[tile] != 0;
+            hz_more = (L.hz_phase == 1 || L.hz_phase == 3) && L.tile_more[tile] != 0;
             if (L.hz_phase == 2) {
                 hz_a = L.hz_state[2 * (size_t)ray_id];
                 hz_mode = (int)hz_a.w;
@@ -285,8 +288,10 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 4) march_forward_lists_k
         if (HZ && hz_more && !(first < L.horizon)) {                             // nothing before the horizon: ask again later
             hz_susp = true;
             if (lane == 0) {
-                L.hz_state[2 * (size_t)ray_id] = make_float4(tenter, 1.0f, tenter, 2.0f);
-                L.tile_resume[tile] = 1;
+                if (L.hz_phase == 1) {
+                    L.hz_state[2 * (size_t)ray_id] = make_float4(tenter, 1.0f, tenter, 2.0f);
+                    L.tile_resume[tile] = 1;
+                }
                 atomicAdd(L.hz_count, 1u);
             }
         } else if (first < INFINITY && first < texit) {                           // :249-260
@@ -303,9 +308,11 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 4) march_forward_lists_k
                 if (HZ && hz_more && !(p.tmax < L.horizon)) {                        // this slab needs pairs from beyond
                     hz_susp = true;
                     if (lane == 0) {
-                        L.hz_state[2 * (size_t)ray_id] = make_float4(tbuffer, T, tenter, 1.0f);
-                        L.hz_state[2 * (size_t)ray_id + 1] = sh.color[warp];
-                        L.tile_resume[tile] = 1;
+                        if (L.hz_phase == 1) {
+                            L.hz_state[2 * (size_t)ray_id] = make_float4(tbuffer, T, tenter, 1.0f);
+                            L.hz_state[2 * (size_t)ray_id + 1] = sh.color[warp];
+                            L.tile_resume[tile] = 1;
+                        }
                         atomicAdd(L.hz_count, 1u);
                     }
                     break;
@@ -365,9 +372,11 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 4) march_forward_lists_k
                     if (HZ && hz_more && !(nxt < L.horizon)) {                   // the next hit, if any, is beyond the horizon
                         hz_susp = true;
                         if (lane == 0) {
-                            L.hz_state[2 * (size_t)ray_id] = make_float4(tbuffer, T, tenter, 3.0f);
-                            L.hz_state[2 * (size_t)ray_id + 1] = sh.color[warp];
-                            L.tile_resume[tile] = 1;
+                            if (L.hz_phase == 1) {
+                                L.hz_state[2 * (size_t)ray_id] = make_float4(tbuffer, T, tenter, 3.0f);
+                                L.hz_state[2 * (size_t)ray_id + 1] = sh.color[warp];
+                                L.tile_resume[tile] = 1;
+                            }
                             atomicAdd(L.hz_count, 1u);
                         }
                         break;
@@ -735,7 +744,8 @@ cudaError_t launch_march_forward(const MarchLaunch& m, cudaStream_t s) {
     const bool count = (m.m.flags & RGX_FLAG_COUNT_WORK) != 0, save = m.tape != nullptr;
     const int ctas = grid * kTileSplit;
     if (m.hz_phase != 0) {
-        note_launch(), march_forward_lists_kernel<false, false, true><<<ctas, kThreads, 0, s>>>(m);
+        if (save) note_launch(), march_forward_lists_kernel<false, true, true><<<ctas, kThreads, 0, s>>>(m);
+        else note_launch(), march_forward_lists_kernel<false, false, true><<<ctas, kThreads, 0, s>>>(m);
         return cudaGetLastError();
     }
     if (count && save) note_launch(), march_forward_lists_kernel<true, true><<<ctas, kThreads, 0, s>>>(m);

@@ -255,6 +255,14 @@ class Renderer:
         _lib.check(self._ctx, self._lib.rgx_hint_next_view(self._ctx, C.byref(cam) if cam is not None else None,
                                                            C.byref(march) if march is not None else None))
 
+    def near_lists(self, budget_per_ray: int = -1) -> dict:
+        """Lists up to a horizon for recording forwards (``rgx_debug_near_lists``): sets the budget of pairs per ray
+        (0 switches the feature off, negative leaves it) and returns the figures since the last call."""
+        _lib.check(self._ctx, self._lib.rgx_debug_near_lists(self._ctx, int(budget_per_ray)))
+        out = (C.c_longlong * 4)()
+        _lib.check(self._ctx, self._lib.rgx_read_near_lists(self._ctx, out))
+        return dict(views=out[0], pairs_emitted=out[1], pairs_kept=out[2], views_marched_again=out[3])
+
     def lists_made_ahead(self) -> int:
         return int(self._lib.rgx_lists_made_ahead(self._ctx))
 
@@ -389,7 +397,8 @@ class RenderOptixFunction(torch.autograd.Function):
         nxt = getattr(settings, "next_viewpoint_cam", None)      # same Gaussians, next view of an accumulation step
         if nxt is not None:
             ncam = camera_struct(nxt, settings.supersampling)
-            r.hint_next_view(ncam, _settings_march(settings, ncam, rows=getattr(settings, "next_rows", None)))
+            r.hint_next_view(ncam, _settings_march(settings, ncam, flags=_lib.FLAG_SAVE_HITS,
+                                                   rows=getattr(settings, "next_rows", None)))
         r.backward(*tensors, cam, march, rgb, dl, tuple(grads))
         if leaves is not None:            # already in the leaves' .grad: nothing for autograd to accumulate
             return (None,) * 9

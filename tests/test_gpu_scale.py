@@ -312,3 +312,43 @@ def test_lists_made_ahead_change_nothing(kind):
     r.forward(*tens, c0, m0, out=other)                    # ... but c0 is rendered again
     assert torch.equal(other, rgb0)
     r.hint_next_view(None, None)
+
+
+def test_lists_up_to_a_horizon_change_nothing(big):
+    """A recording forward sorts only the pairs that begin nearest to the eye; the image, the recording and the
+    gradients must be those of the complete lists -- also when the budget is so small that rays reach the horizon
+    and the view has to be marched again with complete lists."""
+    ro, r, sc, tens, cs = big
+    save = march(ro, sc, cs, flags=_lib.FLAG_SAVE_HITS)
+
+    def run(budget):
+        r.near_lists(budget)                        # also forgets the cached lists
+        rgb, _, _ = r.forward(*tens, cs, save)
+        rgb = rgb.clone()
+        stats = r.near_lists()
+        dl = torch.sign(rgb - 0.5) / (3 * rgb.shape[0])
+        grads = [torch.zeros_like(t) for t in tens]
+        r.backward(*tens, cs, march(ro, sc, cs), rgb, dl, tuple(grads))
+        torch.cuda.synchronize()
+        return rgb, grads, stats
+
+    full_rgb, full_grads, st0 = run(0)
+    assert st0["views"] == 0
+    near_rgb, near_grads, st1 = run(6)
+    assert st1["views"] == 1 and st1["views_marched_again"] == 0 and st1["pairs_kept"] * 2 < st1["pairs_emitted"]
+    assert torch.equal(near_rgb, full_rgb)
+    again_rgb, again_grads, st2 = run(1)            # one pair per ray: far too shallow
+    assert st2["views"] == 1 and st2["views_marched_again"] == 1
+    assert torch.equal(again_rgb, full_rgb)
+    for a, b, c in zip(full_grads[:5], near_grads[:5], again_grads[:5]):
+        scale = a.abs().max()
+        assert ((a - b).abs().max() / scale).item() < 3e-4 and ((a - c).abs().max() / scale).item() < 3e-4
+    # the budget was multiplied by four after the second march; put the default back for the tests that follow
+    r.near_lists(6)
+    # a forward without recording on the cached near lists, and a counting forward (which wants complete lists)
+    r.forward(*tens, cs, save)
+    plain, _, _ = r.forward(*tens, cs, march(ro, sc, cs))
+    assert torch.equal(plain, full_rgb)
+    r.reset_counters()
+    counted, _, _ = r.forward(*tens, cs, march(ro, sc, cs, flags=_lib.FLAG_COUNT_WORK))
+    assert torch.equal(counted, full_rgb) and r.read_counters()["rays"] == cs.width * cs.height
