@@ -282,12 +282,14 @@ def main():
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     launches0 = int(_lib.lib().rgx_kernel_launches())
+    renderer.near_lists()                 # clears the figures of the warm-up
     ev0.record()
     for _ in range(args.steps):
         step()
     ev1.record()
     barrier()
     gpu_launches = int(_lib.lib().rgx_kernel_launches()) - launches0      # counted by the library at every launch
+    near_lists = renderer.near_lists()    # views whose lists stopped at a horizon, and how many had to be marched twice
     ms = ev0.elapsed_time(ev1)
     clocks = sampler.stop() if rank == 0 else None
     ktimes = renderer.read_kernel_times()
@@ -520,7 +522,7 @@ def main():
                                    "overflows the 512-hit cap in its first slab and parity is undefined)",
                    "l2": "inputs larger than L2 (Gaussian records 0.65 GB, gradient rows 0.8 GB, 3 GB recorded per view)"},
         "views_per_s": args.views / (ms_per_step * 1e-3),
-        "clocks": clocks, "e2e": e2e, "gpu_launches": gpu_launches,
+        "clocks": clocks, "e2e": e2e, "gpu_launches": gpu_launches, "near_lists": near_lists,
         "roofline": roofline, "cpu_baseline": cpu_baseline, "secondary": secondary,
     }
     print(json.dumps(out))

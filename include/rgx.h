@@ -260,14 +260,14 @@ RGX_API int rgx_read_two_depth(rgx_ctx* ctx, long long out[4]);
 
 /* Lists up to a horizon for recording forwards (no counterpart in the reference).  A forward with
  * RGX_FLAG_SAVE_HITS -- a training view, whose rays end long before they have seen most of their tile's list --
- * sorts and lays out only the (tile, Gaussian) pairs that begin nearest to the eye, about `budget_per_ray` per ray
- * (default 6; views with fewer than 2^21 pairs, or whose budget covers half of them, get complete lists).  The march
- * counts the rays that would have needed more; if there are any, the complete lists are made and the whole view is
- * marched again (same image and recording as without the feature), and the budget is multiplied by four for the
- * views to come.  Costs one more wait on the stream per new view (the histogram that picks the horizon) and one
- * after the march (the count).  budget_per_ray = 0 switches the feature off, < 0 leaves it as it is.
- * rgx_read_near_lists returns and clears (views whose lists stopped at a horizon, pairs emitted for them, pairs
- * kept, views that had to be marched again). */
+ * emits, sorts and lays out only the (tile, Gaussian) pairs that begin nearest to the eye, about `budget_per_ray`
+ * per ray (default 6; the horizon is picked on the device from an estimate of the pairs by distance; views with
+ * fewer than 2^21 estimated pairs, or whose budget covers half of them, get complete lists).  The march counts the
+ * rays that would have needed more; if there are any, the complete lists are made and the whole view is marched
+ * again (same image and recording as without the feature), and the budget is multiplied by four for the views to
+ * come.  Costs one more wait on the stream after the march (the count).  budget_per_ray = 0 switches the feature
+ * off, < 0 leaves it as it is.  rgx_read_near_lists returns and clears (views whose lists stopped at a horizon,
+ * the estimated number of all pairs of those views, pairs kept, views that had to be marched again). */
 RGX_API int rgx_debug_near_lists(rgx_ctx* ctx, int budget_per_ray);
 RGX_API int rgx_read_near_lists(rgx_ctx* ctx, long long out[4]);
 

@@ -77,8 +77,14 @@ struct rgx_ctx {
     // lists of a recording forward's view may hold only the pairs that begin before a horizon (lists_from_pairs)
     bool lists_partial = false;
     float lists_horizon = 0.f;
+    long long lists_rays = 0;          // rays of the view the partial lists were made for
     int near_budget_per_ray = RGX_NEAR_BUDGET;   // pairs per ray such lists keep; multiplied by four whenever a ray reached the horizon
-    long long near_stats[4] = {0, 0, 0, 0};   // views with such lists, pairs emitted, pairs kept, views marched again
+    long long near_stats[4] = {0, 0, 0, 0};   // views with such lists, pairs of those views (estimate), pairs kept, views marched again
+    double near_ratio = 2.0;                  // estimated pairs (tile rectangles) per pair kept up to the horizon, from the latest such view
+    HorizonPick* near_pick = nullptr; HorizonPick* near_pick_host = nullptr;     // host copy pinned
+    unsigned long long* near_hist = nullptr;
+    uint2* g_rect = nullptr; unsigned int* g_code = nullptr; int g_rect_cap = 0;
+    int* tile_diff = nullptr; size_t tile_diff_cap = 0;
     unsigned long long lists_build_id = 0;
     rgx_camera lists_cam{};
     int lists_row_begin = 0, lists_row_end = 0;
@@ -308,8 +314,13 @@ void fill_sorted(const rgx_ctx* ctx, SortedGaussians& g) {
     g.n = ctx->n; g.n_pad = ctx->n_pad;
 }
 
-int run_colors(rgx_ctx* ctx, const rgx_scene* sc, const float eye[3], cudaStream_t s) {
+// listed_only: the current lists stop at a horizon; only the Gaussians that were emitted for them get their colours
+// (the march, the replay of its recording and a search over the same lists meet no others).
+int run_colors(rgx_ctx* ctx, const rgx_scene* sc, const float eye[3], cudaStream_t s, bool listed_only = false) {
     ColorLaunch c{};
+    if (listed_only && ctx->lists_partial && ctx->g_code) {
+        c.listed_rect = ctx->g_rect; c.listed_code = ctx->g_code; c.listed_cut = ctx->near_pick_host->cut;
+    }
     c.sc = *sc;
     std::memcpy(c.eye, eye, sizeof(c.eye));
     c.perm = ctx->vals_out;
@@ -465,7 +476,9 @@ static cudaError_t grow_pairs(rgx_ctx* ctx, size_t pairs) {
 
 // Emission of a view's (tile, Gaussian) pairs, unsorted, into ctx->bin_keys_in / bin_vals_in, in three steps so that
 // a caller can put other launches between the second and the third: workspace and launch parameters ...
-static int emit_setup(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, BinLaunch& b, int& ntiles) {
+static int two_depth_workspace(rgx_ctx* ctx, int ntiles, bool selection = true);
+
+static int emit_setup(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, BinLaunch& b, int& ntiles, bool near_only = false) {
     cudaError_t e = cudaSuccess;
     const int tiles_x = (cam->width + kBinTile - 1) / kBinTile;
     if (tiles_x > 65535) return fail(ctx, RGX_E_TOO_LARGE, "image wider than 65535 tiles");
@@ -504,6 +517,29 @@ static int emit_setup(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, B
     b.tiles_x = tiles_x; b.tiles_y = tiles_y; b.ty_first = ty_first;
     b.total_dev = ctx->bin_total_dev;
     b.big_slot = ctx->big_slot; b.big_rect = ctx->big_rect; b.big_grid = ctx->sm_count * 4;
+    if (near_only && ctx->near_budget_per_ray > 0) {
+        // the view of a recording forward: only the pairs that begin before a horizon are emitted (binning.cu)
+        int rc = two_depth_workspace(ctx, ntiles, false);   // tile_more, and the counter of rays that reach the horizon
+        if (rc) return rc;
+        if (!ctx->near_pick) {
+            RGB_(near_pick, 1); RGB_(near_hist, 2048);
+            if ((e = cudaMallocHost((void**)&ctx->near_pick_host, sizeof(HorizonPick))) != cudaSuccess)
+                return cuda_fail(ctx, e, "pinned horizon");
+        }
+        if (ctx->n_pad > ctx->g_rect_cap) {
+            RGB_(g_rect, (size_t)ctx->n_pad); RGB_(g_code, (size_t)ctx->n_pad);
+            ctx->g_rect_cap = ctx->n_pad;
+        }
+        const size_t diff = (size_t)(tiles_x + 1) * (size_t)(tiles_y + 1);
+        if (diff > ctx->tile_diff_cap) {
+            RGB_(tile_diff, diff + 64);
+            ctx->tile_diff_cap = diff + 64;
+        }
+        b.pick = ctx->near_pick; b.near_hist = ctx->near_hist; b.g_rect = ctx->g_rect; b.g_code = ctx->g_code;
+        b.tile_diff = ctx->tile_diff; b.tile_more = ctx->tile_more;
+        const double rays = (double)cam->width * (double)(m->row_end - m->row_begin);
+        b.near_target = (unsigned long long)((double)ctx->near_budget_per_ray * rays * ctx->near_ratio);
+    }
     return RGX_OK;
 }
 
@@ -514,6 +550,8 @@ static int emit_launch(rgx_ctx* ctx, BinLaunch& b, cudaStream_t s) {
     if ((e = launch_bin_emit(b, s)) != cudaSuccess) return cuda_fail(ctx, e, "tile-list pairs");
     if ((e = cudaMemcpyAsync(ctx->bin_total_host, ctx->bin_total_dev, sizeof(unsigned long long), cudaMemcpyDeviceToHost, s)) != cudaSuccess)
         return cuda_fail(ctx, e, "tile-list pair count read-back");
+    if (b.pick && (e = cudaMemcpyAsync(ctx->near_pick_host, b.pick, sizeof(HorizonPick), cudaMemcpyDeviceToHost, s)) != cudaSuccess)
+        return cuda_fail(ctx, e, "horizon read-back");
     return RGX_OK;
 }
 
@@ -535,8 +573,8 @@ static int emit_finish(rgx_ctx* ctx, BinLaunch& b, cudaStream_t s, int& total) {
 }
 
 static int emit_pairs(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, cudaStream_t s, BinLaunch& b, int& total,
-                      int& ntiles) {
-    int rc = emit_setup(ctx, cam, m, b, ntiles);
+                      int& ntiles, bool near_only = false) {
+    int rc = emit_setup(ctx, cam, m, b, ntiles, near_only);
     if (rc || (rc = emit_launch(ctx, b, s))) return rc;
     return emit_finish(ctx, b, s, total);
 }
@@ -580,7 +618,7 @@ static void lists_now_valid(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march
     ctx->last_pairs = total;
 }
 
-static int two_depth_workspace(rgx_ctx* ctx, int ntiles) {
+static int two_depth_workspace(rgx_ctx* ctx, int ntiles, bool selection) {
     cudaError_t e = cudaSuccess;
     if (!ctx->hz_hist) {
         RGB_(hz_hist, 2048); RGB_(hz_scalars, 4);
@@ -588,7 +626,7 @@ static int two_depth_workspace(rgx_ctx* ctx, int ntiles) {
             (e = cudaMallocHost((void**)&ctx->hz_scalars_host, 4 * sizeof(unsigned long long))) != cudaSuccess)
             return cuda_fail(ctx, e, "pinned histogram");
     }
-    if (ctx->bin_pair_cap > ctx->sel_cap) {
+    if (selection && ctx->bin_pair_cap > ctx->sel_cap) {
         RGB_(sel_keys, ctx->bin_pair_cap); RGB_(sel_vals, ctx->bin_pair_cap);
         ctx->sel_cap = ctx->bin_pair_cap;
     }
@@ -599,53 +637,29 @@ static int two_depth_workspace(rgx_ctx* ctx, int ntiles) {
     return RGX_OK;
 }
 
-// Turns the emitted pairs into ctx->lists.  near_only: the view belongs to a recording forward -- a training view,
-// whose rays end long before they have seen most of their tile's list (on the 3 M-Gaussian scene every ray ends within
-// the nearest eighth of the pairs).  Then only the pairs that begin before a horizon are sorted and laid out, about
-// near_budget_per_ray per ray: a histogram of the near distances picks the horizon (one more wait on `s`), the march
-// counts the rays that would have needed more (march_lists.cu, hz_phase 3), and forward_impl, should there be any,
-// makes the complete lists and marches the view again.  Sorting is the largest part of a view's list construction.
+// Turns the emitted pairs into ctx->lists.  The view of a recording forward -- a training view, whose rays end long
+// before they have seen most of their tile's list (on the 3 M-Gaussian scene every ray ends within the nearest eighth
+// of the pairs) -- was emitted only up to a horizon (emit_setup with near_only; binning.cu picks the horizon so that
+// about near_budget_per_ray pairs per ray begin before it): such lists are marked partial, the march counts the rays
+// that would have needed more (march_lists.cu, hz_phase 3), and forward_impl, should there be any, makes the complete
+// lists and marches the view again.  Emission and sorting are nearly all of a view's list construction.
 static int lists_from_pairs(rgx_ctx* ctx, BinLaunch& b, int total, int ntiles, const rgx_camera* cam, const rgx_march* m,
-                            bool near_only, cudaStream_t s) {
-    cudaError_t e = cudaSuccess;
+                            cudaStream_t s) {
     int rc;
-    const long long rays = (long long)cam->width * (m->row_end - m->row_begin);
-    const long long budget = (long long)ctx->near_budget_per_ray * rays;
-    if (near_only && total >= (1 << 21) && budget * 2 < (long long)total) {
-        if ((rc = two_depth_workspace(ctx, ntiles))) return rc;
-        if ((e = cudaMemsetAsync(ctx->hz_hist, 0, 2048 * sizeof(unsigned int), s)) != cudaSuccess ||
-            (e = cudaMemsetAsync(ctx->tile_more, 0, sizeof(int) * (size_t)ntiles, s)) != cudaSuccess ||
-            (e = cudaMemsetAsync(ctx->hz_scalars, 0, 4 * sizeof(unsigned long long), s)) != cudaSuccess ||
-            (e = launch_bin_hist(b, total, ctx->hz_hist, s)) != cudaSuccess ||
-            (e = cudaMemcpyAsync(ctx->hz_hist_host, ctx->hz_hist, 2048 * sizeof(unsigned int), cudaMemcpyDeviceToHost, s)) != cudaSuccess ||
-            (e = cudaStreamSynchronize(s)) != cudaSuccess)
-            return cuda_fail(ctx, e, "near-distance histogram");
-        long long cum = 0;
-        int cut = -1;
-        for (int i = 0; i < 2048; ++i) {
-            if (ctx->hz_hist_host[i] == 0) continue;
-            if (cut >= 0 && cum + ctx->hz_hist_host[i] > budget) break;
-            cum += ctx->hz_hist_host[i];
-            cut = i;
-        }
-        if (cut >= 0 && cum * 2 < (long long)total) {            // worth it: less than half of the pairs
-            if ((e = launch_bin_select(b, total, 0, (unsigned int)cut, nullptr, ctx->sel_keys, ctx->sel_vals, ctx->hz_scalars,
-                                       ctx->tile_more, s)) != cudaSuccess)
-                return cuda_fail(ctx, e, "pair selection");
-            uint64_t* all_keys = b.keys_in;
-            uint32_t* all_vals = b.vals_in;
-            rc = fill_lists(ctx, b, ctx->sel_keys, ctx->sel_vals, (int)cum, ntiles, s);
-            b.keys_in = all_keys; b.vals_in = all_vals;
-            if (rc) return rc;
-            lists_now_valid(ctx, cam, m, total);
-            ctx->lists_partial = true;
-            ctx->lists_horizon = bin_hist_bucket_end(b, cut);
-            ctx->near_stats[0] += 1; ctx->near_stats[1] += total; ctx->near_stats[2] += cum;
-            return RGX_OK;
-        }
-    }
     if ((rc = fill_lists(ctx, b, ctx->bin_keys_in, ctx->bin_vals_in, total, ntiles, s))) return rc;
     lists_now_valid(ctx, cam, m, total);
+    if (b.pick && ctx->near_pick_host->cut != kAllBuckets) {
+        const HorizonPick& pk = *ctx->near_pick_host;
+        ctx->lists_partial = true;
+        ctx->lists_horizon = bin_hist_bucket_end(b, (int)pk.cut);
+        ctx->lists_rays = (long long)cam->width * (m->row_end - m->row_begin);
+        ctx->near_stats[0] += 1; ctx->near_stats[1] += (long long)pk.est_total; ctx->near_stats[2] += total;
+        // the estimate counts every tile of a Gaussian's rectangle; what it is worth in pairs is learnt from view to view
+        if (total > 0) {
+            const double r = (double)pk.est_kept / (double)total;
+            ctx->near_ratio = std::min(8.0, std::max(1.0, r));
+        }
+    }
     return RGX_OK;
 }
 
@@ -659,9 +673,9 @@ static int ensure_lists(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m,
     ScopedTimer timer(ctx, s, 2);
     BinLaunch b;
     int total = 0, ntiles = 0;
-    int rc = emit_pairs(ctx, cam, m, s, b, total, ntiles);
+    int rc = emit_pairs(ctx, cam, m, s, b, total, ntiles, near_only);
     if (rc) return rc;
-    return lists_from_pairs(ctx, b, total, ntiles, cam, m, near_only, s);
+    return lists_from_pairs(ctx, b, total, ntiles, cam, m, s);
 }
 
 // Lists of the announced view, made on the context's own stream while the stream of the caller replays a
@@ -700,7 +714,8 @@ static void lists_ahead_begin(rgx_ctx* ctx, cudaStream_t s, ListsAhead& a) {
     }
     if (cudaEventRecord(ctx->ev_main, s) != cudaSuccess || cudaStreamWaitEvent(ctx->side, ctx->ev_main, 0) != cudaSuccess) return;
     ctx->lists_valid = false;                      // from here on the list arrays belong to the announced view
-    if (emit_setup(ctx, cam, m, a.b, a.ntiles) || emit_launch(ctx, a.b, ctx->side)) {
+    const bool near_only = (m->flags & RGX_FLAG_SAVE_HITS) && !(m->flags & RGX_FLAG_COUNT_WORK);
+    if (emit_setup(ctx, cam, m, a.b, a.ntiles, near_only) || emit_launch(ctx, a.b, ctx->side)) {
         cudaEventRecord(ctx->ev_lists, ctx->side);
         ctx->lists_event_set = true;
         return;
@@ -713,9 +728,8 @@ static void lists_ahead_end(rgx_ctx* ctx, ListsAhead& a) {
     int total = 0;
     {
         ScopedTimer timer(ctx, ctx->side, 2);
-        const bool near_only = (ctx->hint_march.flags & RGX_FLAG_SAVE_HITS) && !(ctx->hint_march.flags & RGX_FLAG_COUNT_WORK);
         if (emit_finish(ctx, a.b, ctx->side, total) == RGX_OK &&
-            lists_from_pairs(ctx, a.b, total, a.ntiles, &ctx->hint_cam, &ctx->hint_march, near_only, ctx->side) == RGX_OK)
+            lists_from_pairs(ctx, a.b, total, a.ntiles, &ctx->hint_cam, &ctx->hint_march, ctx->side) == RGX_OK)
             ctx->prefetched++;
     }
     cudaEventRecord(ctx->ev_lists, ctx->side);
@@ -841,8 +855,9 @@ static int forward_impl(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* 
     if (!rgb && !frame) return fail(ctx, RGX_E_INVALID, "colour output is null");
     cudaStream_t s = (cudaStream_t)stream;
     join_side(ctx, s);
-    if ((rc = run_colors(ctx, scene, cam->eye, s))) return rc;
     L.rgb = rgb; L.alpha = alpha; L.depth = depth; L.frame = frame;
+    const bool counting = (march->flags & RGX_FLAG_COUNT_WORK) != 0;
+    bool have_colors = false;
     if (!(march->flags & (RGX_FLAG_BRUTE_FORCE | RGX_FLAG_PER_RAY_SEARCH))) {
         // a forward that nothing follows (no recording, no counting) and whose lists are yet to be made may take
         // the two-depth path, if the view turns out to have far more pairs than rays
@@ -850,6 +865,8 @@ static int forward_impl(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* 
                                   march->row_end > march->row_begin && ctx->hz_min_pairs_per_ray >= 0;
         if (forward_only && !lists_cached(ctx, cam, march)) {
             bool handled = false;
+            if ((rc = run_colors(ctx, scene, cam->eye, s))) return rc;
+            have_colors = true;
             if ((rc = forward_two_depth(ctx, cam, march, L, s, handled))) return rc;
             if (handled) return RGX_OK;
         } else {
@@ -859,7 +876,8 @@ static int forward_impl(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* 
         }
         L.lists = ctx->lists;
     }
-    const bool counting = (march->flags & RGX_FLAG_COUNT_WORK) != 0;
+    if (!have_colors && (rc = run_colors(ctx, scene, cam->eye, s, L.lists.ent_id != nullptr && ctx->lists_partial && !counting)))
+        return rc;
     // one march of the view over the lists in L.lists (a lambda: a view whose lists stop at a horizon may need a second one)
     auto march_once = [&]() -> int {
         cudaError_t e;
@@ -951,10 +969,12 @@ static int forward_impl(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* 
         if (e1 != cudaSuccess) return cuda_fail(ctx, e1, "horizon read-back");
         if ((ctx->hz_scalars_host[1] & 0xffffffffull) == 0ull) return RGX_OK;      // every ray ended before the horizon
         // some ray reached the horizon: the complete lists, the whole view again, and deeper lists from now on
+        // (unless the lists fell short of the budget: then the estimate was off, and has been corrected already)
         ctx->near_stats[3] += 1;
-        ctx->near_budget_per_ray = ctx->near_budget_per_ray < (1 << 18) ? ctx->near_budget_per_ray * 4 : ctx->near_budget_per_ray;
+        if ((double)ctx->last_pairs >= 0.75 * (double)ctx->near_budget_per_ray * (double)ctx->lists_rays && ctx->near_budget_per_ray < (1 << 18))
+            ctx->near_budget_per_ray *= 4;
         ctx->lists_valid = false;
-        if ((rc = ensure_lists(ctx, cam, march, s))) return rc;
+        if ((rc = ensure_lists(ctx, cam, march, s)) || (rc = run_colors(ctx, scene, cam->eye, s))) return rc;
         L.lists = ctx->lists;
     }
 }

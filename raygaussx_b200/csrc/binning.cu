@@ -27,6 +27,7 @@ constexpr unsigned kFullMask = 0xffffffffu;
 struct Projector {     // pixel coordinates of a world point: px = (a / (2 tan) + pp) * size - 0.5
     float eye[3], du[3], dv[3], dw[3];   // dual basis of (u, v, w)
     float sx, sy, ox, oy;                // px = a * sx + ox, py = b * sy + oy
+    float plane[4][4];                   // the view's four side planes through the eye: inward normal, and its length
 };
 
 __device__ __forceinline__ Projector make_projector(const BinLaunch& b) {
@@ -36,6 +37,18 @@ __device__ __forceinline__ Projector make_projector(const BinLaunch& b) {
     p.sy = (float)b.cam.height / (2.0f * b.cam.tan_half_fov[1]);
     p.ox = b.cam.pp[0] * (float)b.cam.width - 0.5f;
     p.oy = b.cam.pp[1] * (float)b.cam.height - 0.5f;
+    // a point eye + t (a u + b v + w), t > 0, of a ray of the rows at hand has a within [a0, a1] and b within [b0, b1]
+    // (one pixel of margin), that is x_c - a0 z_c >= 0, a1 z_c - x_c >= 0 and the same for rows
+    const float a0 = (-1.0f - p.ox) / p.sx, a1 = ((float)b.cam.width - p.ox) / p.sx;
+    const float b0 = ((float)b.row_begin - 1.0f - p.oy) / p.sy, b1 = ((float)b.row_end - p.oy) / p.sy;
+    for (int k = 0; k < 3; ++k) {
+        p.plane[0][k] = p.du[k] - a0 * p.dw[k];
+        p.plane[1][k] = a1 * p.dw[k] - p.du[k];
+        p.plane[2][k] = p.dv[k] - b0 * p.dw[k];
+        p.plane[3][k] = b1 * p.dw[k] - p.dv[k];
+    }
+    for (int q = 0; q < 4; ++q)
+        p.plane[q][3] = sqrtf(p.plane[q][0] * p.plane[q][0] + p.plane[q][1] * p.plane[q][1] + p.plane[q][2] * p.plane[q][2]);
     return p;
 }
 
@@ -139,7 +152,9 @@ __global__ void bin_tile_dirs_kernel(BinLaunch b, int ntiles) {
         float3 d = pixel_dir(b.cam, (c & 1) ? x1 : x0, (c & 2) ? y1 : y0) - dc;
         chord = fmaxf(chord, sqrtf(dot3(d, d)));
     }
-    b.tile_dir[t] = make_float4(dc.x, dc.y, dc.z, chord * 1.001f + 1e-7f);
+    const float w = chord * 1.001f + 1e-7f;
+    b.tile_dir[t] = make_float4(dc.x, dc.y, dc.z, w);
+    if (b.pick) atomicMax(&b.pick->chord_bits, __float_as_uint(w));      // positive floats order like their bits
 }
 
 // Per-Gaussian data needed to bound its meeting with a tile.
@@ -296,80 +311,225 @@ __device__ __forceinline__ void emit_flush(const BinLaunch& b, EmitShared& sh, i
     __syncthreads();
 }
 
+// Rectangle of tiles that Gaussian j can touch: the rectangle of its box cut by the rectangle of the oriented box
+// of its truncation ellipsoid.  Returns the number of tiles (0: none, rect untouched).
+__device__ __forceinline__ int gaussian_rect(const BinLaunch& b, const Projector& p, int j, float2 bx, float2 by, float2 bz,
+                                             uint2& rect) {
+    const int W = b.cam.width, H = b.cam.height;
+    const int tiles_x_all = (W + b.tile - 1) / b.tile, tiles_y_all = (H + b.tile - 1) / b.tile;
+    {
+        // most Gaussians lie outside the view: the sphere about the box against the four side planes
+        const float cx = 0.5f * (bx.x + bx.y) - p.eye[0], cy = 0.5f * (by.x + by.y) - p.eye[1], cz = 0.5f * (bz.x + bz.y) - p.eye[2];
+        const float hx = 0.5f * (bx.y - bx.x), hy = 0.5f * (by.y - by.x), hz = 0.5f * (bz.y - bz.x);
+        const float r = sqrtf(hx * hx + hy * hy + hz * hz) * (1.0f + 1e-4f), far = sqrtf(cx * cx + cy * cy + cz * cz);
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            if (p.plane[q][0] * cx + p.plane[q][1] * cy + p.plane[q][2] * cz < -(r + 1e-5f * far + 1e-7f) * p.plane[q][3]) return 0;
+    }
+    float xc[8], yc[8], zc[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+        to_camera(p, (c & 1) ? bx.y : bx.x, (c & 2) ? by.y : by.x, (c & 4) ? bz.y : bz.x, xc[c], yc[c], zc[c]);
+    float lox, hix, loy, hiy;
+    int kind = project_corners(p, xc, yc, zc, lox, hix, loy, hiy);
+    if (kind == 0) return 0;
+    if (kind == 2) {
+        straddle_tiles(xc, zc, p.sx, p.ox, tiles_x_all, b.tile, W, lox, hix);
+        straddle_tiles(yc, zc, p.sy, p.oy, tiles_y_all, b.tile, H, loy, hiy);
+    }
+    {
+        // oriented box of the ellipsoid {x : |S^-1 R^T (x - p)| <= k}: centre +- k s_a col_a
+        const float4 sd = b.sdens[j], q = b.quat[j], g0 = b.g0[j];
+        const float k = sqrtf(2.0f * 0.6931471805599453f * b.hk[j]) * 1.0001f;
+        float3 U, V, Wc;
+        quat_to_columns(q, U, V, Wc);
+        float3 e0 = U * (k * sd.x), e1 = V * (k * sd.y), e2 = Wc * (k * sd.z);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            float sa = (c & 1) ? 1.f : -1.f, sb = (c & 2) ? 1.f : -1.f, sc = (c & 4) ? 1.f : -1.f;
+            to_camera(p, g0.x + sa * e0.x + sb * e1.x + sc * e2.x, g0.y + sa * e0.y + sb * e1.y + sc * e2.y,
+                      g0.z + sa * e0.z + sb * e1.z + sc * e2.z, xc[c], yc[c], zc[c]);
+        }
+        float olx, ohx, oly, ohy;
+        int okind = project_corners(p, xc, yc, zc, olx, ohx, oly, ohy);
+        if (okind == 0) return 0;
+        if (okind == 2) {
+            straddle_tiles(xc, zc, p.sx, p.ox, tiles_x_all, b.tile, W, olx, ohx);
+            straddle_tiles(yc, zc, p.sy, p.oy, tiles_y_all, b.tile, H, oly, ohy);
+        }
+        lox = fmaxf(lox, olx); hix = fminf(hix, ohx); loy = fmaxf(loy, oly); hiy = fminf(hiy, ohy);
+    }
+    // rays sit at integer pixel coordinates; keep a small safety margin for rounding
+    const float m = 0.02f;
+    float fx0 = ceilf(lox - m - 1e-5f * fabsf(lox)), fx1 = floorf(hix + m + 1e-5f * fabsf(hix));
+    float fy0 = ceilf(loy - m - 1e-5f * fabsf(loy)), fy1 = floorf(hiy + m + 1e-5f * fabsf(hiy));
+    fx0 = fmaxf(fx0, 0.f); fx1 = fminf(fx1, (float)W - 1.f);
+    fy0 = fmaxf(fy0, (float)b.row_begin); fy1 = fminf(fy1, (float)b.row_end - 1.f);
+    if (!(fx0 <= fx1 && fy0 <= fy1)) return 0;
+    const unsigned tx0 = (unsigned)fx0 / b.tile, tx1 = (unsigned)fx1 / b.tile;
+    const unsigned ty0 = (unsigned)fy0 / b.tile - b.ty_first, ty1 = (unsigned)fy1 / b.tile - b.ty_first;
+    rect = make_uint2(tx0 | (tx1 << 16), ty0 | (ty1 << 16));
+    return (int)((tx1 - tx0 + 1) * (ty1 - ty0 + 1));
+}
+
+constexpr int kHistBits = 11;      // leading bits of the quantised near distance: its exponent bits and 3 to 6 of the mantissa
+constexpr unsigned kNoRect = 0xffffffffu;
+
+__device__ __forceinline__ unsigned hist_bucket(float tn, const KeyLayout& kl) {
+    return near_quantised(tn, kl) >> (kl.near_bits - kHistBits);
+}
+
+// ---------------------------------------------------------------- culled emission (views of recording forwards)
+//
+// A training view's rays end long before they have seen most of their tile's list, so its lists need only
+// hold the pairs that begin before a horizon (about near_target of them), and the pairs beyond need not even be
+// emitted.  The horizon is picked before the emission, on the device, from what is cheap to know of a Gaussian:
+// the rectangle of tiles it can touch (an upper bound of its pairs) and a lower bound of the distance at which any
+// of its pairs begins.  bin_near_hist_kernel: those two per Gaussian, and their histogram; bin_pick_horizon_kernel:
+// the bucket at which the running sum reaches the target; the emission kernels then skip Gaussians and pairs that
+// lie in later buckets and note, per tile, that something was skipped (tile_more; for a skipped Gaussian all tiles
+// of its rectangle, added up from rectangle corners by bin_tile_more_kernel).
+
+__global__ void __launch_bounds__(kEmitThreads) bin_near_hist_kernel(BinLaunch b) {
+    __shared__ unsigned int local[1 << kHistBits];
+    for (int i = threadIdx.x; i < (1 << kHistBits); i += kEmitThreads) local[i] = 0u;
+    __syncthreads();
+    const int j = blockIdx.x * kEmitThreads + threadIdx.x;
+    uint2 rect = make_uint2(kNoRect, 0u);
+    unsigned code = 0u;
+    if (j < b.n) {
+        const float2 bx = b.bx[j], by = b.by[j], bz = b.bz[j];
+        if (bx.x <= bx.y) {
+            const Projector p = make_projector(b);
+            const KeyLayout kl = key_layout(b.tiles_x * ((b.cam.height + b.tile - 1) / b.tile), b.n_pad);
+            uint2 r;
+            const int count = gaussian_rect(b, p, j, bx, by, bz, r);
+            if (count > 0) {
+                // No pair of this Gaussian begins before `gn`: a pair's near distance is where the tile's central ray
+                // enters the box grown by far_box * chord (pair_range), a point no nearer to the eye than the box less
+                // sqrt(3) times that; the margins are ten times those pair_range takes off.
+                const float* e = b.cam.eye;
+                const float dx = fmaxf(fmaxf(bx.x - e[0], e[0] - bx.y), 0.f), dy = fmaxf(fmaxf(by.x - e[1], e[1] - by.y), 0.f),
+                            dz = fmaxf(fmaxf(bz.x - e[2], e[2] - bz.y), 0.f);
+                const float fx = fmaxf(fabsf(bx.x - e[0]), fabsf(bx.y - e[0])), fy = fmaxf(fabsf(by.x - e[1]), fabsf(by.y - e[1])),
+                            fz = fmaxf(fabsf(bz.x - e[2]), fabsf(bz.y - e[2]));
+                const float far_box = sqrtf(fx * fx + fy * fy + fz * fz) * (1.0f + 1e-5f) + 1e-6f;
+                const float infl = far_box * __uint_as_float(b.pick->chord_bits) * 1.0001f + 1e-6f;
+                const float gn = fmaxf((sqrtf(dx * dx + dy * dy + dz * dz) - 1.7321f * infl) * (1.0f - 1e-4f) - 1e-4f, 0.f);
+                code = hist_bucket(gn, kl);
+                rect = r;
+                atomicAdd(&local[code], (unsigned)count);
+            }
+        }
+    }
+    if (j < b.n_pad) { b.g_rect[j] = rect; b.g_code[j] = code; }
+    __syncthreads();
+    for (int i = threadIdx.x; i < (1 << kHistBits); i += kEmitThreads)
+        if (local[i]) atomicAdd(&b.near_hist[i], (unsigned long long)local[i]);
+}
+
+// The cut: the last non-empty bucket up to which the estimated pairs stay within the target (the first non-empty
+// one if none does).  Everything is kept (cut = kAllBuckets) when the view has fewer than min_total estimated
+// pairs or the cut would keep half of them or more.
+__global__ void __launch_bounds__(1024) bin_pick_horizon_kernel(BinLaunch b, unsigned long long min_total) {
+    using Scan = cub::BlockScan<unsigned long long, 1024>;
+    __shared__ typename Scan::TempStorage scan_tmp;
+    __shared__ int s_cut, s_first;
+    const int t = threadIdx.x;
+    const unsigned long long h0 = b.near_hist[2 * t], h1 = b.near_hist[2 * t + 1];
+    unsigned long long incl, total;
+    if (t == 0) { s_cut = -1; s_first = 1 << kHistBits; }
+    __syncthreads();
+    Scan(scan_tmp).InclusiveSum(h0 + h1, incl, total);
+    const unsigned long long p0 = incl - h1, p1 = incl;
+    if (h0) { atomicMin(&s_first, 2 * t); if (p0 <= b.near_target) atomicMax(&s_cut, 2 * t); }
+    if (h1) { atomicMin(&s_first, 2 * t + 1); if (p1 <= b.near_target) atomicMax(&s_cut, 2 * t + 1); }
+    __syncthreads();
+    const int cut = s_cut >= 0 ? s_cut : s_first;
+    if (t == 0) b.pick->est_total = total;
+    if (cut >= (1 << kHistBits)) { if (t == 0) { b.pick->cut = kAllBuckets; b.pick->est_kept = total; } return; }
+    if (t == (cut >> 1)) {
+        const unsigned long long kept = (cut & 1) ? p1 : p0;
+        const bool partial = total >= min_total && kept * 2 < total && cut + 1 < (1 << kHistBits);
+        b.pick->cut = partial ? (unsigned)cut : kAllBuckets;
+        b.pick->est_kept = partial ? kept : total;
+    }
+}
+
+// tile_diff holds +1 / -1 at the corners of the rectangles of the skipped Gaussians; its two-dimensional running
+// sum is the number of skipped rectangles over each tile.
+constexpr int kDiffShared = 12000;
+__global__ void __launch_bounds__(1024) bin_tile_more_kernel(BinLaunch b) {
+    __shared__ int s_diff[kDiffShared];
+    const int W = b.tiles_x + 1, H = b.tiles_y + 1;
+    int* d = b.tile_diff;
+    if (W * H <= kDiffShared) {
+        for (int i = threadIdx.x; i < W * H; i += blockDim.x) s_diff[i] = b.tile_diff[i];
+        d = s_diff;
+    }
+    __syncthreads();
+    for (int r = threadIdx.x; r < H; r += blockDim.x) {
+        int run = 0;
+        for (int c = 0; c < W; ++c) { run += d[r * W + c]; d[r * W + c] = run; }
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < b.tiles_x; c += blockDim.x) {
+        int run = 0;
+        for (int r = 0; r < b.tiles_y; ++r) {
+            run += d[r * W + c];
+            if (run > 0) b.tile_more[r * b.tiles_x + c] = 1;
+        }
+    }
+}
+
 // One block per 256 sorted slots.  First every thread finds its Gaussian's rectangle of
 // tiles (box rectangle cut by the rectangle of the oriented box of the truncation
 // ellipsoid).  Then the block walks all (Gaussian, tile) candidates of its 256 Gaussians
 // together, one candidate per thread and round, whatever Gaussian it belongs to -- a
 // Gaussian that covers the screen costs its block a few rounds, not one thread thousands
 // of iterations -- and keeps the pairs in which some ray of the tile can meet the Gaussian.
+// CULL: rectangles and buckets come from bin_near_hist_kernel; what lies beyond the cut is skipped.
+template <bool CULL>
 __global__ void __launch_bounds__(kEmitThreads) bin_emit_kernel(BinLaunch b) {
     __shared__ EmitShared sh;
     using Scan = cub::BlockScan<int, kEmitThreads>;
     __shared__ typename Scan::TempStorage scan_tmp;
     const int tid = threadIdx.x, lane = tid & 31;
     const int j = blockIdx.x * kEmitThreads + tid;
+    const unsigned cut = CULL ? b.pick->cut : kAllBuckets;
     int count = 0;
     if (j < b.n) {
         const float2 bx = b.bx[j], by = b.by[j], bz = b.bz[j];
         if (bx.x <= bx.y) {
-            const Projector p = make_projector(b);
-            const int W = b.cam.width, H = b.cam.height;
-            const int tiles_x_all = (W + b.tile - 1) / b.tile, tiles_y_all = (H + b.tile - 1) / b.tile;
-            float xc[8], yc[8], zc[8];
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-                to_camera(p, (c & 1) ? bx.y : bx.x, (c & 2) ? by.y : by.x, (c & 4) ? bz.y : bz.x, xc[c], yc[c], zc[c]);
-            float lox, hix, loy, hiy;
-            int kind = project_corners(p, xc, yc, zc, lox, hix, loy, hiy);
-            if (kind == 2) {
-                straddle_tiles(xc, zc, p.sx, p.ox, tiles_x_all, b.tile, W, lox, hix);
-                straddle_tiles(yc, zc, p.sy, p.oy, tiles_y_all, b.tile, H, loy, hiy);
-            }
-            const float4 sd = b.sdens[j], q = b.quat[j], g0 = b.g0[j];
-            const float kk = sqrtf(2.0f * 0.6931471805599453f * b.hk[j]);
-            if (kind != 0) {
-                // oriented box of the ellipsoid {x : |S^-1 R^T (x - p)| <= k}: centre +- k s_a col_a
-                const float k = kk * 1.0001f;
-                float3 U, V, Wc;
-                quat_to_columns(q, U, V, Wc);
-                float3 e0 = U * (k * sd.x), e1 = V * (k * sd.y), e2 = Wc * (k * sd.z);
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    float sa = (c & 1) ? 1.f : -1.f, sb = (c & 2) ? 1.f : -1.f, sc = (c & 4) ? 1.f : -1.f;
-                    to_camera(p, g0.x + sa * e0.x + sb * e1.x + sc * e2.x, g0.y + sa * e0.y + sb * e1.y + sc * e2.y,
-                              g0.z + sa * e0.z + sb * e1.z + sc * e2.z, xc[c], yc[c], zc[c]);
-                }
-                float olx, ohx, oly, ohy;
-                int okind = project_corners(p, xc, yc, zc, olx, ohx, oly, ohy);
-                if (okind == 0) kind = 0;
-                else {
-                    if (okind == 2) {
-                        straddle_tiles(xc, zc, p.sx, p.ox, tiles_x_all, b.tile, W, olx, ohx);
-                        straddle_tiles(yc, zc, p.sy, p.oy, tiles_y_all, b.tile, H, oly, ohy);
+            uint2 rect = make_uint2(kNoRect, 0u);
+            if (CULL) {
+                rect = b.g_rect[j];
+                if (rect.x != kNoRect) {
+                    const unsigned tx0 = rect.x & 0xffffu, tx1 = rect.x >> 16, ty0 = rect.y & 0xffffu, ty1 = rect.y >> 16;
+                    if (b.g_code[j] > cut) {            // every pair of this Gaussian begins beyond the horizon
+                        const int Wd = b.tiles_x + 1;
+                        atomicAdd(&b.tile_diff[ty0 * Wd + tx0], 1);
+                        atomicAdd(&b.tile_diff[ty0 * Wd + tx1 + 1], -1);
+                        atomicAdd(&b.tile_diff[(ty1 + 1) * Wd + tx0], -1);
+                        atomicAdd(&b.tile_diff[(ty1 + 1) * Wd + tx1 + 1], 1);
+                    } else {
+                        count = (int)((tx1 - tx0 + 1) * (ty1 - ty0 + 1));
                     }
-                    lox = fmaxf(lox, olx); hix = fminf(hix, ohx); loy = fmaxf(loy, oly); hiy = fminf(hiy, ohy);
                 }
+            } else {
+                const Projector p = make_projector(b);
+                count = gaussian_rect(b, p, j, bx, by, bz, rect);
             }
-            if (kind != 0) {
-                // rays sit at integer pixel coordinates; keep a small safety margin for rounding
-                const float m = 0.02f;
-                float fx0 = ceilf(lox - m - 1e-5f * fabsf(lox)), fx1 = floorf(hix + m + 1e-5f * fabsf(hix));
-                float fy0 = ceilf(loy - m - 1e-5f * fabsf(loy)), fy1 = floorf(hiy + m + 1e-5f * fabsf(hiy));
-                fx0 = fmaxf(fx0, 0.f); fx1 = fminf(fx1, (float)W - 1.f);
-                fy0 = fmaxf(fy0, (float)b.row_begin); fy1 = fminf(fy1, (float)b.row_end - 1.f);
-                if (fx0 <= fx1 && fy0 <= fy1) {
-                    unsigned tx0 = (unsigned)fx0 / b.tile, tx1 = (unsigned)fx1 / b.tile;
-                    unsigned ty0 = (unsigned)fy0 / b.tile - b.ty_first, ty1 = (unsigned)fy1 / b.tile - b.ty_first;
-                    sh.rect[tid] = make_uint2(tx0 | (tx1 << 16), ty0 | (ty1 << 16));
-                    count = (int)((tx1 - tx0 + 1) * (ty1 - ty0 + 1));
-                    if (count > kBigRect) {
-                        const unsigned long long at = atomicAdd(b.total_dev + 1, 1ull);
-                        b.big_slot[at] = j;
-                        b.big_rect[at] = sh.rect[tid];
-                        count = 0;
-                    }
-                    const PairGeom g = make_pair_geom(p.eye, bx, by, bz, g0, b.g1[j], b.g2[j], sd, q, kk);
-                    sh.geom[tid] = g;
+            if (count > 0) {
+                sh.rect[tid] = rect;
+                if (count > kBigRect) {
+                    const unsigned long long at = atomicAdd(b.total_dev + 1, 1ull);
+                    b.big_slot[at] = j;
+                    b.big_rect[at] = rect;
+                    count = 0;
+                } else {
+                    const float kk = sqrtf(2.0f * 0.6931471805599453f * b.hk[j]);
+                    sh.geom[tid] = make_pair_geom(b.cam.eye, bx, by, bz, b.g0[j], b.g1[j], b.g2[j], b.sdens[j], b.quat[j], kk);
                 }
             }
         }
@@ -399,6 +559,7 @@ __global__ void __launch_bounds__(kEmitThreads) bin_emit_kernel(BinLaunch b) {
             const unsigned t = (ty0 + local / w) * (unsigned)b.tiles_x + tx0 + local % w;
             float tn;
             keep = pair_range(b.cam.eye, b.tile_dir[t], sh.geom[lo], tn, tf);
+            if (CULL && keep && hist_bucket(tn, kl) > cut) { keep = false; b.tile_more[t] = 1; }
             if (keep) key = pair_key(kl, t, tn, (unsigned)(blockIdx.x * kEmitThreads + lo));
         }
         const unsigned m = __ballot_sync(kFullMask, keep);
@@ -419,7 +580,9 @@ __global__ void __launch_bounds__(kEmitThreads) bin_emit_kernel(BinLaunch b) {
 constexpr int kBigWarps = 8;
 constexpr int kBigBuf = 256;
 
+template <bool CULL>
 __global__ void __launch_bounds__(kBigWarps * 32) bin_emit_big_kernel(BinLaunch b) {
+    const unsigned cut = CULL ? b.pick->cut : kAllBuckets;
     __shared__ unsigned long long s_keys[kBigWarps][kBigBuf];
     __shared__ float s_fars[kBigWarps][kBigBuf];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -461,6 +624,7 @@ __global__ void __launch_bounds__(kBigWarps * 32) bin_emit_big_kernel(BinLaunch 
                 const unsigned t = (ty0 + item / w) * (unsigned)b.tiles_x + tx0 + item % w;
                 float tn;
                 keep = pair_range(b.cam.eye, b.tile_dir[t], g, tn, tf);
+                if (CULL && keep && hist_bucket(tn, kl) > cut) { keep = false; b.tile_more[t] = 1; }
                 if (keep) key = pair_key(kl, t, tn, (unsigned)j);
             }
             const unsigned m = __ballot_sync(kFullMask, keep);
@@ -528,8 +692,6 @@ __global__ void __launch_bounds__(256) bin_blocks_kernel(BinLaunch b, size_t n_b
 // or two, look at a few.  For such a view the pairs are not sorted all at once: a histogram of their near
 // distances picks a depth, only the pairs that begin before it are sorted and marched, and the rest is
 // sorted only for the tiles in which some ray got that far (march_lists.cu, horizon variant).
-
-constexpr int kHistBits = 11;      // leading bits of the quantised near distance: its exponent bits and 3 to 6 of the mantissa
 
 __global__ void __launch_bounds__(256) bin_hist_kernel(const uint64_t* __restrict__ keys, int total, int shift,
                                                        unsigned int* hist) {
@@ -604,17 +766,36 @@ size_t binning_cub_temp_bytes(size_t pair_cap, int ntiles) {
     return a > d ? a : d;
 }
 
-// Phase 1: all (tile, Gaussian) pairs, unsorted, and their number in b.total_dev (which keeps
-// counting past b.pair_cap; the caller reads it back and repeats the phase with more room if needed).
+// Phase 1: all (tile, Gaussian) pairs -- with b.pick those that begin before the horizon picked on the way --,
+// unsorted, and their number in b.total_dev (which keeps counting past b.pair_cap; the caller reads it back and
+// repeats the phase with more room if needed).
 cudaError_t launch_bin_emit(const BinLaunch& b, cudaStream_t s) {
     const int tb = 256;
     const int ntiles = b.tiles_x * b.tiles_y;
     cudaError_t e;
     // total_dev: [0] pairs, [1] length of the list of large Gaussians, [2] next of them to take
     if ((e = cudaMemsetAsync(b.total_dev, 0, 4 * sizeof(unsigned long long), s)) != cudaSuccess) return e;
+    const int blocks = (b.n_pad + kEmitThreads - 1) / kEmitThreads;
+    if (b.pick) {
+        // only the pairs that begin before a horizon, which is picked on the way (see bin_near_hist_kernel)
+        const KeyLayout kl = key_layout(b.tiles_x * ((b.cam.height + b.tile - 1) / b.tile), b.n_pad);
+        if (kl.near_bits < kHistBits) return cudaErrorInvalidValue;
+        if ((e = cudaMemsetAsync(b.pick, 0, sizeof(HorizonPick), s)) != cudaSuccess ||
+            (e = cudaMemsetAsync(b.near_hist, 0, sizeof(unsigned long long) << kHistBits, s)) != cudaSuccess ||
+            (e = cudaMemsetAsync(b.tile_diff, 0, sizeof(int) * (size_t)(b.tiles_x + 1) * (size_t)(b.tiles_y + 1), s)) != cudaSuccess ||
+            (e = cudaMemsetAsync(b.tile_more, 0, sizeof(int) * (size_t)ntiles, s)) != cudaSuccess)
+            return e;
+        note_launch(), bin_tile_dirs_kernel<<<(ntiles + tb - 1) / tb, tb, 0, s>>>(b, ntiles);
+        note_launch(), bin_near_hist_kernel<<<blocks, kEmitThreads, 0, s>>>(b);
+        note_launch(), bin_pick_horizon_kernel<<<1, 1024, 0, s>>>(b, 1ull << 21);
+        note_launch(), bin_emit_kernel<true><<<blocks, kEmitThreads, 0, s>>>(b);
+        note_launch(), bin_emit_big_kernel<true><<<b.big_grid, kBigWarps * 32, 0, s>>>(b);
+        note_launch(), bin_tile_more_kernel<<<1, 1024, 0, s>>>(b);
+        return cudaGetLastError();
+    }
     note_launch(), bin_tile_dirs_kernel<<<(ntiles + tb - 1) / tb, tb, 0, s>>>(b, ntiles);
-    note_launch(), bin_emit_kernel<<<(b.n_pad + kEmitThreads - 1) / kEmitThreads, kEmitThreads, 0, s>>>(b);
-    note_launch(), bin_emit_big_kernel<<<b.big_grid, kBigWarps * 32, 0, s>>>(b);
+    note_launch(), bin_emit_kernel<false><<<blocks, kEmitThreads, 0, s>>>(b);
+    note_launch(), bin_emit_big_kernel<false><<<b.big_grid, kBigWarps * 32, 0, s>>>(b);
     return cudaGetLastError();
 }
 

@@ -86,6 +86,7 @@ __global__ void __launch_bounds__(128) colors_kernel(ColorLaunch c) {
     const int n_slots = c.perm ? ((n + 31) / 32) * 32 : n;
     if (j >= n_slots) return;
     if (j >= n) { c.rgba[j] = make_float4(0.f, 0.f, 0.f, 0.f); return; }
+    if (c.listed_code && (c.listed_rect[j].x == 0xffffffffu || c.listed_code[j] > c.listed_cut)) return;   // on no list of this view
     const int i = c.perm ? (int)c.perm[j] : j;
     const int K = c.sc.sh_coeffs, G = c.sc.num_lobes;
     float3 v = make_float3(c.sc.positions[3 * i] - c.eye[0], c.sc.positions[3 * i + 1] - c.eye[1],

@@ -85,6 +85,17 @@ struct TileLists {
     int tiles_x, tiles_y, ty_first;
 };
 
+// Horizon of a culled emission (binning.cu): picked on the device from a histogram of the Gaussians' nearest
+// distances, read by the emission kernels of the same stream and, afterwards, by the host.
+struct HorizonPick {
+    unsigned int cut;                   // last histogram bucket kept; kAllBuckets: every pair is kept
+    unsigned int chord_bits;            // largest chord of a tile (float bits), from bin_tile_dirs_kernel
+    unsigned long long est_kept;        // estimated pairs up to the cut (tile rectangles, an upper bound)
+    unsigned long long est_total;       // estimated pairs of the view
+    unsigned long long reserved;
+};
+constexpr unsigned int kAllBuckets = 0xffffffffu;
+
 struct BinLaunch {
     int n, n_pad;
     const float2 *bx, *by, *bz;            // level-0 boxes
@@ -104,6 +115,13 @@ struct BinLaunch {
     unsigned long long* total_dev;         // [4]; [0] = number of pairs met by the emission (may exceed pair_cap)
     int* big_slot; uint2* big_rect;        // [n_pad] Gaussians that cover many tiles, and their tile rectangles
     int big_grid;                          // CTAs that work the list off (a few per SM)
+    // culled emission (null / unused for a complete one): only the pairs that begin before a horizon are emitted
+    HorizonPick* pick;
+    unsigned long long* near_hist;         // [2048] estimated pairs by nearest distance of the Gaussian
+    uint2* g_rect; unsigned int* g_code;   // [n_pad] tile rectangle (x = ~0: none) and histogram bucket of every Gaussian
+    int* tile_diff;                        // [(tiles_x + 1) * (tiles_y + 1)] corners of the rectangles of culled Gaussians
+    int* tile_more;                        // [tiles] the tile has pairs that were not emitted
+    unsigned long long near_target;        // estimated pairs to keep
 };
 
 struct MarchLaunch {
@@ -149,6 +167,10 @@ struct ColorLaunch {
     float4* rgba;          // sorted order output (when perm != null)
     float* rgb_out;
     float sigma_threshold;
+    // lists that stop at a horizon (binning.cu): the Gaussians none of whose pairs were emitted keep whatever rgba holds
+    const uint2* listed_rect;
+    const unsigned int* listed_code;
+    unsigned int listed_cut;
 };
 
 struct FinalizeLaunch {

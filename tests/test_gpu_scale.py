@@ -319,6 +319,7 @@ def test_lists_up_to_a_horizon_change_nothing(big):
     gradients must be those of the complete lists -- also when the budget is so small that rays reach the horizon
     and the view has to be marched again with complete lists."""
     ro, r, sc, tens, cs = big
+    r.build(*tens[:4])                              # other tests of this module built their own scenes meanwhile
     save = march(ro, sc, cs, flags=_lib.FLAG_SAVE_HITS)
 
     def run(budget):
@@ -335,7 +336,7 @@ def test_lists_up_to_a_horizon_change_nothing(big):
     full_rgb, full_grads, st0 = run(0)
     assert st0["views"] == 0
     near_rgb, near_grads, st1 = run(6)
-    assert st1["views"] == 1 and st1["views_marched_again"] == 0 and st1["pairs_kept"] * 2 < st1["pairs_emitted"]
+    assert st1["views"] == 1 and st1["views_marched_again"] == 0 and st1["pairs_kept"] * 2 < st1["pairs_estimated"]
     assert torch.equal(near_rgb, full_rgb)
     again_rgb, again_grads, st2 = run(1)            # one pair per ray: far too shallow
     assert st2["views"] == 1 and st2["views_marched_again"] == 1
