@@ -30,6 +30,9 @@ struct rgx_ctx {
     float2 *bx = nullptr, *by = nullptr, *bz = nullptr;
     float4 *g0 = nullptr, *g1 = nullptr, *g2 = nullptr, *quat = nullptr, *sdens = nullptr, *rgba = nullptr;
     float4* grad_rows = nullptr;
+    bool grad_rows_clear = false;     // every row is zero (the gradient kernel clears what it reads); false after a failed backward
+    unsigned char* listed = nullptr; int listed_cap = 0;   // per sorted slot: on some list of the view whose colours rgba holds
+    unsigned long long listed_serial = 0;                  // the colour evaluation `listed` belongs to (0: none)
     int grad_copies = 1;     // sets of gradient rows the backward spreads its atomic additions over
     float* hk = nullptr;
     unsigned int* refit_counters = nullptr;
@@ -62,13 +65,11 @@ struct rgx_ctx {
     unsigned long long* bin_total_dev = nullptr;
     unsigned long long* bin_total_host = nullptr;      // pinned
     // two-depth lists of forward-only views (binning.cu, march_lists.cu HZ variant)
-    uint64_t* sel_keys = nullptr; uint32_t* sel_vals = nullptr; size_t sel_cap = 0;
-    unsigned int* hz_hist = nullptr; unsigned int* hz_hist_host = nullptr;       // 2048 buckets; host copy pinned
     int *tile_more = nullptr, *tile_resume = nullptr; int hz_tiles_cap = 0;
     float4* hz_state = nullptr; long long hz_state_cap = 0;
     unsigned long long* hz_scalars = nullptr; unsigned long long* hz_scalars_host = nullptr;   // [0] selected pairs, [1] stopped rays (low 32 bits)
     int hz_min_pairs_per_ray = 48, hz_budget_per_ray = 16;                        // when to use them, how deep the first phase goes
-    long long hz_last[4] = {0, 0, 0, 0};                                          // pairs emitted, sorted in phase 1, rays stopped, sorted in phase 2
+    long long hz_last[4] = {0, 0, 0, 0};                                          // pairs of the view (estimate), sorted in phase 1, rays stopped, sorted in phase 2
     // what the current lists were made for
     int last_pairs = 0;
     float binning_ms = 0.f; int binning_runs = 0;
@@ -175,9 +176,10 @@ void release_workspace(rgx_ctx* ctx) {
                      (void**)&ctx->bin_cub, (void**)&ctx->bin_total_dev, (void**)&ctx->tape, (void**)&ctx->tape_used,
                      (void**)&ctx->ray_head, (void**)&ctx->tile_dir, (void**)&ctx->tile_iota,
                      (void**)&ctx->tile_cnt_sorted, (void**)&ctx->tile_order, (void**)&ctx->big_slot,
-                     (void**)&ctx->big_rect, (void**)&ctx->tile_unrecorded, (void**)&ctx->sel_keys, (void**)&ctx->sel_vals,
-                     (void**)&ctx->hz_hist, (void**)&ctx->tile_more, (void**)&ctx->tile_resume, (void**)&ctx->hz_state,
-                     (void**)&ctx->hz_scalars, (void**)&ctx->tape_tile_order};
+                     (void**)&ctx->big_rect, (void**)&ctx->tile_unrecorded, (void**)&ctx->tile_more, (void**)&ctx->tile_resume,
+                     (void**)&ctx->hz_state, (void**)&ctx->hz_scalars, (void**)&ctx->tape_tile_order, (void**)&ctx->near_pick,
+                     (void**)&ctx->near_hist, (void**)&ctx->g_rect, (void**)&ctx->g_code, (void**)&ctx->tile_diff,
+                     (void**)&ctx->listed};
     for (void** p : ptrs) {
         if (*p) cudaFree(*p);
         *p = nullptr;
@@ -194,7 +196,9 @@ void release_workspace(rgx_ctx* ctx) {
     ctx->tape_order_cap = 0;
     ctx->lists_event_set = false;
     ctx->hint_set = false;
-    ctx->sel_cap = 0; ctx->hz_tiles_cap = 0; ctx->hz_state_cap = 0;
+    ctx->hz_tiles_cap = 0; ctx->hz_state_cap = 0;
+    ctx->g_rect_cap = 0; ctx->tile_diff_cap = 0; ctx->listed_cap = 0; ctx->listed_serial = 0;
+    ctx->grad_rows_clear = false;
     ctx->built = false;
     ctx->lists_valid = false;
     ctx->tape_valid = false;
@@ -248,6 +252,7 @@ int ensure_workspace(rgx_ctx* ctx, int n_pad, int boxes) {
         int copies = 4;
         while (copies > 1 && (size_t)copies * c * 64 > ((size_t)2 << 30)) copies >>= 1;
         if ((e = regrow(ctx, ctx->grad_rows, 4 * c * (size_t)copies)) != cudaSuccess) return cuda_fail(ctx, e, "workspace grad_rows");
+        ctx->grad_rows_clear = false;
         ctx->grad_copies = copies;
         ctx->cap_n_pad = (int)c;
         size_t cub = build_cub_temp_bytes((int)c);
@@ -318,8 +323,10 @@ void fill_sorted(const rgx_ctx* ctx, SortedGaussians& g) {
 // (the march, the replay of its recording and a search over the same lists meet no others).
 int run_colors(rgx_ctx* ctx, const rgx_scene* sc, const float eye[3], cudaStream_t s, bool listed_only = false) {
     ColorLaunch c{};
-    if (listed_only && ctx->lists_partial && ctx->g_code) {
+    const bool listed = listed_only && ctx->lists_partial && ctx->g_code && ctx->listed && ctx->listed_cap >= ctx->n_pad;
+    if (listed) {
         c.listed_rect = ctx->g_rect; c.listed_code = ctx->g_code; c.listed_cut = ctx->near_pick_host->cut;
+        c.listed_out = ctx->listed;
     }
     c.sc = *sc;
     std::memcpy(c.eye, eye, sizeof(c.eye));
@@ -327,6 +334,7 @@ int run_colors(rgx_ctx* ctx, const rgx_scene* sc, const float eye[3], cudaStream
     c.rgba = ctx->rgba;
     c.sigma_threshold = ctx->sigma_threshold;
     ctx->rgba_serial++;
+    ctx->listed_serial = listed ? ctx->rgba_serial : 0;
     cudaError_t e = launch_colors(c, s);
     return e == cudaSuccess ? RGX_OK : cuda_fail(ctx, e, "colour kernel");
 }
@@ -378,7 +386,7 @@ void rgx_destroy(rgx_ctx* ctx) {
     release_workspace(ctx);
     if (ctx->bin_total_host) cudaFreeHost(ctx->bin_total_host);
     if (ctx->tape_used_host) cudaFreeHost(ctx->tape_used_host);
-    if (ctx->hz_hist_host) cudaFreeHost(ctx->hz_hist_host);
+    if (ctx->near_pick_host) cudaFreeHost(ctx->near_pick_host);
     if (ctx->hz_scalars_host) cudaFreeHost(ctx->hz_scalars_host);
     if (ctx->side) cudaStreamDestroy(ctx->side);
     if (ctx->ev_main) cudaEventDestroy(ctx->ev_main);
@@ -476,9 +484,17 @@ static cudaError_t grow_pairs(rgx_ctx* ctx, size_t pairs) {
 
 // Emission of a view's (tile, Gaussian) pairs, unsorted, into ctx->bin_keys_in / bin_vals_in, in three steps so that
 // a caller can put other launches between the second and the third: workspace and launch parameters ...
-static int two_depth_workspace(rgx_ctx* ctx, int ntiles, bool selection = true);
+static int two_depth_workspace(rgx_ctx* ctx, int ntiles);
 
-static int emit_setup(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, BinLaunch& b, int& ntiles, bool near_only = false) {
+// How far an emission goes (binning.cu, culled emission): about budget_per_ray pairs per ray, unless the view has
+// fewer than min_total (estimated) pairs or the cut would keep all of them (half of them, with `half`).
+struct Cull {
+    int budget_per_ray;
+    unsigned long long min_total;
+    bool half;
+};
+
+static int emit_setup(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, BinLaunch& b, int& ntiles, const Cull* cull = nullptr) {
     cudaError_t e = cudaSuccess;
     const int tiles_x = (cam->width + kBinTile - 1) / kBinTile;
     if (tiles_x > 65535) return fail(ctx, RGX_E_TOO_LARGE, "image wider than 65535 tiles");
@@ -487,7 +503,7 @@ static int emit_setup(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, B
     ntiles = tiles_x * tiles_y;
     if (!ctx->bin_total_dev) {
         RGB_(bin_total_dev, 4);
-        if ((e = cudaMallocHost((void**)&ctx->bin_total_host, 4 * sizeof(unsigned long long))) != cudaSuccess)
+        if (!ctx->bin_total_host && (e = cudaMallocHost((void**)&ctx->bin_total_host, 4 * sizeof(unsigned long long))) != cudaSuccess)
             return cuda_fail(ctx, e, "pinned scalar");
         if (cudaDeviceGetAttribute(&ctx->sm_count, cudaDevAttrMultiProcessorCount, ctx->device) != cudaSuccess || ctx->sm_count <= 0)
             ctx->sm_count = 148;
@@ -517,18 +533,23 @@ static int emit_setup(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, B
     b.tiles_x = tiles_x; b.tiles_y = tiles_y; b.ty_first = ty_first;
     b.total_dev = ctx->bin_total_dev;
     b.big_slot = ctx->big_slot; b.big_rect = ctx->big_rect; b.big_grid = ctx->sm_count * 4;
-    if (near_only && ctx->near_budget_per_ray > 0) {
-        // the view of a recording forward: only the pairs that begin before a horizon are emitted (binning.cu)
-        int rc = two_depth_workspace(ctx, ntiles, false);   // tile_more, and the counter of rays that reach the horizon
+    if (cull && cull->budget_per_ray > 0) {
+        // only the pairs that begin before a horizon are emitted (binning.cu)
+        int rc = two_depth_workspace(ctx, ntiles);          // tile_more, and the counter of rays that reach the horizon
         if (rc) return rc;
         if (!ctx->near_pick) {
             RGB_(near_pick, 1); RGB_(near_hist, 2048);
-            if ((e = cudaMallocHost((void**)&ctx->near_pick_host, sizeof(HorizonPick))) != cudaSuccess)
+            if (!ctx->near_pick_host && (e = cudaMallocHost((void**)&ctx->near_pick_host, sizeof(HorizonPick))) != cudaSuccess)
                 return cuda_fail(ctx, e, "pinned horizon");
         }
         if (ctx->n_pad > ctx->g_rect_cap) {
             RGB_(g_rect, (size_t)ctx->n_pad); RGB_(g_code, (size_t)ctx->n_pad);
             ctx->g_rect_cap = ctx->n_pad;
+        }
+        if (ctx->n_pad > ctx->listed_cap) {
+            RGB_(listed, (size_t)ctx->n_pad);
+            ctx->listed_cap = ctx->n_pad;
+            ctx->listed_serial = 0;
         }
         const size_t diff = (size_t)(tiles_x + 1) * (size_t)(tiles_y + 1);
         if (diff > ctx->tile_diff_cap) {
@@ -538,7 +559,8 @@ static int emit_setup(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, B
         b.pick = ctx->near_pick; b.near_hist = ctx->near_hist; b.g_rect = ctx->g_rect; b.g_code = ctx->g_code;
         b.tile_diff = ctx->tile_diff; b.tile_more = ctx->tile_more;
         const double rays = (double)cam->width * (double)(m->row_end - m->row_begin);
-        b.near_target = (unsigned long long)((double)ctx->near_budget_per_ray * rays * ctx->near_ratio);
+        b.near_target = (unsigned long long)((double)cull->budget_per_ray * rays * ctx->near_ratio);
+        b.near_min_total = cull->min_total; b.near_half = cull->half ? 1 : 0;
     }
     return RGX_OK;
 }
@@ -573,8 +595,8 @@ static int emit_finish(rgx_ctx* ctx, BinLaunch& b, cudaStream_t s, int& total) {
 }
 
 static int emit_pairs(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, cudaStream_t s, BinLaunch& b, int& total,
-                      int& ntiles, bool near_only = false) {
-    int rc = emit_setup(ctx, cam, m, b, ntiles, near_only);
+                      int& ntiles, const Cull* cull = nullptr) {
+    int rc = emit_setup(ctx, cam, m, b, ntiles, cull);
     if (rc || (rc = emit_launch(ctx, b, s))) return rc;
     return emit_finish(ctx, b, s, total);
 }
@@ -618,17 +640,12 @@ static void lists_now_valid(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march
     ctx->last_pairs = total;
 }
 
-static int two_depth_workspace(rgx_ctx* ctx, int ntiles, bool selection) {
+static int two_depth_workspace(rgx_ctx* ctx, int ntiles) {
     cudaError_t e = cudaSuccess;
-    if (!ctx->hz_hist) {
-        RGB_(hz_hist, 2048); RGB_(hz_scalars, 4);
-        if ((e = cudaMallocHost((void**)&ctx->hz_hist_host, 2048 * sizeof(unsigned int))) != cudaSuccess ||
-            (e = cudaMallocHost((void**)&ctx->hz_scalars_host, 4 * sizeof(unsigned long long))) != cudaSuccess)
-            return cuda_fail(ctx, e, "pinned histogram");
-    }
-    if (selection && ctx->bin_pair_cap > ctx->sel_cap) {
-        RGB_(sel_keys, ctx->bin_pair_cap); RGB_(sel_vals, ctx->bin_pair_cap);
-        ctx->sel_cap = ctx->bin_pair_cap;
+    if (!ctx->hz_scalars) {
+        RGB_(hz_scalars, 4);
+        if (!ctx->hz_scalars_host && (e = cudaMallocHost((void**)&ctx->hz_scalars_host, 4 * sizeof(unsigned long long))) != cudaSuccess)
+            return cuda_fail(ctx, e, "pinned scalars");
     }
     if (ntiles > ctx->hz_tiles_cap) {
         RGB_(tile_more, (size_t)ntiles + 64); RGB_(tile_resume, (size_t)ntiles + 64);
@@ -636,6 +653,14 @@ static int two_depth_workspace(rgx_ctx* ctx, int ntiles, bool selection) {
     }
     return RGX_OK;
 }
+
+// What a culled emission teaches about the next one: the estimate counts every tile of a Gaussian's rectangle, and
+// what that is worth in pairs is learnt from view to view.
+static void learn_ratio(rgx_ctx* ctx, int kept) {
+    if (kept > 0) ctx->near_ratio = std::min(8.0, std::max(1.0, (double)ctx->near_pick_host->est_kept / (double)kept));
+}
+
+static Cull near_cull(const rgx_ctx* ctx) { return Cull{ctx->near_budget_per_ray, 1ull << 21, true}; }
 
 // Turns the emitted pairs into ctx->lists.  The view of a recording forward -- a training view, whose rays end long
 // before they have seen most of their tile's list (on the 3 M-Gaussian scene every ray ends within the nearest eighth
@@ -654,11 +679,7 @@ static int lists_from_pairs(rgx_ctx* ctx, BinLaunch& b, int total, int ntiles, c
         ctx->lists_horizon = bin_hist_bucket_end(b, (int)pk.cut);
         ctx->lists_rays = (long long)cam->width * (m->row_end - m->row_begin);
         ctx->near_stats[0] += 1; ctx->near_stats[1] += (long long)pk.est_total; ctx->near_stats[2] += total;
-        // the estimate counts every tile of a Gaussian's rectangle; what it is worth in pairs is learnt from view to view
-        if (total > 0) {
-            const double r = (double)pk.est_kept / (double)total;
-            ctx->near_ratio = std::min(8.0, std::max(1.0, r));
-        }
+        learn_ratio(ctx, total);
     }
     return RGX_OK;
 }
@@ -673,7 +694,8 @@ static int ensure_lists(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m,
     ScopedTimer timer(ctx, s, 2);
     BinLaunch b;
     int total = 0, ntiles = 0;
-    int rc = emit_pairs(ctx, cam, m, s, b, total, ntiles, near_only);
+    const Cull cull = near_cull(ctx);
+    int rc = emit_pairs(ctx, cam, m, s, b, total, ntiles, near_only ? &cull : nullptr);
     if (rc) return rc;
     return lists_from_pairs(ctx, b, total, ntiles, cam, m, s);
 }
@@ -715,7 +737,8 @@ static void lists_ahead_begin(rgx_ctx* ctx, cudaStream_t s, ListsAhead& a) {
     if (cudaEventRecord(ctx->ev_main, s) != cudaSuccess || cudaStreamWaitEvent(ctx->side, ctx->ev_main, 0) != cudaSuccess) return;
     ctx->lists_valid = false;                      // from here on the list arrays belong to the announced view
     const bool near_only = (m->flags & RGX_FLAG_SAVE_HITS) && !(m->flags & RGX_FLAG_COUNT_WORK);
-    if (emit_setup(ctx, cam, m, a.b, a.ntiles, near_only) || emit_launch(ctx, a.b, ctx->side)) {
+    const Cull cull = near_cull(ctx);
+    if (emit_setup(ctx, cam, m, a.b, a.ntiles, near_only ? &cull : nullptr) || emit_launch(ctx, a.b, ctx->side)) {
         cudaEventRecord(ctx->ev_lists, ctx->side);
         ctx->lists_event_set = true;
         return;
@@ -746,53 +769,32 @@ static int forward_two_depth(rgx_ctx* ctx, const rgx_camera* cam, const rgx_marc
     ctx->lists_valid = false;
     BinLaunch b;
     int total = 0, ntiles = 0, rc;
-    {
-        ScopedTimer timer(ctx, s, 2);
-        if ((rc = emit_pairs(ctx, cam, m, s, b, total, ntiles))) return rc;
-    }
     const long long rays = (long long)cam->width * (m->row_end - m->row_begin);
-    auto plain = [&]() -> int {
-        ScopedTimer timer(ctx, s, 2);
-        int r2 = fill_lists(ctx, b, ctx->bin_keys_in, ctx->bin_vals_in, total, ntiles, s);
-        if (r2 == RGX_OK) lists_now_valid(ctx, cam, m, total);
-        return r2;
-    };
-    if ((long long)total < (long long)ctx->hz_min_pairs_per_ray * rays || total == 0) return plain();
-    // workspace of the two-depth path
-    if ((rc = two_depth_workspace(ctx, ntiles))) return rc;
     const long long all_rays = (long long)cam->width * cam->height;
     if (2 * all_rays > ctx->hz_state_cap) {
         RGB_(hz_state, (size_t)(2 * all_rays));
         ctx->hz_state_cap = 2 * all_rays;
     }
-    // where the pairs begin: the first phase takes the nearest ones, about hz_budget_per_ray per ray
-    if ((e = cudaMemsetAsync(ctx->hz_hist, 0, 2048 * sizeof(unsigned int), s)) != cudaSuccess ||
-        (e = cudaMemsetAsync(ctx->tile_more, 0, sizeof(int) * (size_t)ntiles, s)) != cudaSuccess ||
-        (e = cudaMemsetAsync(ctx->tile_resume, 0, sizeof(int) * (size_t)ntiles, s)) != cudaSuccess ||
-        (e = cudaMemsetAsync(ctx->hz_scalars, 0, 4 * sizeof(unsigned long long), s)) != cudaSuccess ||
-        (e = launch_bin_hist(b, total, ctx->hz_hist, s)) != cudaSuccess ||
-        (e = cudaMemcpyAsync(ctx->hz_hist_host, ctx->hz_hist, 2048 * sizeof(unsigned int), cudaMemcpyDeviceToHost, s)) != cudaSuccess ||
-        (e = cudaStreamSynchronize(s)) != cudaSuccess)
-        return cuda_fail(ctx, e, "near-distance histogram");
-    const long long budget = (long long)ctx->hz_budget_per_ray * rays;
-    long long cum = 0;
-    int cut = -1;
-    for (int i = 0; i < 2048; ++i) {
-        if (ctx->hz_hist_host[i] == 0) continue;
-        if (cut >= 0 && cum + ctx->hz_hist_host[i] > budget) break;
-        cum += ctx->hz_hist_host[i];
-        cut = i;
+    // first depth: the pairs that begin nearest to the eye, about hz_budget_per_ray per ray -- or all of them, if the
+    // view has fewer than hz_min_pairs_per_ray per ray or the budget covers them
+    const Cull cull{ctx->hz_budget_per_ray > 0 ? ctx->hz_budget_per_ray : 1,
+                    (unsigned long long)((long long)ctx->hz_min_pairs_per_ray * rays), false};
+    {
+        ScopedTimer timer(ctx, s, 2);
+        if ((rc = emit_pairs(ctx, cam, m, s, b, total, ntiles, &cull))) return rc;
+        if ((rc = fill_lists(ctx, b, ctx->bin_keys_in, ctx->bin_vals_in, total, ntiles, s))) return rc;
     }
-    if (cut < 0 || cum >= total) return plain();               // everything begins within the budget: one depth is enough
-    const float horizon = bin_hist_bucket_end(b, cut);
-    const int count1 = (int)cum;
-    if ((e = launch_bin_select(b, total, 0, (unsigned int)cut, nullptr, ctx->sel_keys, ctx->sel_vals, ctx->hz_scalars, ctx->tile_more, s)) != cudaSuccess)
-        return cuda_fail(ctx, e, "pair selection");
-    uint64_t* all_keys = ctx->bin_keys_in;
-    uint32_t* all_vals = ctx->bin_vals_in;
-    if ((rc = fill_lists(ctx, b, ctx->sel_keys, ctx->sel_vals, count1, ntiles, s))) return rc;
+    const HorizonPick pk = *ctx->near_pick_host;
+    if (pk.cut == kAllBuckets || total == 0) {                     // one depth is enough: these are the complete lists
+        lists_now_valid(ctx, cam, m, total);
+        return RGX_OK;
+    }
+    learn_ratio(ctx, total);
+    if ((e = cudaMemsetAsync(ctx->tile_resume, 0, sizeof(int) * (size_t)ntiles, s)) != cudaSuccess ||
+        (e = cudaMemsetAsync(ctx->hz_scalars, 0, 4 * sizeof(unsigned long long), s)) != cudaSuccess)
+        return cuda_fail(ctx, e, "two-depth workspace");
     L.lists = ctx->lists;
-    L.hz_phase = 1; L.horizon = horizon; L.hz_state = ctx->hz_state; L.tile_more = ctx->tile_more;
+    L.hz_phase = 1; L.horizon = bin_hist_bucket_end(b, (int)pk.cut); L.hz_state = ctx->hz_state; L.tile_more = ctx->tile_more;
     L.tile_resume = ctx->tile_resume; L.hz_count = reinterpret_cast<unsigned int*>(ctx->hz_scalars + 1);
     {
         ScopedTimer timer(ctx, s, 0);
@@ -803,17 +805,16 @@ static int forward_two_depth(rgx_ctx* ctx, const rgx_camera* cam, const rgx_marc
         (e = cudaStreamSynchronize(s)) != cudaSuccess)
         return cuda_fail(ctx, e, "first depth read-back");
     const long long stopped = (long long)(ctx->hz_scalars_host[1] & 0xffffffffull);
-    long long count2 = 0;
+    int total2 = 0;
     if (stopped > 0) {
-        // the complete lists of the tiles in which a ray stopped
-        b.keys_in = all_keys; b.vals_in = all_vals;
-        if ((e = cudaMemsetAsync(ctx->hz_scalars, 0, sizeof(unsigned long long), s)) != cudaSuccess ||
-            (e = launch_bin_select(b, total, 1, 0u, ctx->tile_resume, ctx->sel_keys, ctx->sel_vals, ctx->hz_scalars, nullptr, s)) != cudaSuccess ||
-            (e = cudaMemcpyAsync(ctx->hz_scalars_host, ctx->hz_scalars, sizeof(unsigned long long), cudaMemcpyDeviceToHost, s)) != cudaSuccess ||
-            (e = cudaStreamSynchronize(s)) != cudaSuccess)
-            return cuda_fail(ctx, e, "second depth selection");
-        count2 = (long long)ctx->hz_scalars_host[0];
-        if ((rc = fill_lists(ctx, b, ctx->sel_keys, ctx->sel_vals, (int)count2, ntiles, s))) return rc;
+        // second depth: all pairs of the tiles in which a ray stopped
+        {
+            ScopedTimer timer(ctx, s, 2);
+            b.pick = nullptr;
+            b.tile_flag = ctx->tile_resume;
+            if ((rc = emit_launch(ctx, b, s)) || (rc = emit_finish(ctx, b, s, total2))) return rc;
+            if ((rc = fill_lists(ctx, b, ctx->bin_keys_in, ctx->bin_vals_in, total2, ntiles, s))) return rc;
+        }
         L.lists = ctx->lists;
         L.hz_phase = 2;
         {
@@ -822,7 +823,7 @@ static int forward_two_depth(rgx_ctx* ctx, const rgx_camera* cam, const rgx_marc
         }
         if (e != cudaSuccess) return cuda_fail(ctx, e, "forward march, second depth");
     }
-    ctx->hz_last[0] = total; ctx->hz_last[1] = count1; ctx->hz_last[2] = stopped; ctx->hz_last[3] = count2;
+    ctx->hz_last[0] = (long long)pk.est_total; ctx->hz_last[1] = total; ctx->hz_last[2] = stopped; ctx->hz_last[3] = total2;
     ctx->last_pairs = total;
     handled = true;
     return RGX_OK;
@@ -1021,8 +1022,14 @@ int rgx_backward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, co
                               ctx->tape_march.transmittance_eps == march->transmittance_eps;
     const bool replays = tape_matches && !(march->flags & (RGX_FLAG_BRUTE_FORCE | RGX_FLAG_PER_RAY_SEARCH));
     if (!(replays && ctx->rgba_serial == ctx->tape_rgba_serial) && (rc = run_colors(ctx, scene, cam->eye, s))) return rc;
-    cudaError_t e = cudaMemsetAsync(ctx->grad_rows, 0, sizeof(float4) * 4 * (size_t)ctx->n_pad * (size_t)ctx->grad_copies, s);
-    if (e != cudaSuccess) return cuda_fail(ctx, e, "backward memset");
+    // the gradient kernel of the previous backward left the rows cleared; the first backward, and one after a failure, clears them
+    cudaError_t e = cudaSuccess;
+    if (!ctx->grad_rows_clear &&
+        (e = cudaMemsetAsync(ctx->grad_rows, 0, sizeof(float4) * 4 * (size_t)ctx->cap_n_pad * (size_t)ctx->grad_copies, s)) != cudaSuccess)   // all of it: a later build may lay the rows out differently
+        return cuda_fail(ctx, e, "backward memset");
+    ctx->grad_rows_clear = false;
+    // the rays of a view whose lists stop at a horizon met listed Gaussians only (whichever lists this backward searches)
+    const bool rows_listed = ctx->listed_serial != 0 && ctx->listed_serial == ctx->rgba_serial;
     if (!(march->flags & (RGX_FLAG_BRUTE_FORCE | RGX_FLAG_PER_RAY_SEARCH))) {
         // lists that stop at a horizon serve the backward of the view whose forward they were checked by (its rays
         // are known to end before the horizon); any other backward gets complete lists
@@ -1057,9 +1064,11 @@ int rgx_backward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, co
     std::memcpy(f.eye, cam->eye, sizeof(f.eye));
     f.perm = ctx->vals_out;
     f.grad_rows = ctx->grad_rows; f.grad_copies = ctx->grad_copies; f.n_pad = ctx->n_pad;
+    f.listed = rows_listed ? ctx->listed : nullptr;
     f.quat = ctx->quat; f.sdens = ctx->sdens; f.hk = ctx->hk;
     f.flags = march->flags;
     e = launch_finalize(f, s);
+    ctx->grad_rows_clear = e == cudaSuccess;
     lists_ahead_end(ctx, ahead);
     return e == cudaSuccess ? RGX_OK : cuda_fail(ctx, e, "gradient finalise");
 }

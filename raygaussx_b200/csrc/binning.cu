@@ -379,11 +379,13 @@ __device__ __forceinline__ unsigned hist_bucket(float tn, const KeyLayout& kl) {
     return near_quantised(tn, kl) >> (kl.near_bits - kHistBits);
 }
 
-// ---------------------------------------------------------------- culled emission (views of recording forwards)
+// ---------------------------------------------------------------- culled emission
 //
-// A training view's rays end long before they have seen most of their tile's list, so its lists need only
-// hold the pairs that begin before a horizon (about near_target of them), and the pairs beyond need not even be
-// emitted.  The horizon is picked before the emission, on the device, from what is cheap to know of a Gaussian:
+// Rays that end early -- those of a training view, of a dense scene -- look at the beginning of their tile's list
+// only.  Such a view's lists need only hold the pairs that begin before a horizon (about near_target of them), and
+// the pairs beyond need not even be emitted.  A recording forward counts the rays that reach the horizon after all
+// and, if there are any, starts over with complete lists; a forward that records nothing puts those rays aside and
+// takes them up again with the complete lists of their tiles (b.tile_flag) -- lists in two depths (march_lists.cu).  The horizon is picked before the emission, on the device, from what is cheap to know of a Gaussian:
 // the rectangle of tiles it can touch (an upper bound of its pairs) and a lower bound of the distance at which any
 // of its pairs begins.  bin_near_hist_kernel: those two per Gaussian, and their histogram; bin_pick_horizon_kernel:
 // the bucket at which the running sum reaches the target; the emission kernels then skip Gaussians and pairs that
@@ -429,9 +431,9 @@ __global__ void __launch_bounds__(kEmitThreads) bin_near_hist_kernel(BinLaunch b
 }
 
 // The cut: the last non-empty bucket up to which the estimated pairs stay within the target (the first non-empty
-// one if none does).  Everything is kept (cut = kAllBuckets) when the view has fewer than min_total estimated
-// pairs or the cut would keep half of them or more.
-__global__ void __launch_bounds__(1024) bin_pick_horizon_kernel(BinLaunch b, unsigned long long min_total) {
+// one if none does).  Everything is kept (cut = kAllBuckets) when the view has fewer than near_min_total estimated
+// pairs or the cut would keep all of them (half of them or more, with near_half).
+__global__ void __launch_bounds__(1024) bin_pick_horizon_kernel(BinLaunch b) {
     using Scan = cub::BlockScan<unsigned long long, 1024>;
     __shared__ typename Scan::TempStorage scan_tmp;
     __shared__ int s_cut, s_first;
@@ -450,7 +452,8 @@ __global__ void __launch_bounds__(1024) bin_pick_horizon_kernel(BinLaunch b, uns
     if (cut >= (1 << kHistBits)) { if (t == 0) { b.pick->cut = kAllBuckets; b.pick->est_kept = total; } return; }
     if (t == (cut >> 1)) {
         const unsigned long long kept = (cut & 1) ? p1 : p0;
-        const bool partial = total >= min_total && kept * 2 < total && cut + 1 < (1 << kHistBits);
+        const bool partial = total >= b.near_min_total && (b.near_half ? kept * 2 < total : kept < total) &&
+                             cut + 1 < (1 << kHistBits);
         b.pick->cut = partial ? (unsigned)cut : kAllBuckets;
         b.pick->est_kept = partial ? kept : total;
     }
@@ -557,8 +560,8 @@ __global__ void __launch_bounds__(kEmitThreads) bin_emit_kernel(BinLaunch b) {
             const unsigned tx0 = rect.x & 0xffffu, tx1 = rect.x >> 16, ty0 = rect.y & 0xffffu;
             const unsigned w = tx1 - tx0 + 1, local = (unsigned)(item - sh.prefix[lo]);
             const unsigned t = (ty0 + local / w) * (unsigned)b.tiles_x + tx0 + local % w;
-            float tn;
-            keep = pair_range(b.cam.eye, b.tile_dir[t], sh.geom[lo], tn, tf);
+            float tn = 0.f;
+            keep = (!b.tile_flag || b.tile_flag[t] != 0) && pair_range(b.cam.eye, b.tile_dir[t], sh.geom[lo], tn, tf);
             if (CULL && keep && hist_bucket(tn, kl) > cut) { keep = false; b.tile_more[t] = 1; }
             if (keep) key = pair_key(kl, t, tn, (unsigned)(blockIdx.x * kEmitThreads + lo));
         }
@@ -622,8 +625,8 @@ __global__ void __launch_bounds__(kBigWarps * 32) bin_emit_big_kernel(BinLaunch 
             float tf = 0.f;
             if (item < count) {
                 const unsigned t = (ty0 + item / w) * (unsigned)b.tiles_x + tx0 + item % w;
-                float tn;
-                keep = pair_range(b.cam.eye, b.tile_dir[t], g, tn, tf);
+                float tn = 0.f;
+                keep = (!b.tile_flag || b.tile_flag[t] != 0) && pair_range(b.cam.eye, b.tile_dir[t], g, tn, tf);
                 if (CULL && keep && hist_bucket(tn, kl) > cut) { keep = false; b.tile_more[t] = 1; }
                 if (keep) key = pair_key(kl, t, tn, (unsigned)j);
             }
@@ -686,72 +689,6 @@ __global__ void __launch_bounds__(256) bin_blocks_kernel(BinLaunch b, size_t n_b
     if (lane == 0) b.blk[blk] = make_float2(lo, hi);
 }
 
-// ---------------------------------------------------------------- lists in two depths (forward-only views whose rays end early)
-//
-// A dense view can have hundreds of (tile, Gaussian) pairs per ray of which the rays, ending after a slab
-// or two, look at a few.  For such a view the pairs are not sorted all at once: a histogram of their near
-// distances picks a depth, only the pairs that begin before it are sorted and marched, and the rest is
-// sorted only for the tiles in which some ray got that far (march_lists.cu, horizon variant).
-
-__global__ void __launch_bounds__(256) bin_hist_kernel(const uint64_t* __restrict__ keys, int total, int shift,
-                                                       unsigned int* hist) {
-    __shared__ unsigned int local[1 << kHistBits];
-    for (int i = threadIdx.x; i < (1 << kHistBits); i += blockDim.x) local[i] = 0u;
-    __syncthreads();
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
-        atomicAdd(&local[(unsigned)(keys[i] >> shift) & ((1u << kHistBits) - 1u)], 1u);
-    __syncthreads();
-    for (int i = threadIdx.x; i < (1 << kHistBits); i += blockDim.x)
-        if (local[i]) atomicAdd(&hist[i], local[i]);
-}
-
-// MODE 0: keeps the pairs whose near distance lies in histogram bucket <= cut, and marks the tiles that have
-// pairs beyond.  MODE 1: keeps the pairs of the tiles flagged in tile_flag.  Output order is arbitrary (the
-// keys are unique and get sorted).  One atomic per block.
-template <int MODE>
-__global__ void __launch_bounds__(256) bin_select_kernel(const uint64_t* __restrict__ keys, const uint32_t* __restrict__ vals,
-                                                         int total, KeyLayout kl, unsigned int cut, const int* __restrict__ tile_flag,
-                                                         uint64_t* out_k, uint32_t* out_v, unsigned long long* counter,
-                                                         int* tile_more) {
-    constexpr int kPer = 8;
-    using Scan = cub::BlockScan<int, 256>;
-    __shared__ typename Scan::TempStorage scan_tmp;
-    __shared__ unsigned long long base_s;
-    const long long blk0 = (long long)blockIdx.x * 256 * kPer;
-    uint64_t k[kPer];
-    unsigned keep = 0u;
-    int mine = 0;
-#pragma unroll
-    for (int i = 0; i < kPer; ++i) {
-        const long long idx = blk0 + (long long)i * 256 + threadIdx.x;
-        k[i] = 0;
-        if (idx < total) {
-            k[i] = keys[idx];
-            const int t = (int)(k[i] >> (kl.near_bits + kl.id_bits));
-            bool kp;
-            if (MODE == 0) {
-                kp = ((unsigned)(k[i] >> (kl.id_bits + kl.near_bits - kHistBits)) & ((1u << kHistBits) - 1u)) <= cut;
-                if (!kp) tile_more[t] = 1;
-            } else {
-                kp = tile_flag[t] != 0;
-            }
-            if (kp) { keep |= 1u << i; ++mine; }
-        }
-    }
-    int offset, block_total;
-    Scan(scan_tmp).ExclusiveSum(mine, offset, block_total);
-    if (threadIdx.x == 0) base_s = block_total ? atomicAdd(counter, (unsigned long long)block_total) : 0ull;
-    __syncthreads();
-    unsigned long long at = base_s + (unsigned long long)offset;
-#pragma unroll
-    for (int i = 0; i < kPer; ++i)
-        if (keep & (1u << i)) {
-            out_k[at] = k[i];
-            out_v[at] = vals[blk0 + (long long)i * 256 + threadIdx.x];
-            ++at;
-        }
-}
-
 }  // namespace
 
 size_t binning_cub_temp_bytes(size_t pair_cap, int ntiles) {
@@ -787,7 +724,7 @@ cudaError_t launch_bin_emit(const BinLaunch& b, cudaStream_t s) {
             return e;
         note_launch(), bin_tile_dirs_kernel<<<(ntiles + tb - 1) / tb, tb, 0, s>>>(b, ntiles);
         note_launch(), bin_near_hist_kernel<<<blocks, kEmitThreads, 0, s>>>(b);
-        note_launch(), bin_pick_horizon_kernel<<<1, 1024, 0, s>>>(b, 1ull << 21);
+        note_launch(), bin_pick_horizon_kernel<<<1, 1024, 0, s>>>(b);
         note_launch(), bin_emit_kernel<true><<<blocks, kEmitThreads, 0, s>>>(b);
         note_launch(), bin_emit_big_kernel<true><<<b.big_grid, kBigWarps * 32, 0, s>>>(b);
         note_launch(), bin_tile_more_kernel<<<1, 1024, 0, s>>>(b);
@@ -831,31 +768,12 @@ cudaError_t launch_bin_fill(const BinLaunch& b, int total, cudaStream_t s) {
     return cudaGetLastError();
 }
 
-// Histogram of the pairs' near distances (2^11 buckets, see bin_hist_kernel), added into hist.
-cudaError_t launch_bin_hist(const BinLaunch& b, int total, unsigned int* hist, cudaStream_t s) {
-    const KeyLayout kl = key_layout(b.tiles_x * ((b.cam.height + b.tile - 1) / b.tile), b.n_pad);
-    if (kl.near_bits < kHistBits) return cudaErrorInvalidValue;
-    if (total > 0) note_launch(), bin_hist_kernel<<<592, 256, 0, s>>>(b.keys_in, total, kl.id_bits + kl.near_bits - kHistBits, hist);
-    return cudaGetLastError();
-}
-
 // Upper end of histogram bucket `bucket` as a distance: every pair in buckets <= bucket begins before it.
 float bin_hist_bucket_end(const BinLaunch& b, int bucket) {
     const KeyLayout kl = key_layout(b.tiles_x * ((b.cam.height + b.tile - 1) / b.tile), b.n_pad);
     // bucket = the leading kHistBits bits of the quantised distance; the next bucket's smallest code bounds this one
     if (bucket + 1 >= (1 << kHistBits)) return INFINITY;
     return near_stored((unsigned)(bucket + 1) << (kl.near_bits - kHistBits), kl);
-}
-
-// Selection of pairs into (out_k, out_v); counter (zeroed by the caller) receives their number.
-cudaError_t launch_bin_select(const BinLaunch& b, int total, int mode, unsigned int cut, const int* tile_flag, uint64_t* out_k,
-                              uint32_t* out_v, unsigned long long* counter, int* tile_more, cudaStream_t s) {
-    const KeyLayout kl = key_layout(b.tiles_x * ((b.cam.height + b.tile - 1) / b.tile), b.n_pad);
-    if (total <= 0) return cudaSuccess;
-    const int blocks = (int)(((long long)total + 2047) / 2048);
-    if (mode == 0) note_launch(), bin_select_kernel<0><<<blocks, 256, 0, s>>>(b.keys_in, b.vals_in, total, kl, cut, tile_flag, out_k, out_v, counter, tile_more);
-    else note_launch(), bin_select_kernel<1><<<blocks, 256, 0, s>>>(b.keys_in, b.vals_in, total, kl, cut, tile_flag, out_k, out_v, counter, tile_more);
-    return cudaGetLastError();
 }
 
 }  // namespace rgx

@@ -85,8 +85,16 @@ __global__ void __launch_bounds__(128) colors_kernel(ColorLaunch c) {
     const int n = c.sc.n;
     const int n_slots = c.perm ? ((n + 31) / 32) * 32 : n;
     if (j >= n_slots) return;
-    if (j >= n) { c.rgba[j] = make_float4(0.f, 0.f, 0.f, 0.f); return; }
-    if (c.listed_code && (c.listed_rect[j].x == 0xffffffffu || c.listed_code[j] > c.listed_cut)) return;   // on no list of this view
+    if (j >= n) {
+        c.rgba[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c.listed_code) c.listed_out[j] = 0;
+        return;
+    }
+    if (c.listed_code) {
+        const bool listed = !(c.listed_rect[j].x == 0xffffffffu || c.listed_code[j] > c.listed_cut);
+        c.listed_out[j] = listed ? 1 : 0;
+        if (!listed) return;                   // on no list of this view
+    }
     const int i = c.perm ? (int)c.perm[j] : j;
     const int K = c.sc.sh_coeffs, G = c.sc.num_lobes;
     float3 v = make_float3(c.sc.positions[3 * i] - c.eye[0], c.sc.positions[3 * i + 1] - c.eye[1],
@@ -128,19 +136,25 @@ __global__ void __launch_bounds__(128) finalize_kernel(FinalizeLaunch f) {
     int j = blockIdx.x * blockDim.x + threadIdx.x;
     const int n = f.sc.n;
     if (j >= n) return;
+    if (f.listed && !f.listed[j]) return;              // on no list of the view: no ray met it, its rows are clear
     const int i = (int)f.perm[j];
     const int K = f.sc.sh_coeffs, G = f.sc.num_lobes;
     const bool acc = (f.flags & RGX_FLAG_ACCUMULATE) != 0;
     const bool exact = (f.flags & RGX_FLAG_EXACT_SH_GRAD) != 0;
-    float4 r0 = f.grad_rows[4 * (size_t)j], r1 = f.grad_rows[4 * (size_t)j + 1],
-           r2 = f.grad_rows[4 * (size_t)j + 2], r3 = f.grad_rows[4 * (size_t)j + 3];
-    for (int c = 1; c < f.grad_copies; ++c) {          // the march spreads its additions over several sets of rows
-        const float4* row = f.grad_rows + 4 * ((size_t)c * (size_t)f.n_pad + (size_t)j);
+    float4 r0 = make_float4(0.f, 0.f, 0.f, 0.f), r1 = r0, r2 = r0, r3 = r0;
+    for (int c = 0; c < f.grad_copies; ++c) {          // the march spreads its additions over several sets of rows
+        float4* row = f.grad_rows + 4 * ((size_t)c * (size_t)f.n_pad + (size_t)j);
         const float4 a0 = row[0], a1 = row[1], a2 = row[2], a3 = row[3];
         r0.x += a0.x; r0.y += a0.y; r0.z += a0.z; r0.w += a0.w;
         r1.x += a1.x; r1.y += a1.y; r1.z += a1.z; r1.w += a1.w;
         r2.x += a2.x; r2.y += a2.y; r2.z += a2.z; r2.w += a2.w;
         r3.x += a3.x;
+        // rows that received something are cleared again: every backward finds all rows clear
+        const unsigned any = __float_as_uint(a0.x) | __float_as_uint(a0.y) | __float_as_uint(a0.z) | __float_as_uint(a0.w) |
+                             __float_as_uint(a1.x) | __float_as_uint(a1.y) | __float_as_uint(a1.z) | __float_as_uint(a1.w) |
+                             __float_as_uint(a2.x) | __float_as_uint(a2.y) | __float_as_uint(a2.z) | __float_as_uint(a2.w) |
+                             __float_as_uint(a3.x) | __float_as_uint(a3.y) | __float_as_uint(a3.z) | __float_as_uint(a3.w);
+        if (any) row[0] = row[1] = row[2] = row[3] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     // A Gaussian no ray met (most of a large scene, in any one view) has nothing to add: the gradient tensors were
     // cleared by the launcher unless they accumulate, and are written for the others only.

@@ -216,7 +216,8 @@ __device__ __forceinline__ bool ray_pixel(const MarchLaunch& L, int tile_x, int 
 // L.hz_phase == 3 is the first phase without a second one, for recording forwards (training views, whose rays
 // are expected to end before the horizon): a ray that would need more is only counted, and the caller, if the
 // count is not zero, makes the complete lists and marches the whole view again.
-template <bool COUNT, bool SAVE, bool HZ = false>
+// HZ = 1: the two phases (L.hz_phase 1 or 2); HZ = 2: counting only (L.hz_phase 3), nothing is put aside.
+template <bool COUNT, bool SAVE, int HZ = 0>
 __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 4) march_forward_lists_kernel(const __grid_constant__ MarchLaunch L) {
     __shared__ ListShared sh;
     __shared__ TapeState tape_state[SAVE ? kWarps : 1];
@@ -226,7 +227,9 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 4) march_forward_lists_k
     int* pend = sh.pend[warp];
     const int unit = blockIdx.x / kTileSplit, part = blockIdx.x % kTileSplit;
     const int tile = L.lists.tile_order ? __ldg(&L.lists.tile_order[unit]) : unit;   // longest lists first
-    if (HZ && L.hz_phase == 2 && !L.tile_resume[tile]) return;      // no ray of this tile stopped at the horizon
+    if (HZ == 1 && L.hz_phase == 2 && !L.tile_resume[tile]) return;      // no ray of this tile stopped at the horizon
+    // the tile has pairs beyond the horizon that its lists do not hold
+    const bool hz_more = HZ != 0 && (HZ == 2 || L.hz_phase == 1) && L.tile_more[tile] != 0;
     const int tile_x = tile % L.lists.tiles_x, tile_y = tile / L.lists.tiles_x;
     const float eps = L.m.transmittance_eps;
     const float bg = L.m.white_background ? 1.0f : 0.0f;
@@ -267,10 +270,9 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 4) march_forward_lists_k
         // two-depth variant: 0 = march from the start, 1 = resume at a slab, 2 = resume at the first query,
         // 3 = resume at a query after an empty slab; what was put aside is (tbuffer, T, tenter, mode) + colour
         int hz_mode = 0;
-        bool hz_more = false, hz_susp = false;
+        bool hz_susp = false;
         float4 hz_a = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (HZ) {
-            hz_more = (L.hz_phase == 1 || L.hz_phase == 3) && L.tile_more[tile] != 0;
+        if (HZ == 1) {
             if (L.hz_phase == 2) {
                 hz_a = L.hz_state[2 * (size_t)ray_id];
                 hz_mode = (int)hz_a.w;
@@ -282,13 +284,13 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 4) march_forward_lists_k
             }
         }
         float first;
-        if (HZ && (hz_mode == 1 || hz_mode == 3)) first = hz_a.z;                  // the first hit is known
+        if (HZ == 1 && (hz_mode == 1 || hz_mode == 3)) first = hz_a.z;                  // the first hit is known
         else first = closest_in_tile<COUNT>(L, r, tenter, texit, tv, cursor, pend, lane, tl);
         if (COUNT) tl.v[C_CYC_SEEK] += clock64() - c_ray;
         if (HZ && hz_more && !(first < L.horizon)) {                             // nothing before the horizon: ask again later
             hz_susp = true;
             if (lane == 0) {
-                if (L.hz_phase == 1) {
+                if (HZ == 1 && L.hz_phase == 1) {
                     L.hz_state[2 * (size_t)ray_id] = make_float4(tenter, 1.0f, tenter, 2.0f);
                     L.tile_resume[tile] = 1;
                 }
@@ -298,8 +300,8 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 4) march_forward_lists_k
             tenter = first;
             float tbuffer = tenter;
             int slab_index = 0;
-            if (HZ && hz_mode == 1) tbuffer = hz_a.x;
-            if (HZ && hz_mode == 3) {                                             // the query after an empty slab, again
+            if (HZ == 1 && hz_mode == 1) tbuffer = hz_a.x;
+            if (HZ == 1 && hz_mode == 3) {                                             // the query after an empty slab, again
                 const float nxt = closest_in_tile<COUNT>(L, r, hz_a.x, texit, tv, cursor, pend, lane, tl);
                 tbuffer = nxt < INFINITY ? nxt : texit;                           // nothing further: the loop below does not start
             }
@@ -308,7 +310,7 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 4) march_forward_lists_k
                 if (HZ && hz_more && !(p.tmax < L.horizon)) {                        // this slab needs pairs from beyond
                     hz_susp = true;
                     if (lane == 0) {
-                        if (L.hz_phase == 1) {
+                        if (HZ == 1 && L.hz_phase == 1) {
                             L.hz_state[2 * (size_t)ray_id] = make_float4(tbuffer, T, tenter, 1.0f);
                             L.hz_state[2 * (size_t)ray_id + 1] = sh.color[warp];
                             L.tile_resume[tile] = 1;
@@ -372,7 +374,7 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 4) march_forward_lists_k
                     if (HZ && hz_more && !(nxt < L.horizon)) {                   // the next hit, if any, is beyond the horizon
                         hz_susp = true;
                         if (lane == 0) {
-                            if (L.hz_phase == 1) {
+                            if (HZ == 1 && L.hz_phase == 1) {
                                 L.hz_state[2 * (size_t)ray_id] = make_float4(tbuffer, T, tenter, 3.0f);
                                 L.hz_state[2 * (size_t)ray_id + 1] = sh.color[warp];
                                 L.tile_resume[tile] = 1;
@@ -396,7 +398,7 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 4) march_forward_lists_k
             const float4 acc = sh.color[warp];
             const RayColor st = {T, acc.x, acc.y, acc.z, acc.w};
             write_ray(L, ray_id, st, bg);
-            if (HZ && L.hz_phase == 1) L.hz_state[2 * (size_t)ray_id] = make_float4(0.f, 0.f, 0.f, 0.f);   // done
+            if (HZ == 1 && L.hz_phase == 1) L.hz_state[2 * (size_t)ray_id] = make_float4(0.f, 0.f, 0.f, 0.f);   // done
             if (save) {
                 L.ray_head[ray_id] = tq.ok ? tq.head : -2;
                 if (!tq.ok) L.tile_unrecorded[tile] = 1;
@@ -743,9 +745,14 @@ cudaError_t launch_march_forward(const MarchLaunch& m, cudaStream_t s) {
     if (grid <= 0) return cudaSuccess;
     const bool count = (m.m.flags & RGX_FLAG_COUNT_WORK) != 0, save = m.tape != nullptr;
     const int ctas = grid * kTileSplit;
+    if (m.hz_phase == 3) {
+        if (save) note_launch(), march_forward_lists_kernel<false, true, 2><<<ctas, kThreads, 0, s>>>(m);
+        else note_launch(), march_forward_lists_kernel<false, false, 2><<<ctas, kThreads, 0, s>>>(m);
+        return cudaGetLastError();
+    }
     if (m.hz_phase != 0) {
-        if (save) note_launch(), march_forward_lists_kernel<false, true, true><<<ctas, kThreads, 0, s>>>(m);
-        else note_launch(), march_forward_lists_kernel<false, false, true><<<ctas, kThreads, 0, s>>>(m);
+        if (save) note_launch(), march_forward_lists_kernel<false, true, 1><<<ctas, kThreads, 0, s>>>(m);
+        else note_launch(), march_forward_lists_kernel<false, false, 1><<<ctas, kThreads, 0, s>>>(m);
         return cudaGetLastError();
     }
     if (count && save) note_launch(), march_forward_lists_kernel<true, true><<<ctas, kThreads, 0, s>>>(m);

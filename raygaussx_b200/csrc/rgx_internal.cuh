@@ -122,6 +122,9 @@ struct BinLaunch {
     int* tile_diff;                        // [(tiles_x + 1) * (tiles_y + 1)] corners of the rectangles of culled Gaussians
     int* tile_more;                        // [tiles] the tile has pairs that were not emitted
     unsigned long long near_target;        // estimated pairs to keep
+    unsigned long long near_min_total;     // views with fewer estimated pairs are emitted completely ...
+    int near_half;                         // ... and so are views of which the cut would keep all (0) or half or more (1)
+    const int* tile_flag;                  // null, or [tiles]: pairs of unflagged tiles are not emitted
 };
 
 struct MarchLaunch {
@@ -171,6 +174,7 @@ struct ColorLaunch {
     const uint2* listed_rect;
     const unsigned int* listed_code;
     unsigned int listed_cut;
+    unsigned char* listed_out;   // [n_pad] 1 where the Gaussian is on some list of the view (written with listed_code)
 };
 
 struct FinalizeLaunch {
@@ -178,7 +182,8 @@ struct FinalizeLaunch {
     rgx_grads gr;
     float eye[3];
     const uint32_t* perm;
-    const float4* grad_rows;   // [grad_copies, n_pad, 4], see emit_global
+    float4* grad_rows;         // [grad_copies, n_pad, 4], see emit_global; the kernel leaves them cleared for the next backward
+    const unsigned char* listed;   // null, or [n_pad]: the march can only have met the Gaussians marked here
     int grad_copies, n_pad;
     const float4 *quat, *sdens;   // sorted copies the march used
     const float* hk;
@@ -217,10 +222,7 @@ cudaError_t launch_finalize(const FinalizeLaunch& f, cudaStream_t s);
 size_t binning_cub_temp_bytes(size_t pair_cap, int ntiles);
 cudaError_t launch_bin_emit(const BinLaunch& b, cudaStream_t s);
 cudaError_t launch_bin_fill(const BinLaunch& b, int total, cudaStream_t s);
-cudaError_t launch_bin_hist(const BinLaunch& b, int total, unsigned int* hist, cudaStream_t s);
 float bin_hist_bucket_end(const BinLaunch& b, int bucket);
-cudaError_t launch_bin_select(const BinLaunch& b, int total, int mode, unsigned int cut, const int* tile_flag, uint64_t* out_k,
-                              uint32_t* out_v, unsigned long long* counter, int* tile_more, cudaStream_t s);
 cudaError_t launch_march_forward(const MarchLaunch& m, cudaStream_t s);
 // The backward in two launches: rays without a recording (searches the lists or the hierarchy), then the replay of
 // the recording, which reads neither lists nor hierarchy.
