@@ -266,9 +266,9 @@ RGX_API int rgx_read_two_depth(rgx_ctx* ctx, long long out[4]);
  * rays that would have needed more; if there are any, the complete lists are made and the whole view is marched
  * again (same image and recording as without the feature), and the budget is multiplied by four for the views to
  * come.  Costs one more wait on the stream after the march (the count).  budget_per_ray = 0 switches the feature
- * off, < 0 leaves it as it is.  rgx_read_near_lists returns and clears (views whose lists stopped at a horizon,
+ * off, < 0 leaves it as it is; min_pairs >= 0 replaces the 2^21 (tests use 0 to take small views through it).  rgx_read_near_lists returns and clears (views whose lists stopped at a horizon,
  * the estimated number of all pairs of those views, pairs kept, views that had to be marched again). */
-RGX_API int rgx_debug_near_lists(rgx_ctx* ctx, int budget_per_ray);
+RGX_API int rgx_debug_near_lists(rgx_ctx* ctx, int budget_per_ray, long long min_pairs);
 RGX_API int rgx_read_near_lists(rgx_ctx* ctx, long long out[4]);
 
 /* Per-view tile-list construction (binning + sort), timed like the march kernels while

@@ -72,7 +72,7 @@ SYMBOLS = {
     "rgx_debug_cap_recording": (C.c_int, [C.c_void_p, C.c_longlong]),
     "rgx_debug_two_depth": (C.c_int, [C.c_void_p, C.c_int, C.c_int]),
     "rgx_read_two_depth": (C.c_int, [C.c_void_p, C.POINTER(C.c_longlong)]),
-    "rgx_debug_near_lists": (C.c_int, [C.c_void_p, C.c_int]),
+    "rgx_debug_near_lists": (C.c_int, [C.c_void_p, C.c_int, C.c_longlong]),
     "rgx_read_near_lists": (C.c_int, [C.c_void_p, C.POINTER(C.c_longlong)]),
     "rgx_measure_peaks": (C.c_int, [C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "rgx_knn_mean_dist2": (C.c_int, [C.c_int, _fp, C.c_int, _fp, C.c_void_p]),

@@ -81,6 +81,7 @@ struct rgx_ctx {
     long long lists_rays = 0;          // rays of the view the partial lists were made for
     int near_budget_per_ray = RGX_NEAR_BUDGET;   // pairs per ray such lists keep; multiplied by four whenever a ray reached the horizon
     long long near_stats[4] = {0, 0, 0, 0};   // views with such lists, pairs of those views (estimate), pairs kept, views marched again
+    long long near_min_pairs = 1ll << 21;     // views with fewer (estimated) pairs get complete lists
     double near_ratio = 2.0;                  // estimated pairs (tile rectangles) per pair kept up to the horizon, from the latest such view
     HorizonPick* near_pick = nullptr; HorizonPick* near_pick_host = nullptr;     // host copy pinned
     unsigned long long* near_hist = nullptr;
@@ -660,7 +661,7 @@ static void learn_ratio(rgx_ctx* ctx, int kept) {
     if (kept > 0) ctx->near_ratio = std::min(8.0, std::max(1.0, (double)ctx->near_pick_host->est_kept / (double)kept));
 }
 
-static Cull near_cull(const rgx_ctx* ctx) { return Cull{ctx->near_budget_per_ray, 1ull << 21, true}; }
+static Cull near_cull(const rgx_ctx* ctx) { return Cull{ctx->near_budget_per_ray, (unsigned long long)ctx->near_min_pairs, true}; }
 
 // Turns the emitted pairs into ctx->lists.  The view of a recording forward -- a training view, whose rays end long
 // before they have seen most of their tile's list (on the 3 M-Gaussian scene every ray ends within the nearest eighth
@@ -1132,9 +1133,10 @@ int rgx_debug_two_depth(rgx_ctx* ctx, int min_pairs_per_ray, int budget_per_ray)
     return RGX_OK;
 }
 
-int rgx_debug_near_lists(rgx_ctx* ctx, int budget_per_ray) {
+int rgx_debug_near_lists(rgx_ctx* ctx, int budget_per_ray, long long min_pairs) {
     if (!ctx) return RGX_E_INVALID;
     if (budget_per_ray >= 0) ctx->near_budget_per_ray = budget_per_ray;
+    if (min_pairs >= 0) ctx->near_min_pairs = min_pairs;
     ctx->lists_valid = false;          // lists made under the old setting are not reused
     return RGX_OK;
 }

@@ -255,10 +255,11 @@ class Renderer:
         _lib.check(self._ctx, self._lib.rgx_hint_next_view(self._ctx, C.byref(cam) if cam is not None else None,
                                                            C.byref(march) if march is not None else None))
 
-    def near_lists(self, budget_per_ray: int = -1) -> dict:
+    def near_lists(self, budget_per_ray: int = -1, min_pairs: int = -1) -> dict:
         """Lists up to a horizon for recording forwards (``rgx_debug_near_lists``): sets the budget of pairs per ray
-        (0 switches the feature off, negative leaves it) and returns the figures since the last call."""
-        _lib.check(self._ctx, self._lib.rgx_debug_near_lists(self._ctx, int(budget_per_ray)))
+        (0 switches the feature off, negative leaves it) and the number of pairs below which a view gets complete
+        lists anyway (negative leaves it), and returns the figures since the last call."""
+        _lib.check(self._ctx, self._lib.rgx_debug_near_lists(self._ctx, int(budget_per_ray), int(min_pairs)))
         out = (C.c_longlong * 4)()
         _lib.check(self._ctx, self._lib.rgx_read_near_lists(self._ctx, out))
         return dict(views=out[0], pairs_estimated=out[1], pairs_kept=out[2], views_marched_again=out[3])

@@ -353,3 +353,58 @@ def test_lists_up_to_a_horizon_change_nothing(big):
     r.reset_counters()
     counted, _, _ = r.forward(*tens, cs, march(ro, sc, cs, flags=_lib.FLAG_COUNT_WORK))
     assert torch.equal(counted, full_rgb) and r.read_counters()["rays"] == cs.width * cs.height
+
+
+@pytest.mark.parametrize("kind,budget", [("stress", 2), ("stress", 4), ("unbounded", 2), ("unbounded", 12), ("tiny", 2),
+                                         ("unbounded_mid", 3)])
+def test_lists_up_to_a_horizon_on_small_and_awkward_views(kind, budget):
+    """The culled emission on the views that are hardest for it -- the camera inside the scene (Gaussians that
+    straddle the eye plane or fill the view), needles at random orientations, a view of 960 rays -- with the
+    threshold on the view's size taken away: whatever the budget, whether the view has to be marched again or not,
+    a recording forward gives the image of complete lists bit for bit and its backward the same gradients.  (Views
+    of this size either get complete lists after all or are marched twice; lists that stop at a horizon and suffice
+    need the large scene of test_lists_up_to_a_horizon_change_nothing.)"""
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device: there is no CPU path")
+    from raygaussx_b200 import render_optix as ro
+    dev = torch.device("cuda")
+    if kind == "stress":
+        sc = scenes.stress_scene(n_uniform=60_000, n_cluster=10_000, n_cameras=2, width=320, height=180)
+    elif kind == "unbounded":
+        sc = scenes.unbounded_scene(n=200_000, n_cameras=3, width=314, height=207)
+    elif kind == "unbounded_mid":
+        sc = scenes.unbounded_scene(n=1_000_000, n_cameras=3, width=628, height=414)
+    else:
+        sc = scenes.tiny_scene(n=512, width=40, height=24, log_scale_mean=-2.5, dynamic_sampling=True, dt_step=0.005)
+    tens = [t.to(dev).contiguous() for t in sc.tensors()]
+    r = ro.Renderer(dev)
+    r.build(*tens[:4])
+    try:
+        for cam in sc.cameras[:3]:
+            cam.to(dev)
+            cs = ro.camera_struct(cam)
+            save = march(ro, sc, cs, flags=_lib.FLAG_SAVE_HITS)
+            results = []
+            for b in (0, budget):
+                r.near_lists(b, 0)                            # also forgets the cached lists
+                rgb, alpha, depth = r.forward(*tens, cs, save, want_alpha=True, want_depth=True)
+                rgb, alpha, depth = rgb.clone(), alpha.clone(), depth.clone()
+                st = r.near_lists()
+                dl = torch.sign(rgb - 0.5) / (3 * rgb.shape[0])
+                grads = [torch.zeros_like(t) for t in tens]
+                r.backward(*tens, cs, march(ro, sc, cs), rgb, dl, tuple(grads))
+                torch.cuda.synchronize()
+                results.append((rgb, alpha, depth, grads, st))
+            full, near = results
+            assert full[4]["views"] == 0
+            for a, b2 in zip(full[:3], near[:3]):
+                assert torch.equal(a, b2)
+            for a, b2 in zip(full[3][:5], near[3][:5]):
+                scale = a.abs().max().clamp_min(1e-30)
+                assert ((a - b2).abs().max() / scale).item() < 3e-4
+            if near[4]["views"] == 1:
+                assert near[4]["pairs_kept"] < near[4]["pairs_estimated"]
+            print(f"{kind} budget {budget}: {near[4]}")
+    finally:
+        r.near_lists(6, 1 << 21)
+        del r
