@@ -81,6 +81,14 @@ struct rgx_ctx {
     long long lists_rays = 0;          // rays of the view the partial lists were made for
     int near_budget_per_ray = RGX_NEAR_BUDGET;   // pairs per ray such lists keep; multiplied by four whenever a ray reached the horizon
     long long near_stats[4] = {0, 0, 0, 0};   // views with such lists, pairs of those views (estimate), pairs kept, views marched again
+    // rays that went beyond the horizon in the latest march over such lists: counted on the device, finished there by a
+    // per-ray search, and known to the host only later (settle_beyond)
+    int* hz_rays = nullptr; long long hz_rays_cap = 0;
+    unsigned long long* beyond_host = nullptr;   // pinned
+    cudaEvent_t ev_beyond = nullptr;
+    bool beyond_pending = false, beyond_recorded = false;
+    long long beyond_kept = 0, beyond_lists_rays = 0; int beyond_budget = 0;   // of the lists that march used
+    long long tape_beyond_rays = 0;              // rays of the current recording that went beyond (they are not recorded)
     long long near_min_pairs = 1ll << 21;     // views with fewer (estimated) pairs get complete lists
     double near_ratio = 2.0;                  // estimated pairs (tile rectangles) per pair kept up to the horizon, from the latest such view
     HorizonPick* near_pick = nullptr; HorizonPick* near_pick_host = nullptr;     // host copy pinned
@@ -180,7 +188,7 @@ void release_workspace(rgx_ctx* ctx) {
                      (void**)&ctx->big_rect, (void**)&ctx->tile_unrecorded, (void**)&ctx->tile_more, (void**)&ctx->tile_resume,
                      (void**)&ctx->hz_state, (void**)&ctx->hz_scalars, (void**)&ctx->tape_tile_order, (void**)&ctx->near_pick,
                      (void**)&ctx->near_hist, (void**)&ctx->g_rect, (void**)&ctx->g_code, (void**)&ctx->tile_diff,
-                     (void**)&ctx->listed};
+                     (void**)&ctx->listed, (void**)&ctx->hz_rays};
     for (void** p : ptrs) {
         if (*p) cudaFree(*p);
         *p = nullptr;
@@ -199,6 +207,7 @@ void release_workspace(rgx_ctx* ctx) {
     ctx->hint_set = false;
     ctx->hz_tiles_cap = 0; ctx->hz_state_cap = 0;
     ctx->g_rect_cap = 0; ctx->tile_diff_cap = 0; ctx->listed_cap = 0; ctx->listed_serial = 0;
+    ctx->hz_rays_cap = 0; ctx->beyond_pending = false;
     ctx->grad_rows_clear = false;
     ctx->built = false;
     ctx->lists_valid = false;
@@ -340,6 +349,39 @@ int run_colors(rgx_ctx* ctx, const rgx_scene* sc, const float eye[3], cudaStream
     return e == cudaSuccess ? RGX_OK : cuda_fail(ctx, e, "colour kernel");
 }
 
+// After a march over lists that stop at a horizon: the colours of all Gaussians, for the rays that went beyond it --
+// a kernel that returns at once when `count` is zero.  The same evaluation as the one rgba holds (same eye): neither
+// serial moves; every Gaussian then counts as listed.
+int run_colors_if_beyond(rgx_ctx* ctx, const rgx_scene* sc, const float eye[3], const unsigned int* count, cudaStream_t s) {
+    ColorLaunch c{};
+    c.sc = *sc;
+    std::memcpy(c.eye, eye, sizeof(c.eye));
+    c.perm = ctx->vals_out;
+    c.rgba = ctx->rgba;
+    c.sigma_threshold = ctx->sigma_threshold;
+    c.only_if = count;
+    c.listed_out = ctx->listed_serial == ctx->rgba_serial ? ctx->listed : nullptr;
+    cudaError_t e = launch_colors(c, s);
+    return e == cudaSuccess ? RGX_OK : cuda_fail(ctx, e, "colour kernel");
+}
+
+// The number of rays that went beyond the horizon in the latest march over lists that stop at one was copied to the
+// host behind that march; whoever needs it waits for the copy here (by then long done).  A view in which it is not
+// zero makes the lists of the views to come four times deeper -- unless its own lists had fallen short of the budget:
+// then the estimate was off, and has been corrected already.
+void settle_beyond(rgx_ctx* ctx) {
+    if (!ctx->beyond_pending) return;
+    ctx->beyond_pending = false;
+    if (cudaEventSynchronize(ctx->ev_beyond) != cudaSuccess) { (void)cudaGetLastError(); return; }
+    const long long n = (long long)(*ctx->beyond_host & 0xffffffffull);
+    if (ctx->beyond_recorded) ctx->tape_beyond_rays = n;
+    if (n == 0) return;
+    ctx->near_stats[3] += 1;
+    if ((double)ctx->beyond_kept >= 0.75 * (double)ctx->beyond_budget * (double)ctx->beyond_lists_rays &&
+        ctx->near_budget_per_ray == ctx->beyond_budget && ctx->near_budget_per_ray < (1 << 18))
+        ctx->near_budget_per_ray *= 4;
+}
+
 struct ScopedTimer {   // brackets one kernel launch with events when profiling is on
     rgx_ctx* ctx;
     cudaStream_t s;
@@ -388,6 +430,8 @@ void rgx_destroy(rgx_ctx* ctx) {
     if (ctx->bin_total_host) cudaFreeHost(ctx->bin_total_host);
     if (ctx->tape_used_host) cudaFreeHost(ctx->tape_used_host);
     if (ctx->near_pick_host) cudaFreeHost(ctx->near_pick_host);
+    if (ctx->beyond_host) cudaFreeHost(ctx->beyond_host);
+    if (ctx->ev_beyond) cudaEventDestroy(ctx->ev_beyond);
     if (ctx->hz_scalars_host) cudaFreeHost(ctx->hz_scalars_host);
     if (ctx->side) cudaStreamDestroy(ctx->side);
     if (ctx->ev_main) cudaEventDestroy(ctx->ev_main);
@@ -856,6 +900,7 @@ static int forward_impl(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* 
     if (rc) return rc;
     if (!rgb && !frame) return fail(ctx, RGX_E_INVALID, "colour output is null");
     cudaStream_t s = (cudaStream_t)stream;
+    settle_beyond(ctx);
     join_side(ctx, s);
     L.rgb = rgb; L.alpha = alpha; L.depth = depth; L.frame = frame;
     const bool counting = (march->flags & RGX_FLAG_COUNT_WORK) != 0;
@@ -953,32 +998,40 @@ static int forward_impl(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* 
         }
         return RGX_OK;
     };
-    for (int attempt = 0;; ++attempt) {
-        const bool near_lists = L.lists.ent_id != nullptr && ctx->lists_partial && !counting && attempt == 0;
-        L.hz_phase = 0;
-        if (near_lists) {
-            // the lists hold the pairs that begin before the horizon only: rays that would need more are counted
-            L.hz_phase = 3; L.horizon = ctx->lists_horizon; L.tile_more = ctx->tile_more;
-            L.hz_count = reinterpret_cast<unsigned int*>(ctx->hz_scalars + 1);
-            cudaError_t e0 = cudaMemsetAsync(ctx->hz_scalars + 1, 0, sizeof(unsigned long long), s);
-            if (e0 != cudaSuccess) return cuda_fail(ctx, e0, "horizon counter");
-        }
+    const bool near_lists = L.lists.ent_id != nullptr && ctx->lists_partial && !counting;
+    if (!near_lists) {
         if ((rc = march_once())) return rc;
-        if (!near_lists) return RGX_OK;
-        cudaError_t e1 = cudaMemcpyAsync(ctx->hz_scalars_host + 1, ctx->hz_scalars + 1, sizeof(unsigned long long),
-                                         cudaMemcpyDeviceToHost, s);
-        if (e1 == cudaSuccess) e1 = cudaStreamSynchronize(s);
-        if (e1 != cudaSuccess) return cuda_fail(ctx, e1, "horizon read-back");
-        if ((ctx->hz_scalars_host[1] & 0xffffffffull) == 0ull) return RGX_OK;      // every ray ended before the horizon
-        // some ray reached the horizon: the complete lists, the whole view again, and deeper lists from now on
-        // (unless the lists fell short of the budget: then the estimate was off, and has been corrected already)
-        ctx->near_stats[3] += 1;
-        if ((double)ctx->last_pairs >= 0.75 * (double)ctx->near_budget_per_ray * (double)ctx->lists_rays && ctx->near_budget_per_ray < (1 << 18))
-            ctx->near_budget_per_ray *= 4;
-        ctx->lists_valid = false;
-        if ((rc = ensure_lists(ctx, cam, march, s)) || (rc = run_colors(ctx, scene, cam->eye, s))) return rc;
-        L.lists = ctx->lists;
+        if (L.tape) ctx->tape_beyond_rays = 0;
+        return RGX_OK;
     }
+    // The lists hold the pairs that begin before a horizon only.  A ray that would need more is counted, listed and
+    // left unrecorded by the march; the two launches behind it -- no-ops when the count is zero -- evaluate the colours
+    // of all Gaussians and finish those rays by a per-ray search of the hierarchy.  The host learns the count later.
+    cudaError_t e = cudaSuccess;
+    const long long all_rays = (long long)cam->width * cam->height;
+    if (all_rays > ctx->hz_rays_cap) {
+        if ((e = regrow(ctx, ctx->hz_rays, (size_t)all_rays)) != cudaSuccess) return cuda_fail(ctx, e, "rays beyond the horizon");
+        ctx->hz_rays_cap = all_rays;
+    }
+    if (!ctx->beyond_host && (e = cudaMallocHost((void**)&ctx->beyond_host, sizeof(unsigned long long))) != cudaSuccess)
+        return cuda_fail(ctx, e, "pinned counter");
+    if (!ctx->ev_beyond && (e = cudaEventCreateWithFlags(&ctx->ev_beyond, cudaEventDisableTiming)) != cudaSuccess)
+        return cuda_fail(ctx, e, "event");
+    L.hz_phase = 3; L.horizon = ctx->lists_horizon; L.tile_more = ctx->tile_more;
+    L.hz_count = reinterpret_cast<unsigned int*>(ctx->hz_scalars + 1);
+    L.hz_rays = ctx->hz_rays;
+    if ((e = cudaMemsetAsync(ctx->hz_scalars + 1, 0, sizeof(unsigned long long), s)) != cudaSuccess)
+        return cuda_fail(ctx, e, "horizon counter");
+    if ((rc = march_once())) return rc;
+    if ((rc = run_colors_if_beyond(ctx, scene, cam->eye, L.hz_count, s))) return rc;
+    if ((e = launch_march_forward_listed_rays(L, (ctx->sm_count > 0 ? ctx->sm_count : 148) * 4, s)) != cudaSuccess ||
+        (e = cudaMemcpyAsync(ctx->beyond_host, ctx->hz_scalars + 1, sizeof(unsigned long long), cudaMemcpyDeviceToHost, s)) != cudaSuccess ||
+        (e = cudaEventRecord(ctx->ev_beyond, s)) != cudaSuccess)
+        return cuda_fail(ctx, e, "rays beyond the horizon");
+    ctx->beyond_pending = true;
+    ctx->beyond_recorded = L.tape != nullptr;
+    ctx->beyond_kept = ctx->last_pairs; ctx->beyond_lists_rays = ctx->lists_rays; ctx->beyond_budget = ctx->near_budget_per_ray;
+    return RGX_OK;
 }
 
 int rgx_forward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, const rgx_march* march, float* rgb,
@@ -1011,6 +1064,7 @@ int rgx_backward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, co
         return fail(ctx, RGX_E_INVALID, "null spherical-Gaussian gradient tensor");
     if (scene->n == 0) return RGX_OK;
     cudaStream_t s = (cudaStream_t)stream;
+    settle_beyond(ctx);
     join_side(ctx, s);
     // a backward that replays the recording of this very view finds the forward's per-view colours still in place
     // the recording is this view's: same build, camera, rows and the march parameters that shape the slabs
@@ -1032,9 +1086,9 @@ int rgx_backward(rgx_ctx* ctx, const rgx_scene* scene, const rgx_camera* cam, co
     // the rays of a view whose lists stop at a horizon met listed Gaussians only (whichever lists this backward searches)
     const bool rows_listed = ctx->listed_serial != 0 && ctx->listed_serial == ctx->rgba_serial;
     if (!(march->flags & (RGX_FLAG_BRUTE_FORCE | RGX_FLAG_PER_RAY_SEARCH))) {
-        // lists that stop at a horizon serve the backward of the view whose forward they were checked by (its rays
-        // are known to end before the horizon); any other backward gets complete lists
-        if ((rc = ensure_lists(ctx, cam, march, s, false, tape_matches))) return rc;
+        // lists that stop at a horizon serve the backward of the view whose forward found that all its rays end
+        // before the horizon; any other backward gets complete lists
+        if ((rc = ensure_lists(ctx, cam, march, s, false, tape_matches && ctx->tape_beyond_rays == 0))) return rc;
         L.lists = ctx->lists;
     }
     if (L.lists.ent_id && tape_matches) {
@@ -1135,6 +1189,8 @@ int rgx_debug_two_depth(rgx_ctx* ctx, int min_pairs_per_ray, int budget_per_ray)
 
 int rgx_debug_near_lists(rgx_ctx* ctx, int budget_per_ray, long long min_pairs) {
     if (!ctx) return RGX_E_INVALID;
+    DeviceGuard guard(ctx->device);
+    settle_beyond(ctx);
     if (budget_per_ray >= 0) ctx->near_budget_per_ray = budget_per_ray;
     if (min_pairs >= 0) ctx->near_min_pairs = min_pairs;
     ctx->lists_valid = false;          // lists made under the old setting are not reused
@@ -1143,6 +1199,8 @@ int rgx_debug_near_lists(rgx_ctx* ctx, int budget_per_ray, long long min_pairs) 
 
 int rgx_read_near_lists(rgx_ctx* ctx, long long out[4]) {
     if (!ctx || !out) return RGX_E_INVALID;
+    DeviceGuard guard(ctx->device);
+    settle_beyond(ctx);
     for (int i = 0; i < 4; ++i) { out[i] = ctx->near_stats[i]; ctx->near_stats[i] = 0; }
     return RGX_OK;
 }

@@ -85,6 +85,10 @@ __global__ void __launch_bounds__(128) colors_kernel(ColorLaunch c) {
     const int n = c.sc.n;
     const int n_slots = c.perm ? ((n + 31) / 32) * 32 : n;
     if (j >= n_slots) return;
+    if (c.only_if) {                     // the colours of all Gaussians after all: some ray went beyond the lists' horizon
+        if (*c.only_if == 0u) return;
+        if (c.listed_out) c.listed_out[j] = j < n ? 1 : 0;
+    }
     if (j >= n) {
         c.rgba[j] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (c.listed_code) c.listed_out[j] = 0;

@@ -26,6 +26,52 @@ namespace rgx {
 
 namespace {
 
+// One ray from start to end, every query a search of the hierarchy (BRUTE: of all Gaussians).
+template <bool COUNT, bool BRUTE>
+__device__ __forceinline__ void march_ray_by_search(const MarchLaunch& L, int px, int py, const SceneBox& box, float eps,
+                                                    float bg, WarpShared& ws, int lane, Tally& tl) {
+    const int ray_id = py * L.cam.width + px;
+    Ray r;
+    make_ray(L.cam, px, py, r);
+    float tenter, texit;
+    clip_scene(box, r, tenter, texit);
+    RayColor st = {1.0f, 0.f, 0.f, 0.f, 0.f};
+    if (COUNT) tl.v[C_RAYS] += 1;
+    float first = L.g.n > 0 ? search_closest<COUNT, BRUTE>(L, r, tenter, texit, ws, lane, tl) : INFINITY;
+    if (first < INFINITY && first < texit) {                                  // :249-260
+        tenter = first;
+        float tbuffer = tenter;
+        int slab_index = 0;
+        while (tbuffer < texit && st.T > eps && slab_index < kMaxSlabs) {     // :266
+            SlabPlan p = plan_slab(L.m, tbuffer, st.T, tenter, texit);
+            if (COUNT) tl.v[C_SLABS] += 1;
+            ++slab_index;
+            if (!p.traced) { tbuffer = __fadd_rn(tbuffer, p.slab); continue; }
+            const float tau = __fmul_rn((float)lane + 0.5f, p.dt);            // sample offset from tbuffer
+            float s, cr, cg, cb;
+            bool overflow;
+            int nhit = slab_sums<COUNT, false>(L, L.m, tbuffer, tau, ray_id, slab_index, make_float3(0.f, 0.f, 0.f),
+                                               ws, lane, tl, [&](auto&& leaf) {
+                search_all<COUNT, BRUTE>(L, r, p.tmin, p.tmax, ws, lane, tl, leaf);
+            }, s, cr, cg, cb, overflow);
+            if (COUNT) { tl.v[C_HITS] += nhit; tl.v[C_OVF] += overflow ? 1 : 0; }
+            if (nhit == 0) {                                                  // :297-319
+                tbuffer = __fadd_rn(tbuffer, p.slab);
+                float nxt = search_closest<COUNT, BRUTE>(L, r, tbuffer, texit, ws, lane, tl);
+                if (!(nxt < INFINITY)) break;
+                tbuffer = nxt;
+                continue;
+            }
+            if (COUNT) tl.v[C_SLABS_HIT] += 1;
+            composite_forward(p, tbuffer, tau, eps, lane, s, cr, cg, cb, L.depth != nullptr, st);
+            tbuffer = __fadd_rn(tbuffer, p.slab);                             // :324
+        }
+    }
+    if (lane == 0) {                                                           // :326-339
+        write_ray(L, ray_id, st, bg);
+    }
+}
+
 template <bool COUNT, bool BRUTE>
 __global__ void __launch_bounds__(kWarps * 32) march_forward_kernel(const __grid_constant__ MarchLaunch L) {
     __shared__ WarpShared shared[kWarps];
@@ -46,48 +92,30 @@ __global__ void __launch_bounds__(kWarps * 32) march_forward_kernel(const __grid
     for (int k = 0; k < kTile; ++k) {
         const int py = L.m.row_begin + tile_y * kTile + k;
         if (py >= L.m.row_end) break;
-        const int ray_id = py * W + px;
-        Ray r;
-        make_ray(L.cam, px, py, r);
-        float tenter, texit;
-        clip_scene(box, r, tenter, texit);
-        RayColor st = {1.0f, 0.f, 0.f, 0.f, 0.f};
-        if (COUNT) tl.v[C_RAYS] += 1;
-        float first = L.g.n > 0 ? search_closest<COUNT, BRUTE>(L, r, tenter, texit, ws, lane, tl) : INFINITY;
-        if (first < INFINITY && first < texit) {                                  // :249-260
-            tenter = first;
-            float tbuffer = tenter;
-            int slab_index = 0;
-            while (tbuffer < texit && st.T > eps && slab_index < kMaxSlabs) {     // :266
-                SlabPlan p = plan_slab(L.m, tbuffer, st.T, tenter, texit);
-                if (COUNT) tl.v[C_SLABS] += 1;
-                ++slab_index;
-                if (!p.traced) { tbuffer = __fadd_rn(tbuffer, p.slab); continue; }
-                const float tau = __fmul_rn((float)lane + 0.5f, p.dt);            // sample offset from tbuffer
-                float s, cr, cg, cb;
-                bool overflow;
-                int nhit = slab_sums<COUNT, false>(L, L.m, tbuffer, tau, ray_id, slab_index, make_float3(0.f, 0.f, 0.f),
-                                                   ws, lane, tl, [&](auto&& leaf) {
-                    search_all<COUNT, BRUTE>(L, r, p.tmin, p.tmax, ws, lane, tl, leaf);
-                }, s, cr, cg, cb, overflow);
-                if (COUNT) { tl.v[C_HITS] += nhit; tl.v[C_OVF] += overflow ? 1 : 0; }
-                if (nhit == 0) {                                                  // :297-319
-                    tbuffer = __fadd_rn(tbuffer, p.slab);
-                    float nxt = search_closest<COUNT, BRUTE>(L, r, tbuffer, texit, ws, lane, tl);
-                    if (!(nxt < INFINITY)) break;
-                    tbuffer = nxt;
-                    continue;
-                }
-                if (COUNT) tl.v[C_SLABS_HIT] += 1;
-                composite_forward(p, tbuffer, tau, eps, lane, s, cr, cg, cb, L.depth != nullptr, st);
-                tbuffer = __fadd_rn(tbuffer, p.slab);                             // :324
-            }
-        }
-        if (lane == 0) {                                                           // :326-339
-            write_ray(L, ray_id, st, bg);
-        }
+        march_ray_by_search<COUNT, BRUTE>(L, px, py, box, eps, bg, ws, lane, tl);
     }
     if (COUNT) flush_tally(L, tl, lane);
+}
+
+// The rays a list march left unfinished because its lists stop at a horizon (march_lists.cu, HZ = 2): L.hz_rays
+// holds their numbers, *L.hz_count how many.  They are marched again from the start by searching the hierarchy,
+// which needs no lists: same hits, met in slot order instead of list order, so the colour equals that of complete
+// lists to summation rounding.  Launched after every such march; returns at once when there are none.
+__global__ void __launch_bounds__(kWarps * 32) march_forward_listed_rays_kernel(const __grid_constant__ MarchLaunch L) {
+    __shared__ WarpShared shared[kWarps];
+    const unsigned int n = *L.hz_count;
+    if (n == 0u) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float eps = L.m.transmittance_eps;
+    const float bg = L.m.white_background ? 1.0f : 0.0f;
+    const SceneBox box = *L.box;
+    Tally tl;
+#pragma unroll
+    for (int i = 0; i < C_NUM; ++i) tl.v[i] = 0;
+    for (unsigned int i = blockIdx.x * kWarps + warp; i < n; i += gridDim.x * kWarps) {
+        const int ray_id = L.hz_rays[i];
+        march_ray_by_search<false, false>(L, ray_id % L.cam.width, ray_id / L.cam.width, box, eps, bg, shared[warp], lane, tl);
+    }
 }
 
 template <bool BRUTE>
@@ -171,6 +199,12 @@ cudaError_t launch_march_forward_per_ray(const MarchLaunch& m, cudaStream_t s) {
     else if (count) note_launch(), march_forward_kernel<true, false><<<grid, kWarps * 32, 0, s>>>(m);
     else if (brute) note_launch(), march_forward_kernel<false, true><<<grid, kWarps * 32, 0, s>>>(m);
     else note_launch(), march_forward_kernel<false, false><<<grid, kWarps * 32, 0, s>>>(m);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_march_forward_listed_rays(const MarchLaunch& m, int ctas, cudaStream_t s) {
+    if (m.g.n <= 0 || !m.hz_rays || !m.hz_count) return cudaSuccess;
+    note_launch(), march_forward_listed_rays_kernel<<<ctas, kWarps * 32, 0, s>>>(m);
     return cudaGetLastError();
 }
 

@@ -206,6 +206,14 @@ __device__ __forceinline__ bool ray_pixel(const MarchLaunch& L, int tile_x, int 
     return px < L.cam.width && py >= L.m.row_begin && py < L.m.row_end;
 }
 
+// A ray stops at the horizon of its lists: counted; in the counting-only variant its number is kept as well, for the
+// per-ray search that finishes it (march.cu).
+template <int HZ>
+__device__ __forceinline__ void hz_note(const MarchLaunch& L, int ray_id) {
+    const unsigned int at = atomicAdd(L.hz_count, 1u);
+    if (HZ == 2) L.hz_rays[at] = ray_id;
+}
+
 // ---------------------------------------------------------------- forward
 // HZ: the two-depth variant for forward-only views whose rays end early (binning.cu).  In its first phase
 // (L.hz_phase == 1) the tile lists hold only the pairs that begin before L.horizon; a ray that would need more
@@ -214,8 +222,8 @@ __device__ __forceinline__ bool ray_pixel(const MarchLaunch& L, int tile_x, int 
 // The second phase (L.hz_phase == 2) has the complete lists of the flagged tiles and takes those rays up where
 // they stopped: same slabs, same hits in the same order, same image.
 // L.hz_phase == 3 is the first phase without a second one, for recording forwards (training views, whose rays
-// are expected to end before the horizon): a ray that would need more is only counted, and the caller, if the
-// count is not zero, makes the complete lists and marches the whole view again.
+// are expected to end before the horizon): a ray that would need more is counted and listed (L.hz_rays), marked as
+// not recorded, and finished by march_forward_listed_rays_kernel, which the caller launches next.
 // HZ = 1: the two phases (L.hz_phase 1 or 2); HZ = 2: counting only (L.hz_phase 3), nothing is put aside.
 template <bool COUNT, bool SAVE, int HZ = 0>
 __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 4) march_forward_lists_kernel(const __grid_constant__ MarchLaunch L) {
@@ -294,7 +302,7 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 4) march_forward_lists_k
                     L.hz_state[2 * (size_t)ray_id] = make_float4(tenter, 1.0f, tenter, 2.0f);
                     L.tile_resume[tile] = 1;
                 }
-                atomicAdd(L.hz_count, 1u);
+                hz_note<HZ>(L, ray_id);
             }
         } else if (first < INFINITY && first < texit) {                           // :249-260
             tenter = first;
@@ -315,7 +323,7 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 4) march_forward_lists_k
                             L.hz_state[2 * (size_t)ray_id + 1] = sh.color[warp];
                             L.tile_resume[tile] = 1;
                         }
-                        atomicAdd(L.hz_count, 1u);
+                        hz_note<HZ>(L, ray_id);
                     }
                     break;
                 }
@@ -379,7 +387,7 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 4) march_forward_lists_k
                                 L.hz_state[2 * (size_t)ray_id + 1] = sh.color[warp];
                                 L.tile_resume[tile] = 1;
                             }
-                            atomicAdd(L.hz_count, 1u);
+                            hz_note<HZ>(L, ray_id);
                         }
                         break;
                     }
@@ -393,6 +401,10 @@ __global__ void __launch_bounds__(kThreads, COUNT ? 1 : 4) march_forward_lists_k
                 if (COUNT) tl.v[C_CYC_COMP] += clock64() - c_c;
                 tbuffer = __fadd_rn(tbuffer, p.slab);                             // :324
             }
+        }
+        if (HZ == 2 && hz_susp && save && lane == 0) {             // the backward searches this ray again
+            L.ray_head[ray_id] = -2;
+            L.tile_unrecorded[tile] = 1;
         }
         if (lane == 0 && !(HZ && hz_susp)) {                                       // :326-339
             const float4 acc = sh.color[warp];

@@ -159,6 +159,7 @@ struct MarchLaunch {
     const int* tile_more;     // per tile: has pairs that begin beyond the horizon
     int* tile_resume;         // per tile: some ray stopped at the horizon
     unsigned int* hz_count;   // rays that stopped
+    int* hz_rays;             // hz_phase 3: their numbers, for march_forward_listed_rays_kernel
     float4* grad_rows;    // [grad_copies, n_pad, 4] float4 of accumulated moments, layout in emit_global
     int grad_copies;      // power of two
 };
@@ -175,6 +176,7 @@ struct ColorLaunch {
     const unsigned int* listed_code;
     unsigned int listed_cut;
     unsigned char* listed_out;   // [n_pad] 1 where the Gaussian is on some list of the view (written with listed_code)
+    const unsigned int* only_if; // not null: the kernel does nothing when this counter is zero
 };
 
 struct FinalizeLaunch {
@@ -224,6 +226,8 @@ cudaError_t launch_bin_emit(const BinLaunch& b, cudaStream_t s);
 cudaError_t launch_bin_fill(const BinLaunch& b, int total, cudaStream_t s);
 float bin_hist_bucket_end(const BinLaunch& b, int bucket);
 cudaError_t launch_march_forward(const MarchLaunch& m, cudaStream_t s);
+// The rays listed in m.hz_rays by a march over lists that stop at a horizon, again by per-ray search (march.cu).
+cudaError_t launch_march_forward_listed_rays(const MarchLaunch& m, int ctas, cudaStream_t s);
 // The backward in two launches: rays without a recording (searches the lists or the hierarchy), then the replay of
 // the recording, which reads neither lists nor hierarchy.
 cudaError_t launch_march_backward_search(const MarchLaunch& m, cudaStream_t s);

@@ -262,7 +262,7 @@ class Renderer:
         _lib.check(self._ctx, self._lib.rgx_debug_near_lists(self._ctx, int(budget_per_ray), int(min_pairs)))
         out = (C.c_longlong * 4)()
         _lib.check(self._ctx, self._lib.rgx_read_near_lists(self._ctx, out))
-        return dict(views=out[0], pairs_estimated=out[1], pairs_kept=out[2], views_marched_again=out[3])
+        return dict(views=out[0], pairs_estimated=out[1], pairs_kept=out[2], views_with_rays_beyond=out[3])
 
     def lists_made_ahead(self) -> int:
         return int(self._lib.rgx_lists_made_ahead(self._ctx))

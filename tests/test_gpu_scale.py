@@ -315,9 +315,9 @@ def test_lists_made_ahead_change_nothing(kind):
 
 
 def test_lists_up_to_a_horizon_change_nothing(big):
-    """A recording forward sorts only the pairs that begin nearest to the eye; the image, the recording and the
-    gradients must be those of the complete lists -- also when the budget is so small that rays reach the horizon
-    and the view has to be marched again with complete lists."""
+    """A recording forward emits and sorts only the pairs that begin nearest to the eye; the image, the recording and
+    the gradients must be those of the complete lists -- bit for bit while every ray ends before the horizon, and to
+    summation rounding when the budget is so small that rays reach it and are finished by the per-ray search."""
     ro, r, sc, tens, cs = big
     r.build(*tens[:4])                              # other tests of this module built their own scenes meanwhile
     save = march(ro, sc, cs, flags=_lib.FLAG_SAVE_HITS)
@@ -336,15 +336,15 @@ def test_lists_up_to_a_horizon_change_nothing(big):
     full_rgb, full_grads, st0 = run(0)
     assert st0["views"] == 0
     near_rgb, near_grads, st1 = run(6)
-    assert st1["views"] == 1 and st1["views_marched_again"] == 0 and st1["pairs_kept"] * 2 < st1["pairs_estimated"]
+    assert st1["views"] == 1 and st1["views_with_rays_beyond"] == 0 and st1["pairs_kept"] * 2 < st1["pairs_estimated"]
     assert torch.equal(near_rgb, full_rgb)
     again_rgb, again_grads, st2 = run(1)            # one pair per ray: far too shallow
-    assert st2["views"] == 1 and st2["views_marched_again"] == 1
-    assert torch.equal(again_rgb, full_rgb)
+    assert st2["views"] == 1 and st2["views_with_rays_beyond"] == 1
+    assert (again_rgb - full_rgb).abs().max().item() < 2e-5
     for a, b, c in zip(full_grads[:5], near_grads[:5], again_grads[:5]):
         scale = a.abs().max()
         assert ((a - b).abs().max() / scale).item() < 3e-4 and ((a - c).abs().max() / scale).item() < 3e-4
-    # the budget was multiplied by four after the second march; put the default back for the tests that follow
+    # the budget was multiplied by four after that view; put the default back for the tests that follow
     r.near_lists(6)
     # a forward without recording on the cached near lists, and a counting forward (which wants complete lists)
     r.forward(*tens, cs, save)
@@ -361,8 +361,9 @@ def test_lists_up_to_a_horizon_on_small_and_awkward_views(kind, budget):
     """The culled emission on the views that are hardest for it -- the camera inside the scene (Gaussians that
     straddle the eye plane or fill the view), needles at random orientations, a view of 960 rays -- with the
     threshold on the view's size taken away: whatever the budget, whether the view has to be marched again or not,
-    a recording forward gives the image of complete lists bit for bit and its backward the same gradients.  (Views
-    of this size either get complete lists after all or are marched twice; lists that stop at a horizon and suffice
+    a recording forward gives the image of complete lists (bit for bit where no ray reaches the horizon, to summation
+    rounding where some are finished by the per-ray search) and its backward the same gradients.  (Views of this size
+    either get complete lists after all or have rays beyond the horizon; lists that stop at a horizon and suffice
     need the large scene of test_lists_up_to_a_horizon_change_nothing.)"""
     if not torch.cuda.is_available():
         pytest.fail("GPU tests need a CUDA device: there is no CPU path")
@@ -397,8 +398,11 @@ def test_lists_up_to_a_horizon_on_small_and_awkward_views(kind, budget):
                 results.append((rgb, alpha, depth, grads, st))
             full, near = results
             assert full[4]["views"] == 0
-            for a, b2 in zip(full[:3], near[:3]):
-                assert torch.equal(a, b2)
+            for a, b2, tol in zip(full[:3], near[:3], (2e-5, 2e-5, 2e-4)):
+                if near[4]["views_with_rays_beyond"] == 0:
+                    assert torch.equal(a, b2)
+                else:
+                    assert (a - b2).abs().max().item() < tol * max(1.0, a.abs().max().item())
             for a, b2 in zip(full[3][:5], near[3][:5]):
                 scale = a.abs().max().clamp_min(1e-30)
                 assert ((a - b2).abs().max() / scale).item() < 3e-4
