@@ -260,15 +260,20 @@ __host__ __device__ inline float near_stored(unsigned q, const KeyLayout& kl) {
 #endif
 }
 
+// Largest distance from the eye to a point of the box, rounded up (pair_range grows the box in proportion to it).
+__device__ __forceinline__ float box_far_distance(const float* eye, float2 bx, float2 by, float2 bz) {
+    const float fx = fmaxf(fabsf(bx.x - eye[0]), fabsf(bx.y - eye[0])), fy = fmaxf(fabsf(by.x - eye[1]), fabsf(by.y - eye[1])),
+                fz = fmaxf(fabsf(bz.x - eye[2]), fabsf(bz.y - eye[2]));
+    return sqrtf(fx * fx + fy * fy + fz * fz) * (1.0f + 1e-5f) + 1e-6f;
+}
+
 // What pair_range needs to know of a Gaussian, from its box, whitening map, scales, quaternion and hk.
 __device__ __forceinline__ PairGeom make_pair_geom(const float* eye, float2 bx, float2 by, float2 bz, float4 g0, float4 g1,
                                                    float4 g2, float4 sd, float4 q, float kk) {
     PairGeom g;
     g.bx = bx; g.by = by; g.bz = bz;
     g.g0 = g0; g.g1 = g1; g.g2 = g2;
-    float fx = fmaxf(fabsf(bx.x - eye[0]), fabsf(bx.y - eye[0])), fy = fmaxf(fabsf(by.x - eye[1]), fabsf(by.y - eye[1])),
-          fz = fmaxf(fabsf(bz.x - eye[2]), fabsf(bz.y - eye[2]));
-    g.far_box = sqrtf(fx * fx + fy * fy + fz * fz) * (1.0f + 1e-5f) + 1e-6f;
+    g.far_box = box_far_distance(eye, bx, by, bz);
     float smin = fminf(sd.x, fminf(sd.y, sd.z));
     float qn = q.x * q.x + q.y * q.y + q.z * q.z + q.w * q.w;
     g.rho_scale = 1.02f * fmaxf(1.0f, qn) / (kk * smin);
@@ -413,10 +418,7 @@ __global__ void __launch_bounds__(kEmitThreads) bin_near_hist_kernel(BinLaunch b
                 const float* e = b.cam.eye;
                 const float dx = fmaxf(fmaxf(bx.x - e[0], e[0] - bx.y), 0.f), dy = fmaxf(fmaxf(by.x - e[1], e[1] - by.y), 0.f),
                             dz = fmaxf(fmaxf(bz.x - e[2], e[2] - bz.y), 0.f);
-                const float fx = fmaxf(fabsf(bx.x - e[0]), fabsf(bx.y - e[0])), fy = fmaxf(fabsf(by.x - e[1]), fabsf(by.y - e[1])),
-                            fz = fmaxf(fabsf(bz.x - e[2]), fabsf(bz.y - e[2]));
-                const float far_box = sqrtf(fx * fx + fy * fy + fz * fz) * (1.0f + 1e-5f) + 1e-6f;
-                const float infl = far_box * __uint_as_float(b.pick->chord_bits) * 1.0001f + 1e-6f;
+                const float infl = box_far_distance(e, bx, by, bz) * __uint_as_float(b.pick->chord_bits) * 1.0001f + 1e-6f;
                 const float gn = fmaxf((sqrtf(dx * dx + dy * dy + dz * dz) - 1.7321f * infl) * (1.0f - 1e-4f) - 1e-4f, 0.f);
                 code = hist_bucket(gn, kl);
                 rect = r;
