@@ -93,7 +93,7 @@ struct rgx_ctx {
     double near_ratio = 2.0;                  // estimated pairs (tile rectangles) per pair kept up to the horizon, from the latest such view
     HorizonPick* near_pick = nullptr; HorizonPick* near_pick_host = nullptr;     // host copy pinned
     unsigned long long* near_hist = nullptr;
-    uint2* g_rect = nullptr; unsigned int* g_code = nullptr; int g_rect_cap = 0;
+    uint2* g_rect = nullptr; unsigned int* g_code = nullptr; int* kept_slot = nullptr; int g_rect_cap = 0;
     int* tile_diff = nullptr; size_t tile_diff_cap = 0;
     unsigned long long lists_build_id = 0;
     rgx_camera lists_cam{};
@@ -187,7 +187,7 @@ void release_workspace(rgx_ctx* ctx) {
                      (void**)&ctx->tile_cnt_sorted, (void**)&ctx->tile_order, (void**)&ctx->big_slot,
                      (void**)&ctx->big_rect, (void**)&ctx->tile_unrecorded, (void**)&ctx->tile_more, (void**)&ctx->tile_resume,
                      (void**)&ctx->hz_state, (void**)&ctx->hz_scalars, (void**)&ctx->tape_tile_order, (void**)&ctx->near_pick,
-                     (void**)&ctx->near_hist, (void**)&ctx->g_rect, (void**)&ctx->g_code, (void**)&ctx->tile_diff,
+                     (void**)&ctx->near_hist, (void**)&ctx->g_rect, (void**)&ctx->g_code, (void**)&ctx->kept_slot, (void**)&ctx->tile_diff,
                      (void**)&ctx->listed, (void**)&ctx->hz_rays};
     for (void** p : ptrs) {
         if (*p) cudaFree(*p);
@@ -588,7 +588,7 @@ static int emit_setup(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, B
                 return cuda_fail(ctx, e, "pinned horizon");
         }
         if (ctx->n_pad > ctx->g_rect_cap) {
-            RGB_(g_rect, (size_t)ctx->n_pad); RGB_(g_code, (size_t)ctx->n_pad);
+            RGB_(g_rect, (size_t)ctx->n_pad); RGB_(g_code, (size_t)ctx->n_pad); RGB_(kept_slot, (size_t)ctx->n_pad);
             ctx->g_rect_cap = ctx->n_pad;
         }
         if (ctx->n_pad > ctx->listed_cap) {
@@ -601,7 +601,7 @@ static int emit_setup(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, B
             RGB_(tile_diff, diff + 64);
             ctx->tile_diff_cap = diff + 64;
         }
-        b.pick = ctx->near_pick; b.near_hist = ctx->near_hist; b.g_rect = ctx->g_rect; b.g_code = ctx->g_code;
+        b.pick = ctx->near_pick; b.near_hist = ctx->near_hist; b.g_rect = ctx->g_rect; b.g_code = ctx->g_code; b.kept_slot = ctx->kept_slot;
         b.tile_diff = ctx->tile_diff; b.tile_more = ctx->tile_more;
         const double rays = (double)cam->width * (double)(m->row_end - m->row_begin);
         b.near_target = (unsigned long long)((double)cull->budget_per_ray * rays * ctx->near_ratio);

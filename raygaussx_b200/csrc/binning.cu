@@ -292,6 +292,7 @@ constexpr int kEmitBuf = 1280;     // pairs gathered in shared memory between tw
 struct EmitShared {
     PairGeom geom[kEmitThreads];
     uint2 rect[kEmitThreads];
+    int slot[kEmitThreads];
     int prefix[kEmitThreads + 1];
     unsigned long long keys[kEmitBuf];
     float fars[kEmitBuf];
@@ -461,6 +462,37 @@ __global__ void __launch_bounds__(1024) bin_pick_horizon_kernel(BinLaunch b) {
     }
 }
 
+// Sorts the Gaussians into those before the cut (their slots gathered in kept_slot, so that the emission works on
+// full blocks of them) and those beyond it (the corners of their rectangles go into tile_diff).
+__global__ void __launch_bounds__(256) bin_compact_kernel(BinLaunch b) {
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    const unsigned cut = b.pick->cut;
+    bool keep = false;
+    if (j < b.n) {
+        const uint2 rect = b.g_rect[j];
+        if (rect.x != kNoRect) {
+            if (b.g_code[j] > cut) {                // every pair of this Gaussian begins beyond the horizon
+                const unsigned tx0 = rect.x & 0xffffu, tx1 = rect.x >> 16, ty0 = rect.y & 0xffffu, ty1 = rect.y >> 16;
+                const int Wd = b.tiles_x + 1;
+                atomicAdd(&b.tile_diff[ty0 * Wd + tx0], 1);
+                atomicAdd(&b.tile_diff[ty0 * Wd + tx1 + 1], -1);
+                atomicAdd(&b.tile_diff[(ty1 + 1) * Wd + tx0], -1);
+                atomicAdd(&b.tile_diff[(ty1 + 1) * Wd + tx1 + 1], 1);
+            } else {
+                keep = true;
+            }
+        }
+    }
+    const unsigned m = __ballot_sync(kFullMask, keep);
+    if (m) {
+        unsigned long long at = 0;
+        if (lane == __ffs(m) - 1) at = atomicAdd(b.total_dev + 3, (unsigned long long)__popc(m));
+        at = __shfl_sync(kFullMask, at, __ffs(m) - 1) + __popc(m & ((1u << lane) - 1u));
+        if (keep) b.kept_slot[at] = j;
+    }
+}
+
 // tile_diff holds +1 / -1 at the corners of the rectangles of the skipped Gaussians; its two-dimensional running
 // sum is the number of skipped rectangles over each tile.
 constexpr int kDiffShared = 12000;
@@ -500,37 +532,32 @@ __global__ void __launch_bounds__(kEmitThreads) bin_emit_kernel(BinLaunch b) {
     using Scan = cub::BlockScan<int, kEmitThreads>;
     __shared__ typename Scan::TempStorage scan_tmp;
     const int tid = threadIdx.x, lane = tid & 31;
-    const int j = blockIdx.x * kEmitThreads + tid;
     const unsigned cut = CULL ? b.pick->cut : kAllBuckets;
+    // CULL: the block's 256 Gaussians come from the list bin_compact_kernel left; blocks past its end have nothing to do
+    const unsigned long long n_kept = CULL ? b.total_dev[3] : (unsigned long long)b.n;
+    const unsigned long long at = (unsigned long long)blockIdx.x * kEmitThreads + tid;
+    if (CULL && (unsigned long long)blockIdx.x * kEmitThreads >= n_kept) return;
+    const int j = at < n_kept ? (CULL ? b.kept_slot[at] : (int)at) : -1;
     int count = 0;
-    if (j < b.n) {
+    if (j >= 0) {
         const float2 bx = b.bx[j], by = b.by[j], bz = b.bz[j];
         if (bx.x <= bx.y) {
             uint2 rect = make_uint2(kNoRect, 0u);
             if (CULL) {
                 rect = b.g_rect[j];
-                if (rect.x != kNoRect) {
-                    const unsigned tx0 = rect.x & 0xffffu, tx1 = rect.x >> 16, ty0 = rect.y & 0xffffu, ty1 = rect.y >> 16;
-                    if (b.g_code[j] > cut) {            // every pair of this Gaussian begins beyond the horizon
-                        const int Wd = b.tiles_x + 1;
-                        atomicAdd(&b.tile_diff[ty0 * Wd + tx0], 1);
-                        atomicAdd(&b.tile_diff[ty0 * Wd + tx1 + 1], -1);
-                        atomicAdd(&b.tile_diff[(ty1 + 1) * Wd + tx0], -1);
-                        atomicAdd(&b.tile_diff[(ty1 + 1) * Wd + tx1 + 1], 1);
-                    } else {
-                        count = (int)((tx1 - tx0 + 1) * (ty1 - ty0 + 1));
-                    }
-                }
+                const unsigned tx0 = rect.x & 0xffffu, tx1 = rect.x >> 16, ty0 = rect.y & 0xffffu, ty1 = rect.y >> 16;
+                count = (int)((tx1 - tx0 + 1) * (ty1 - ty0 + 1));
             } else {
                 const Projector p = make_projector(b);
                 count = gaussian_rect(b, p, j, bx, by, bz, rect);
             }
             if (count > 0) {
                 sh.rect[tid] = rect;
+                sh.slot[tid] = j;
                 if (count > kBigRect) {
-                    const unsigned long long at = atomicAdd(b.total_dev + 1, 1ull);
-                    b.big_slot[at] = j;
-                    b.big_rect[at] = rect;
+                    const unsigned long long big_at = atomicAdd(b.total_dev + 1, 1ull);
+                    b.big_slot[big_at] = j;
+                    b.big_rect[big_at] = rect;
                     count = 0;
                 } else {
                     const float kk = sqrtf(2.0f * 0.6931471805599453f * b.hk[j]);
@@ -565,7 +592,7 @@ __global__ void __launch_bounds__(kEmitThreads) bin_emit_kernel(BinLaunch b) {
             float tn = 0.f;
             keep = (!b.tile_flag || b.tile_flag[t] != 0) && pair_range(b.cam.eye, b.tile_dir[t], sh.geom[lo], tn, tf);
             if (CULL && keep && hist_bucket(tn, kl) > cut) { keep = false; b.tile_more[t] = 1; }
-            if (keep) key = pair_key(kl, t, tn, (unsigned)(blockIdx.x * kEmitThreads + lo));
+            if (keep) key = pair_key(kl, t, tn, (unsigned)sh.slot[lo]);
         }
         const unsigned m = __ballot_sync(kFullMask, keep);
         if (m) {
@@ -712,7 +739,7 @@ cudaError_t launch_bin_emit(const BinLaunch& b, cudaStream_t s) {
     const int tb = 256;
     const int ntiles = b.tiles_x * b.tiles_y;
     cudaError_t e;
-    // total_dev: [0] pairs, [1] length of the list of large Gaussians, [2] next of them to take
+    // total_dev: [0] pairs, [1] length of the list of large Gaussians, [2] next of them to take, [3] Gaussians before the cut
     if ((e = cudaMemsetAsync(b.total_dev, 0, 4 * sizeof(unsigned long long), s)) != cudaSuccess) return e;
     const int blocks = (b.n_pad + kEmitThreads - 1) / kEmitThreads;
     if (b.pick) {
@@ -727,6 +754,7 @@ cudaError_t launch_bin_emit(const BinLaunch& b, cudaStream_t s) {
         note_launch(), bin_tile_dirs_kernel<<<(ntiles + tb - 1) / tb, tb, 0, s>>>(b, ntiles);
         note_launch(), bin_near_hist_kernel<<<blocks, kEmitThreads, 0, s>>>(b);
         note_launch(), bin_pick_horizon_kernel<<<1, 1024, 0, s>>>(b);
+        note_launch(), bin_compact_kernel<<<(b.n_pad + 255) / 256, 256, 0, s>>>(b);
         note_launch(), bin_emit_kernel<true><<<blocks, kEmitThreads, 0, s>>>(b);
         note_launch(), bin_emit_big_kernel<true><<<b.big_grid, kBigWarps * 32, 0, s>>>(b);
         note_launch(), bin_tile_more_kernel<<<1, 1024, 0, s>>>(b);

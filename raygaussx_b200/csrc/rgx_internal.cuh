@@ -119,6 +119,7 @@ struct BinLaunch {
     HorizonPick* pick;
     unsigned long long* near_hist;         // [2048] estimated pairs by nearest distance of the Gaussian
     uint2* g_rect; unsigned int* g_code;   // [n_pad] tile rectangle (x = ~0: none) and histogram bucket of every Gaussian
+    int* kept_slot;                        // [n_pad] the Gaussians before the cut, in no particular order; their number in total_dev[3]
     int* tile_diff;                        // [(tiles_x + 1) * (tiles_y + 1)] corners of the rectangles of culled Gaussians
     int* tile_more;                        // [tiles] the tile has pairs that were not emitted
     unsigned long long near_target;        // estimated pairs to keep
