@@ -442,7 +442,7 @@ def main():
     view_ms = ms_per_step / max(1, len(blocks0))
     step_fp32 = (f_fwd + f_bwd) / (view_ms * 1e-3) / fp32_peak
     step_mufu = (mufu_fwd + mufu_bwd) / (view_ms * 1e-3) / mufu_peak
-    roofline = {"kernel": "march_forward_lists_kernel<false,true> (forward march, recording for the backward)",
+    roofline = {"kernel": "march_forward_lists_kernel<false,true,2> (forward march, recording for the backward, over lists that stop at a horizon)",
                 "bound": "fp32-issue", "achieved": achieved, "peak": hbm_peak,
                 "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_src, "traffic": traffic,
                 "traffic_note": "DRAM bytes of one launch: the recording (528 B per slab with hits + 4 B per hit) "
