@@ -261,14 +261,14 @@ RGX_API int rgx_read_two_depth(rgx_ctx* ctx, long long out[4]);
 /* Lists up to a horizon for recording forwards (no counterpart in the reference).  A forward with
  * RGX_FLAG_SAVE_HITS -- a training view, whose rays end long before they have seen most of their tile's list --
  * emits, sorts and lays out only the (tile, Gaussian) pairs that begin nearest to the eye, about `budget_per_ray`
- * per ray (default 6; the horizon is picked on the device from an estimate of the pairs by distance; views with
+ * per ray (default 5; the horizon is picked on the device from an estimate of the pairs by distance; views with
  * fewer than 2^21 estimated pairs, or whose budget covers half of them, get complete lists).  A ray that gets as far
  * as the lists reach is marched again, on the device and before the forward's work on the stream ends, by a search
  * of the acceleration structure that needs no lists: it meets the same Gaussians in another order, so its colour is
  * that of complete lists to summation rounding (1e-5); it is not recorded, and the backward searches it again over
  * complete lists, which it then makes.  Every other ray is bit for bit what complete lists give.  No host
  * synchronisation is added: the number of such rays reaches the host behind the forward and is looked at by the next
- * call on the context; a view that had any makes the budget four times larger for the views to come.
+ * call on the context; a view that had any doubles the budget for the views to come.
  * budget_per_ray = 0 switches the feature off, < 0 leaves it as it is; min_pairs >= 0 replaces the 2^21 (tests use 0
  * to take small views through it).  rgx_read_near_lists returns and clears (views whose lists stopped at a horizon,
  * the estimated number of all pairs of those views, pairs kept, views in which some ray went beyond the horizon); it

@@ -286,7 +286,13 @@ __device__ __forceinline__ unsigned long long pair_key(const KeyLayout& kl, unsi
 }
 
 constexpr int kEmitThreads = 256;
-constexpr int kBigRect = 48;       // Gaussians that cover more tiles than this are left to bin_emit_big_kernel
+// Gaussians that cover more tiles than this are left to bin_emit_big_kernel, a warp each: no search for the
+// candidate's Gaussian, no block-wide barrier per round.  3 M-Gaussian step: 96: 375.9 ms, 48: 371.9, 32: 367.4,
+// 24: 364.9, 16: 363.7, 12: 363.7, 8: 363.5.
+#ifndef RGX_BIG_RECT
+#define RGX_BIG_RECT 12
+#endif
+constexpr int kBigRect = RGX_BIG_RECT;
 constexpr int kEmitBuf = 1280;     // pairs gathered in shared memory between two appends to the global arrays
 
 struct EmitShared {

@@ -335,7 +335,7 @@ def test_lists_up_to_a_horizon_change_nothing(big):
 
     full_rgb, full_grads, st0 = run(0)
     assert st0["views"] == 0
-    near_rgb, near_grads, st1 = run(6)
+    near_rgb, near_grads, st1 = run(5)
     assert st1["views"] == 1 and st1["views_with_rays_beyond"] == 0 and st1["pairs_kept"] * 2 < st1["pairs_estimated"]
     assert torch.equal(near_rgb, full_rgb)
     again_rgb, again_grads, st2 = run(1)            # one pair per ray: far too shallow
@@ -344,8 +344,8 @@ def test_lists_up_to_a_horizon_change_nothing(big):
     for a, b, c in zip(full_grads[:5], near_grads[:5], again_grads[:5]):
         scale = a.abs().max()
         assert ((a - b).abs().max() / scale).item() < 3e-4 and ((a - c).abs().max() / scale).item() < 3e-4
-    # the budget was multiplied by four after that view; put the default back for the tests that follow
-    r.near_lists(6)
+    # the budget was doubled after that view; put the default back for the tests that follow
+    r.near_lists(5)
     # a forward without recording on the cached near lists, and a counting forward (which wants complete lists)
     r.forward(*tens, cs, save)
     plain, _, _ = r.forward(*tens, cs, march(ro, sc, cs))
@@ -410,5 +410,5 @@ def test_lists_up_to_a_horizon_on_small_and_awkward_views(kind, budget):
                 assert near[4]["pairs_kept"] < near[4]["pairs_estimated"]
             print(f"{kind} budget {budget}: {near[4]}")
     finally:
-        r.near_lists(6, 1 << 21)
+        r.near_lists(5, 1 << 21)
         del r
