@@ -10,6 +10,9 @@
 
 using namespace rgx;
 
+#ifndef RGX_BIG_GRID
+#define RGX_BIG_GRID 4            // CTAs per SM of bin_emit_pairs_kernel (2, 4, 8: no difference)
+#endif
 // Pairs per ray that the lists of a recording forward keep.  3 M-Gaussian step: 3: rays reach the horizon, 4: 365.2 ms,
 // 5: 368.6, 6: 371.9, 8: 378.6 -- what is kept has to be emitted, sorted and laid out.
 #ifndef RGX_NEAR_BUDGET
@@ -579,7 +582,7 @@ static int emit_setup(rgx_ctx* ctx, const rgx_camera* cam, const rgx_march* m, B
     b.row_begin = m->row_begin; b.row_end = m->row_end; b.tile = kBinTile;
     b.tiles_x = tiles_x; b.tiles_y = tiles_y; b.ty_first = ty_first;
     b.total_dev = ctx->bin_total_dev;
-    b.big_slot = ctx->big_slot; b.big_rect = ctx->big_rect; b.big_grid = ctx->sm_count * 4;
+    b.big_slot = ctx->big_slot; b.big_rect = ctx->big_rect; b.big_grid = ctx->sm_count * RGX_BIG_GRID;
     if (cull && cull->budget_per_ray > 0) {
         // only the pairs that begin before a horizon are emitted (binning.cu)
         int rc = two_depth_workspace(ctx, ntiles);          // tile_more, and the counter of rays that reach the horizon

@@ -286,42 +286,6 @@ __device__ __forceinline__ unsigned long long pair_key(const KeyLayout& kl, unsi
 }
 
 constexpr int kEmitThreads = 256;
-// Gaussians that cover more tiles than this are left to bin_emit_big_kernel, a warp each: no search for the
-// candidate's Gaussian, no block-wide barrier per round.  3 M-Gaussian step: 96: 375.9 ms, 48: 371.9, 32: 367.4,
-// 24: 364.9, 16: 363.7, 12: 363.7, 8: 363.5.
-#ifndef RGX_BIG_RECT
-#define RGX_BIG_RECT 12
-#endif
-constexpr int kBigRect = RGX_BIG_RECT;
-constexpr int kEmitBuf = 1280;     // pairs gathered in shared memory between two appends to the global arrays
-
-struct EmitShared {
-    PairGeom geom[kEmitThreads];
-    uint2 rect[kEmitThreads];
-    int slot[kEmitThreads];
-    int prefix[kEmitThreads + 1];
-    unsigned long long keys[kEmitBuf];
-    float fars[kEmitBuf];
-    int nbuf;
-    unsigned long long base;
-};
-
-// Appends the gathered pairs to the global arrays: one atomic per call and block.  Pairs
-// past the capacity are counted but not written; the host then grows the arrays and
-// runs the emission again.
-__device__ __forceinline__ void emit_flush(const BinLaunch& b, EmitShared& sh, int tid) {
-    const int n = sh.nbuf;
-    if (tid == 0 && n > 0) sh.base = atomicAdd(b.total_dev, (unsigned long long)n);
-    __syncthreads();
-    const unsigned long long base = sh.base;
-    for (int i = tid; i < n; i += kEmitThreads) {
-        const unsigned long long k = base + (unsigned long long)i;
-        if (k < b.pair_cap) { b.keys_in[k] = sh.keys[i]; b.vals_in[k] = __float_as_uint(sh.fars[i]); }
-    }
-    __syncthreads();
-    if (tid == 0) sh.nbuf = 0;
-    __syncthreads();
-}
 
 // Rectangle of tiles that Gaussian j can touch: the rectangle of its box cut by the rectangle of the oriented box
 // of its truncation ellipsoid.  Returns the number of tiles (0: none, rect untouched).
@@ -525,108 +489,51 @@ __global__ void __launch_bounds__(1024) bin_tile_more_kernel(BinLaunch b) {
     }
 }
 
-// One block per 256 sorted slots.  First every thread finds its Gaussian's rectangle of
-// tiles (box rectangle cut by the rectangle of the oriented box of the truncation
-// ellipsoid).  Then the block walks all (Gaussian, tile) candidates of its 256 Gaussians
-// together, one candidate per thread and round, whatever Gaussian it belongs to -- a
-// Gaussian that covers the screen costs its block a few rounds, not one thread thousands
-// of iterations -- and keeps the pairs in which some ray of the tile can meet the Gaussian.
-// CULL: rectangles and buckets come from bin_near_hist_kernel; what lies beyond the cut is skipped.
-template <bool CULL>
-__global__ void __launch_bounds__(kEmitThreads) bin_emit_kernel(BinLaunch b) {
-    __shared__ EmitShared sh;
-    using Scan = cub::BlockScan<int, kEmitThreads>;
-    __shared__ typename Scan::TempStorage scan_tmp;
-    const int tid = threadIdx.x, lane = tid & 31;
-    const unsigned cut = CULL ? b.pick->cut : kAllBuckets;
-    // CULL: the block's 256 Gaussians come from the list bin_compact_kernel left; blocks past its end have nothing to do
-    const unsigned long long n_kept = CULL ? b.total_dev[3] : (unsigned long long)b.n;
-    const unsigned long long at = (unsigned long long)blockIdx.x * kEmitThreads + tid;
-    if (CULL && (unsigned long long)blockIdx.x * kEmitThreads >= n_kept) return;
-    const int j = at < n_kept ? (CULL ? b.kept_slot[at] : (int)at) : -1;
-    int count = 0;
-    if (j >= 0) {
+// Complete emission, first step: every Gaussian's rectangle of tiles; those that have one are listed (big_slot,
+// big_rect, their number in total_dev[1]) for bin_emit_pairs_kernel.  (A culled emission has the rectangles from
+// bin_near_hist_kernel and the list from bin_compact_kernel.)
+__global__ void __launch_bounds__(kEmitThreads) bin_list_kernel(BinLaunch b) {
+    const int j = blockIdx.x * kEmitThreads + threadIdx.x, lane = threadIdx.x & 31;
+    uint2 rect = make_uint2(kNoRect, 0u);
+    bool keep = false;
+    if (j < b.n) {
         const float2 bx = b.bx[j], by = b.by[j], bz = b.bz[j];
         if (bx.x <= bx.y) {
-            uint2 rect = make_uint2(kNoRect, 0u);
-            if (CULL) {
-                rect = b.g_rect[j];
-                const unsigned tx0 = rect.x & 0xffffu, tx1 = rect.x >> 16, ty0 = rect.y & 0xffffu, ty1 = rect.y >> 16;
-                count = (int)((tx1 - tx0 + 1) * (ty1 - ty0 + 1));
-            } else {
-                const Projector p = make_projector(b);
-                count = gaussian_rect(b, p, j, bx, by, bz, rect);
-            }
-            if (count > 0) {
-                sh.rect[tid] = rect;
-                sh.slot[tid] = j;
-                if (count > kBigRect) {
-                    const unsigned long long big_at = atomicAdd(b.total_dev + 1, 1ull);
-                    b.big_slot[big_at] = j;
-                    b.big_rect[big_at] = rect;
-                    count = 0;
-                } else {
-                    const float kk = sqrtf(2.0f * 0.6931471805599453f * b.hk[j]);
-                    sh.geom[tid] = make_pair_geom(b.cam.eye, bx, by, bz, b.g0[j], b.g1[j], b.g2[j], b.sdens[j], b.quat[j], kk);
-                }
-            }
+            const Projector p = make_projector(b);
+            keep = gaussian_rect(b, p, j, bx, by, bz, rect) > 0;
         }
     }
-    int excl, total;
-    Scan(scan_tmp).ExclusiveSum(count, excl, total);
-    sh.prefix[tid] = excl;
-    if (tid == 0) { sh.prefix[kEmitThreads] = total; sh.nbuf = 0; }
-    __syncthreads();
-
-    const KeyLayout kl = key_layout(b.tiles_x * ((b.cam.height + b.tile - 1) / b.tile), b.n_pad);
-    for (int it0 = 0; it0 < total; it0 += kEmitThreads) {
-        if (sh.nbuf > kEmitBuf - kEmitThreads) emit_flush(b, sh, tid);      // same decision in every thread
-        const int item = it0 + tid;
-        bool keep = false;
-        unsigned long long key = 0;
-        float tf = 0.f;
-        if (item < total) {
-            int lo = 0, hi = kEmitThreads - 1;
-            while (lo < hi) {                       // last slot whose first candidate is not after `item`
-                const int mid = (lo + hi + 1) >> 1;
-                if (sh.prefix[mid] <= item) lo = mid; else hi = mid - 1;
-            }
-            const uint2 rect = sh.rect[lo];
-            const unsigned tx0 = rect.x & 0xffffu, tx1 = rect.x >> 16, ty0 = rect.y & 0xffffu;
-            const unsigned w = tx1 - tx0 + 1, local = (unsigned)(item - sh.prefix[lo]);
-            const unsigned t = (ty0 + local / w) * (unsigned)b.tiles_x + tx0 + local % w;
-            float tn = 0.f;
-            keep = (!b.tile_flag || b.tile_flag[t] != 0) && pair_range(b.cam.eye, b.tile_dir[t], sh.geom[lo], tn, tf);
-            if (CULL && keep && hist_bucket(tn, kl) > cut) { keep = false; b.tile_more[t] = 1; }
-            if (keep) key = pair_key(kl, t, tn, (unsigned)sh.slot[lo]);
-        }
-        const unsigned m = __ballot_sync(kFullMask, keep);
-        if (m) {
-            int at = 0;
-            if (lane == __ffs(m) - 1) at = atomicAdd(&sh.nbuf, __popc(m));
-            at = __shfl_sync(kFullMask, at, __ffs(m) - 1) + __popc(m & ((1u << lane) - 1u));
-            if (keep) { sh.keys[at] = key; sh.fars[at] = tf; }
-        }
-        __syncthreads();
+    const unsigned m = __ballot_sync(kFullMask, keep);
+    if (m) {
+        unsigned long long at = 0;
+        if (lane == __ffs(m) - 1) at = atomicAdd(b.total_dev + 1, (unsigned long long)__popc(m));
+        at = __shfl_sync(kFullMask, at, __ffs(m) - 1) + __popc(m & ((1u << lane) - 1u));
+        if (keep) { b.big_slot[at] = j; b.big_rect[at] = rect; }
     }
-    emit_flush(b, sh, tid);
 }
 
-// The Gaussians that cover many tiles: warps take them one at a time from the list the
-// kernel above left, 32 tiles per step, and gather the kept pairs in a buffer of their
-// own in shared memory.
+// The pairs of the listed Gaussians.  Warps take the Gaussians one at a time, 32 tiles of the rectangle per step:
+// the tile's central ray against the box and the ellipsoid, both grown by the tile's angular radius (pair_range),
+// keeps the pairs in which some ray of the tile can meet the Gaussian.  Every warp gathers its pairs in a buffer
+// of its own in shared memory and appends them with one atomic per 256; pairs past the capacity are counted but
+// not written (the host then grows the arrays and runs the emission again).
+// An earlier version walked the candidates of 256 Gaussians block-wide, one candidate per thread whatever
+// Gaussian it belonged to, and left only Gaussians of more than 48 tiles to this kernel; the search for the
+// candidate's Gaussian and a block-wide barrier per round cost more than the idle lanes of small rectangles do here
+// (3 M-Gaussian step by that threshold: 96: 375.9 ms, 48: 371.9, 24: 364.9, 12: 363.7, 4: 362.4, 0: 361.7).
+// CULL: the list is bin_compact_kernel's; single pairs that begin beyond the cut are dropped and their tile marked.
 constexpr int kBigWarps = 8;
 constexpr int kBigBuf = 256;
 
 template <bool CULL>
-__global__ void __launch_bounds__(kBigWarps * 32) bin_emit_big_kernel(BinLaunch b) {
+__global__ void __launch_bounds__(kBigWarps * 32) bin_emit_pairs_kernel(BinLaunch b) {
     const unsigned cut = CULL ? b.pick->cut : kAllBuckets;
     __shared__ unsigned long long s_keys[kBigWarps][kBigBuf];
     __shared__ float s_fars[kBigWarps][kBigBuf];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     unsigned long long* keys = s_keys[warp];
     float* fars = s_fars[warp];
-    const unsigned long long nbig = b.total_dev[1];
+    const unsigned long long nlisted = CULL ? b.total_dev[3] : b.total_dev[1];
     const KeyLayout kl = key_layout(b.tiles_x * ((b.cam.height + b.tile - 1) / b.tile), b.n_pad);
     int nbuf = 0;
     auto flush = [&]() {
@@ -645,9 +552,9 @@ __global__ void __launch_bounds__(kBigWarps * 32) bin_emit_big_kernel(BinLaunch 
         unsigned long long idx = 0;
         if (lane == 0) idx = atomicAdd(b.total_dev + 2, 1ull);
         idx = __shfl_sync(kFullMask, idx, 0);
-        if (idx >= nbig) break;
-        const int j = b.big_slot[idx];
-        const uint2 rect = b.big_rect[idx];
+        if (idx >= nlisted) break;
+        const int j = CULL ? b.kept_slot[idx] : b.big_slot[idx];
+        const uint2 rect = CULL ? b.g_rect[j] : b.big_rect[idx];
         const float4 sd = b.sdens[j];
         const float kk = sqrtf(2.0f * 0.6931471805599453f * b.hk[j]);
         const PairGeom g = make_pair_geom(b.cam.eye, b.bx[j], b.by[j], b.bz[j], b.g0[j], b.g1[j], b.g2[j], sd, b.quat[j], kk);
@@ -745,7 +652,8 @@ cudaError_t launch_bin_emit(const BinLaunch& b, cudaStream_t s) {
     const int tb = 256;
     const int ntiles = b.tiles_x * b.tiles_y;
     cudaError_t e;
-    // total_dev: [0] pairs, [1] length of the list of large Gaussians, [2] next of them to take, [3] Gaussians before the cut
+    // total_dev: [0] pairs, [1] Gaussians listed by bin_list_kernel, [2] next listed Gaussian to take, [3] Gaussians
+    // listed by bin_compact_kernel
     if ((e = cudaMemsetAsync(b.total_dev, 0, 4 * sizeof(unsigned long long), s)) != cudaSuccess) return e;
     const int blocks = (b.n_pad + kEmitThreads - 1) / kEmitThreads;
     if (b.pick) {
@@ -761,14 +669,13 @@ cudaError_t launch_bin_emit(const BinLaunch& b, cudaStream_t s) {
         note_launch(), bin_near_hist_kernel<<<blocks, kEmitThreads, 0, s>>>(b);
         note_launch(), bin_pick_horizon_kernel<<<1, 1024, 0, s>>>(b);
         note_launch(), bin_compact_kernel<<<(b.n_pad + 255) / 256, 256, 0, s>>>(b);
-        note_launch(), bin_emit_kernel<true><<<blocks, kEmitThreads, 0, s>>>(b);
-        note_launch(), bin_emit_big_kernel<true><<<b.big_grid, kBigWarps * 32, 0, s>>>(b);
+        note_launch(), bin_emit_pairs_kernel<true><<<b.big_grid, kBigWarps * 32, 0, s>>>(b);
         note_launch(), bin_tile_more_kernel<<<1, 1024, 0, s>>>(b);
         return cudaGetLastError();
     }
     note_launch(), bin_tile_dirs_kernel<<<(ntiles + tb - 1) / tb, tb, 0, s>>>(b, ntiles);
-    note_launch(), bin_emit_kernel<false><<<blocks, kEmitThreads, 0, s>>>(b);
-    note_launch(), bin_emit_big_kernel<false><<<b.big_grid, kBigWarps * 32, 0, s>>>(b);
+    note_launch(), bin_list_kernel<<<blocks, kEmitThreads, 0, s>>>(b);
+    note_launch(), bin_emit_pairs_kernel<false><<<b.big_grid, kBigWarps * 32, 0, s>>>(b);
     return cudaGetLastError();
 }
 

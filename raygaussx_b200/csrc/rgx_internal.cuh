@@ -113,7 +113,7 @@ struct BinLaunch {
     float4* tile_dir;                      // [tiles] central ray direction, chord to the farthest corner ray
     void* cub_temp; size_t cub_bytes;
     unsigned long long* total_dev;         // [4]; [0] = number of pairs met by the emission (may exceed pair_cap)
-    int* big_slot; uint2* big_rect;        // [n_pad] Gaussians that cover many tiles, and their tile rectangles
+    int* big_slot; uint2* big_rect;        // [n_pad] complete emission: the Gaussians that touch a tile, and their tile rectangles
     int big_grid;                          // CTAs that work the list off (a few per SM)
     // culled emission (null / unused for a complete one): only the pairs that begin before a horizon are emitted
     HorizonPick* pick;
