@@ -317,7 +317,7 @@ __device__ __forceinline__ SlabPlan plan_slab(const rgx_march& m, float tbuffer,
     SlabPlan p;
     p.dt = m.dt_step;
     if (m.dynamic_sampling) {
-        float dt_dist = fmaxf(__fdiv_rn(tbuffer, 1024.0f), m.dt_step);
+        float dt_dist = fmaxf(__fmul_rn(tbuffer, 0.0009765625f), m.dt_step);      // t / 1024: a power of two, the same bits as the division
         p.dt = fminf(__fmul_rn(dt_dist, rcbrtf(T)), __fmul_rn(4.0f, m.dt_step));
     }
     p.slab = __fmul_rn(p.dt, (float)kSlab);

@@ -30,10 +30,10 @@ constexpr int kThreads = kWarps * 32;
 // of a tile is only loosely predicted by the length of its list, so the kernels used to end with a few long
 // tiles on otherwise idle SMs (6 % of their time on the 3 M-Gaussian view); smaller units shorten that tail.
 #ifndef RGX_TILE_SPLIT
-#define RGX_TILE_SPLIT 4          // 3 M-Gaussian step: 1: 440.3 ms, 2: 432.2, 4: 428.5, 8: 427.6
+#define RGX_TILE_SPLIT 8          // 3 M-Gaussian step: 1: 440.3 ms, 2: 432.2, 4: 428.5, 8: 427.6 (later: 4: 358.5, 8: 357.5)
 #endif
 #ifndef RGX_REPLAY_SPLIT
-#define RGX_REPLAY_SPLIT RGX_TILE_SPLIT
+#define RGX_REPLAY_SPLIT 4        // 2: 361.2 ms, 4: 358.5, 8: 358.5
 #endif
 constexpr int kTileSplit = RGX_TILE_SPLIT;
 constexpr int kRaysPerCta = kRaysPerTile / kTileSplit;
